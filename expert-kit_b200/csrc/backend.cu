@@ -1,0 +1,1147 @@
+// Host side of the C ABI: expert registry (the worker's ExpertDB), weight loader that re-tiles
+// bundles into the device layout, workspace, and the forward entry points that chain the
+// kernels on one stream.
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <set>
+#include <shared_mutex>
+#include <string>
+#include <vector>
+
+#include "ek_internal.h"
+#include "safetensors.hpp"
+
+using namespace ek;
+
+namespace {
+
+struct Layer {
+  uint8_t* gu = nullptr;
+  uint8_t* dn = nullptr;
+  float* gu_scale = nullptr;
+  float* dn_scale = nullptr;
+  int32_t* registered = nullptr;     // device flags [n_slots]
+  std::vector<char> host_registered;
+  void* router_w = nullptr;
+  int router_f32 = 0;
+  float* router_bias = nullptr;
+  int32_t* last_counts = nullptr;    // device [E]
+  bool have_counts = false;
+};
+
+struct ExpertRef {
+  int layer;
+  int slot;
+};
+
+}  // namespace
+
+struct ek_backend {
+  ek_config_t cfg;
+  Dims d;
+  int n_local = 0, e_lo = 0, e_hi = 0, n_slots = 0;
+  int n_sm = 148;
+  int rows_cap = 0, max_chunks = 0;
+  cudaStream_t stream = nullptr;       // forward stream (owned unless replaced by ek_set_stream)
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t load_stream = nullptr;
+  cudaEvent_t fwd_done = nullptr;
+  cudaEvent_t ev[EK_STAGE_COUNT + 1] = {};
+  bool timing = false;
+  float stage_ms[EK_STAGE_COUNT] = {};
+  int ffn_impl = 0;                    // 0 tensor cores, 1 CUDA-core checker
+
+  // workspace
+  __nv_bfloat16 *x_dev = nullptr, *y_dev = nullptr, *xp = nullptr, *hbuf = nullptr, *obuf = nullptr;
+  __nv_bfloat16* tk_dev = nullptr;     // [T,k,H] staging of the controller-level call (lazy)
+  size_t tk_cap = 0;
+  float *logits = nullptr, *weights = nullptr, *bias_scratch = nullptr;
+  int32_t *ids = nullptr, *counts = nullptr, *offsets = nullptr, *perm = nullptr, *inv = nullptr;
+  ChunkDesc* chunks = nullptr;
+  int32_t* n_chunks = nullptr;
+  DevStatus* status = nullptr;
+  DevStatus* h_status = nullptr;       // pinned
+  ChunkDesc* h_chunks = nullptr;       // pinned, worker-level call
+  CUtensorMap* maps = nullptr;         // device: x_maps[4], h_maps[4]
+  void* h_x = nullptr;                 // pinned staging
+  void* h_y = nullptr;
+  size_t h_cap = 0;
+  void* h_tk = nullptr;
+  size_t h_tk_cap = 0;
+  // loader staging
+  void* stage[3] = {nullptr, nullptr, nullptr};
+  size_t stage_cap[3] = {0, 0, 0};
+  float* stage_scale[3] = {nullptr, nullptr, nullptr};
+  size_t stage_scale_cap[3] = {0, 0, 0};
+  void* stage_cvt = nullptr;
+  size_t stage_cvt_cap = 0;
+
+  std::map<int, Layer> layers;
+  std::map<std::string, ExpertRef> experts;   // BTreeMap<String, Arc<ExpertBackend>>
+  std::set<std::string> loading;
+  mutable std::shared_mutex reg_mu;           // the worker's RwLock around ExpertDB
+  std::mutex fwd_mu;                          // forwards share one workspace
+  std::mutex load_mu;                         // loads share the staging buffers
+  mutable std::mutex err_mu;
+  mutable std::string err;
+  std::atomic<int64_t> launches{0};
+};
+
+namespace {
+
+int fail(const ek_backend* be, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (be) {
+    std::lock_guard<std::mutex> g(be->err_mu);
+    be->err = buf;
+  }
+  return code;
+}
+
+#define CK(call)                                                                              \
+  do {                                                                                        \
+    cudaError_t e__ = (call);                                                                 \
+    if (e__ != cudaSuccess)                                                                   \
+      return fail(be, EK_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, __LINE__); \
+  } while (0)
+
+bool is_device_ptr(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+bool ends_with(const std::string& s, const char* suf) {
+  size_t n = strlen(suf);
+  return s.size() >= n && memcmp(s.data() + s.size() - n, suf, n) == 0;
+}
+
+// "model/l{L}-e{E}" (ExpertKey::from_expert_id, ek-db/src/safetensor/mod.rs:57-73) or
+// "model/l{L}-shared".  Returns false on a malformed id.
+bool parse_id(const std::string& id, std::string& model, int& layer, int& expert, bool& shared) {
+  size_t p = id.rfind("/l");
+  if (p == std::string::npos) return false;
+  model = id.substr(0, p);
+  std::string rest = id.substr(p + 2);
+  size_t q = rest.find('-');
+  if (q == std::string::npos || q == 0) return false;
+  for (size_t i = 0; i < q; ++i)
+    if (rest[i] < '0' || rest[i] > '9') return false;
+  layer = atoi(rest.substr(0, q).c_str());
+  std::string tail = rest.substr(q + 1);
+  if (tail == "shared") {
+    shared = true;
+    expert = -1;
+    return true;
+  }
+  shared = false;
+  if (tail.size() < 2 || tail[0] != 'e') return false;
+  for (size_t i = 1; i < tail.size(); ++i)
+    if (tail[i] < '0' || tail[i] > '9') return false;
+  expert = atoi(tail.c_str() + 1);
+  return true;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+int make_maps(ek_backend* be) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess)
+    return fail(be, EK_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+  EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(fn);
+  CUtensorMap host[8];
+  const int rows_box[4] = {16, 32, 64, 128};
+  for (int which = 0; which < 2; ++which) {
+    void* base = which == 0 ? (void*)be->xp : (void*)be->hbuf;
+    const uint64_t inner = which == 0 ? (uint64_t)be->d.H : (uint64_t)be->d.Ip;
+    for (int i = 0; i < 4; ++i) {
+      cuuint64_t gdim[2] = {inner, (cuuint64_t)be->rows_cap};
+      cuuint64_t gstride[1] = {inner * 2};
+      cuuint32_t box[2] = {64, (cuuint32_t)rows_box[i]};
+      cuuint32_t estr[2] = {1, 1};
+      CUresult r = encode(&host[which * 4 + i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, gdim, gstride, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return fail(be, EK_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    }
+  }
+  CK(cudaMemcpy(be->maps, host, sizeof host, cudaMemcpyHostToDevice));
+  return EK_OK;
+}
+
+int ensure_layer(ek_backend* be, int layer, Layer** out) {
+  auto it = be->layers.find(layer);
+  if (it != be->layers.end()) {
+    *out = &it->second;
+    return EK_OK;
+  }
+  if ((int)be->layers.size() >= be->cfg.max_layers)
+    return fail(be, EK_INVALID_INPUT, "layer %d exceeds max_layers=%d", layer, be->cfg.max_layers);
+  Layer L;
+  const Dims& d = be->d;
+  const size_t gu_bytes = (size_t)be->n_slots * d.it * d.kt_gu * 2 * kTileBytes;
+  const size_t dn_bytes = (size_t)be->n_slots * d.ht * d.kt_dn * kTileBytes;
+  CK(cudaMalloc(&L.gu, gu_bytes));
+  CK(cudaMalloc(&L.dn, dn_bytes));
+  if (d.quant != EK_QUANT_BF16) {
+    CK(cudaMalloc(&L.gu_scale, (size_t)be->n_slots * d.it * d.kt_gu * 2 * sizeof(float)));
+    CK(cudaMalloc(&L.dn_scale, (size_t)be->n_slots * d.ht * d.kt_dn * sizeof(float)));
+  }
+  CK(cudaMalloc(&L.registered, sizeof(int32_t) * be->n_slots));
+  CK(cudaMemset(L.registered, 0, sizeof(int32_t) * be->n_slots));
+  CK(cudaMalloc(&L.last_counts, sizeof(int32_t) * be->cfg.n_experts));
+  CK(cudaMemset(L.last_counts, 0, sizeof(int32_t) * be->cfg.n_experts));
+  L.host_registered.assign(be->n_slots, 0);
+  auto ins = be->layers.emplace(layer, L);
+  *out = &ins.first->second;
+  return EK_OK;
+}
+
+void free_layer(Layer& L) {
+  cudaFree(L.gu);
+  cudaFree(L.dn);
+  cudaFree(L.gu_scale);
+  cudaFree(L.dn_scale);
+  cudaFree(L.registered);
+  cudaFree(L.router_w);
+  cudaFree(L.router_bias);
+  cudaFree(L.last_counts);
+}
+
+int grow(ek_backend* be, void** buf, size_t* cap, size_t need) {
+  if (*cap >= need) return EK_OK;
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr;
+  *cap = 0;
+  CK(cudaMalloc(buf, need));
+  *cap = need;
+  return EK_OK;
+}
+
+const ek_tensor_view_t* find_suffix(const ek_tensor_view_t* t, int n, const char* a, const char* b) {
+  // first tensor (in bundle order) whose name ends with either suffix
+  // (lookup_suffix, ek-computation/src/backend/torch/mod.rs:137-153)
+  for (int i = 0; i < n; ++i) {
+    std::string nm = t[i].name ? t[i].name : "";
+    if (ends_with(nm, a) || ends_with(nm, b)) return &t[i];
+  }
+  return nullptr;
+}
+const ek_tensor_view_t* find_exact(const ek_tensor_view_t* t, int n, const std::string& name) {
+  for (int i = 0; i < n; ++i)
+    if (t[i].name && name == t[i].name) return &t[i];
+  return nullptr;
+}
+
+FfnParams ffn_params(ek_backend* be, const Layer& L) {
+  FfnParams p;
+  p.d = be->d;
+  p.w.gu_tiles = L.gu;
+  p.w.dn_tiles = L.dn;
+  p.w.gu_scale = L.gu_scale;
+  p.w.dn_scale = L.dn_scale;
+  p.w.registered = L.registered;
+  p.w.n_slots = be->n_slots;
+  p.chunks = be->chunks;
+  p.n_chunks = be->n_chunks;
+  p.xp = be->xp;
+  p.hbuf = be->hbuf;
+  p.obuf = be->obuf;
+  p.rows_cap = be->rows_cap;
+  p.max_chunks = be->max_chunks;
+  p.status = be->status;
+  p.chunk_rows = 0;
+  p.x_maps = be->maps;
+  p.h_maps = be->maps + 4;
+  p.n_sm = be->n_sm;
+  return p;
+}
+
+int pick_nmax(int rows, int n_segments) {
+  const int avg = n_segments > 0 ? (rows + n_segments - 1) / n_segments : rows;
+  return avg <= 20 ? 32 : avg <= 48 ? 64 : 128;
+}
+
+void mark(ek_backend* be, int i) {
+  if (be->timing) cudaEventRecord(be->ev[i], be->stream);
+}
+
+int finish_timing(ek_backend* be) {
+  if (!be->timing) return EK_OK;
+  CK(cudaEventSynchronize(be->ev[EK_STAGE_COUNT]));
+  for (int i = 0; i < EK_STAGE_COUNT; ++i) cudaEventElapsedTime(&be->stage_ms[i], be->ev[i], be->ev[i + 1]);
+  return EK_OK;
+}
+
+// Runs gate/up + down over the work list already on the device.
+void run_ffn(ek_backend* be, const Layer& L, int nmax, int which) {
+  FfnParams p = ffn_params(be, L);
+  if (be->ffn_impl == 1) {
+    p.chunk_rows = 16;
+    be->launches += launch_ffn_simt(p, which, be->stream);
+  } else {
+    p.chunk_rows = nmax;
+    be->launches += launch_ffn_tc(p, nmax, which, be->stream);
+  }
+}
+
+int check_status(ek_backend* be) {
+  CK(cudaMemcpyAsync(be->h_status, be->status, sizeof(DevStatus), cudaMemcpyDeviceToHost, be->stream));
+  CK(cudaStreamSynchronize(be->stream));
+  const DevStatus st = *be->h_status;
+  if (st.code == DEV_OK) return EK_OK;
+  cudaMemsetAsync(be->status, 0, sizeof(DevStatus), be->stream);
+  cudaStreamSynchronize(be->stream);
+  switch (st.code) {
+    case DEV_TIMEOUT:
+      return fail(be, EK_TIMEOUT, "device-side wait ran out (where=%d item=%d k=%d)", st.where, st.aux0, st.aux1);
+    case DEV_MISSING_EXPERT:
+      if (st.aux0 < 0)
+        return fail(be, EK_EXPERT_NOT_FOUND, "shared expert %d of the layer is not registered", -1 - st.aux0);
+      return fail(be, EK_EXPERT_NOT_FOUND, "expert %d selected by routing is not registered", st.aux0);
+    default:
+      return fail(be, EK_BOUNDS, "device-side index check failed (where=%d a0=%d a1=%d)", st.where, st.aux0, st.aux1);
+  }
+}
+
+// Stage timers, routing, bucketing, gather, FFN, combine on device buffers.  `x` is a device
+// pointer to [T,H]; result in `y` (device [T,H]) or, for the controller-level call
+// (given_ids != nullptr), in `out_tk` (device [T,k,H]).
+int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, const int32_t* given_ids_dev,
+              __nv_bfloat16* y, __nv_bfloat16* out_tk) {
+  const ek_config_t& c = be->cfg;
+  const int Tk = T * k;
+  const bool fused = given_ids_dev == nullptr;
+  const int n_shared = fused ? c.n_shared_experts : 0;
+  cudaStream_t s = be->stream;
+  mark(be, 0);
+  const int32_t* ids = given_ids_dev;
+  if (fused) {
+    RouteParams rp;
+    rp.x = x;
+    rp.wg = L.router_w;
+    rp.wg_f32 = L.router_f32;
+    rp.bias = L.router_bias;
+    rp.logits = be->logits;
+    rp.ids = be->ids;
+    rp.weights = be->weights;
+    rp.counts = be->counts;
+    rp.T = T; rp.H = c.hidden; rp.E = c.n_experts; rp.k = k;
+    rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
+    rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling;
+    rp.bf16_weights = c.bf16_combine;
+    be->launches += launch_router_logits(rp, s);
+    be->launches += launch_route_select(rp, s);
+    ids = be->ids;
+  } else {
+    be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
+  }
+  mark(be, 1);
+  PermuteParams pp;
+  pp.ids = ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
+  pp.T = T; pp.k = k; pp.E = c.n_experts; pp.e_lo = be->e_lo; pp.e_hi = be->e_hi;
+  be->launches += launch_permute(pp, s);
+  const int nmax = pick_nmax(Tk, be->n_local);
+  WorklistParams wp;
+  wp.counts = be->counts; wp.offsets = be->offsets; wp.registered = L.registered;
+  wp.chunks = be->chunks; wp.n_chunks = be->n_chunks;
+  wp.E = c.n_experts; wp.e_lo = be->e_lo; wp.e_hi = be->e_hi;
+  wp.chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
+  wp.n_shared = n_shared; wp.T = T; wp.Tk = Tk;
+  wp.max_chunks = be->max_chunks;
+  wp.status = be->status;
+  be->launches += launch_worklist(wp, s);
+  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, n_shared > 0, s);
+  cudaMemcpyAsync(L.last_counts, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s);
+  L.have_counts = true;
+  mark(be, 2);
+  run_ffn(be, L, nmax, 0);
+  mark(be, 3);
+  run_ffn(be, L, nmax, 1);
+  mark(be, 4);
+  if (fused) {
+    CombineParams cp;
+    cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = y;
+    cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = n_shared; cp.Tk = Tk;
+    cp.bf16_products = c.bf16_combine;
+    be->launches += launch_combine(cp, s);
+  } else {
+    be->launches += launch_unpermute(be->obuf, be->inv, out_tk, T, k, c.hidden, s);
+  }
+  mark(be, 5);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(be, EK_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return EK_OK;
+}
+
+}  // namespace
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+extern "C" {
+
+const char* ek_status_name(int32_t s) {
+  switch (s) {
+    case EK_OK: return "EK_OK";
+    case EK_EXPERT_NOT_FOUND: return "EK_EXPERT_NOT_FOUND";
+    case EK_EXPERT_WEIGHT_NOT_FOUND: return "EK_EXPERT_WEIGHT_NOT_FOUND";
+    case EK_INVALID_INPUT: return "EK_INVALID_INPUT";
+    case EK_SAFETENSOR: return "EK_SAFETENSOR";
+    case EK_NOT_FOUND: return "EK_NOT_FOUND";
+    case EK_CUDA: return "EK_CUDA";
+    case EK_TIMEOUT: return "EK_TIMEOUT";
+    case EK_BOUNDS: return "EK_BOUNDS";
+    case EK_NO_MEMORY: return "EK_NO_MEMORY";
+    case EK_UNSUPPORTED: return "EK_UNSUPPORTED";
+  }
+  return "EK_UNKNOWN";
+}
+
+const char* ek_last_error(const ek_backend_t* be) {
+  if (!be) return "";
+  std::lock_guard<std::mutex> g(be->err_mu);
+  static thread_local std::string copy;
+  copy = be->err;
+  return copy.c_str();
+}
+
+static std::string g_create_error;
+const char* ek_create_error(void) { return g_create_error.c_str(); }
+
+int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
+  if (!cfg || !out) return EK_INVALID_INPUT;
+  *out = nullptr;
+  const ek_config_t& c = *cfg;
+  auto bad = [&](const char* m) {
+    g_create_error = m;
+    return (int32_t)EK_INVALID_INPUT;
+  };
+  if (c.hidden < 8 || c.hidden % 8) return bad("hidden must be a positive multiple of 8");
+  if (c.intermediate < 8 || c.intermediate % 8) return bad("intermediate must be a positive multiple of 8");
+  if (c.n_experts < 1 || c.n_experts > 1024) return bad("n_experts must be in [1,1024]");
+  if (c.top_k < 1 || c.top_k > 32 || c.top_k > c.n_experts) return bad("top_k must be in [1,min(32,n_experts)]");
+  if (c.n_group < 1 || c.n_group > 64 || c.n_experts % c.n_group) return bad("n_group must divide n_experts and be <= 64");
+  if (c.topk_group < 1 || c.topk_group > c.n_group) return bad("topk_group must be in [1,n_group]");
+  if (c.quant < 0 || c.quant > 2) return bad("unknown quant");
+  if (c.max_tokens < 1) return bad("max_tokens must be positive");
+  if (c.ep_size < 1 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.n_experts % c.ep_size)
+    return bad("ep_size must divide n_experts and ep_rank be in [0,ep_size)");
+  if (c.n_shared_experts < 0 || c.n_shared_experts > 8) return bad("n_shared_experts must be in [0,8]");
+  if (c.max_layers < 1) return bad("max_layers must be positive");
+
+  ek_backend* be = new ek_backend();
+  be->cfg = c;
+  be->cfg.model_name[sizeof(be->cfg.model_name) - 1] = 0;
+  auto cleanup_fail = [&](int code) {
+    g_create_error = be->err;
+    ek_backend_destroy(be);
+    return (int32_t)code;
+  };
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    cudaGetLastError();
+    g_create_error = "no CUDA device: this backend has no CPU path";
+    delete be;
+    return EK_CUDA;
+  }
+  if (cudaSetDevice(c.device) != cudaSuccess) {
+    g_create_error = "cudaSetDevice failed";
+    delete be;
+    return EK_CUDA;
+  }
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, c.device);
+  if (prop.major != 10) {
+    g_create_error = "this library is built for sm_100a (B200) only";
+    delete be;
+    return EK_UNSUPPORTED;
+  }
+  be->n_sm = prop.multiProcessorCount;
+  Dims& d = be->d;
+  d.H = c.hidden; d.I = c.intermediate;
+  d.Hp = round_up(c.hidden, 128); d.Ip = round_up(c.intermediate, 128);
+  d.quant = c.quant;
+  const int tk = tile_k_elems(c.quant);
+  d.kt_gu = d.Hp / tk; d.kt_dn = d.Ip / tk; d.it = d.Ip / 128; d.ht = d.Hp / 128;
+  be->n_local = c.n_experts / c.ep_size;
+  be->e_lo = c.ep_rank * be->n_local;
+  be->e_hi = be->e_lo + be->n_local;
+  be->n_slots = be->n_local + c.n_shared_experts;
+  be->rows_cap = round_up(c.max_tokens * (c.top_k + c.n_shared_experts), 128) + 128;
+  be->max_chunks = be->rows_cap / 16 + be->n_slots + c.n_shared_experts * (c.max_tokens / 16 + 1) + 8;
+
+#define CKC(call)                                                                                  \
+  do {                                                                                             \
+    cudaError_t e__ = (call);                                                                      \
+    if (e__ != cudaSuccess) {                                                                      \
+      fail(be, EK_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__));                          \
+      return cleanup_fail(e__ == cudaErrorMemoryAllocation ? EK_NO_MEMORY : EK_CUDA);              \
+    }                                                                                              \
+  } while (0)
+  CKC(cudaStreamCreateWithFlags(&be->own_stream, cudaStreamNonBlocking));
+  be->stream = be->own_stream;
+  CKC(cudaStreamCreateWithFlags(&be->load_stream, cudaStreamNonBlocking));
+  CKC(cudaEventCreateWithFlags(&be->fwd_done, cudaEventDisableTiming));
+  for (auto& e : be->ev) CKC(cudaEventCreate(&e));
+  const size_t T = c.max_tokens, H = c.hidden, E = c.n_experts, K = c.top_k;
+  CKC(cudaMalloc(&be->x_dev, T * H * 2));
+  CKC(cudaMalloc(&be->y_dev, T * H * 2));
+  CKC(cudaMalloc(&be->xp, (size_t)be->rows_cap * H * 2));
+  CKC(cudaMalloc(&be->hbuf, (size_t)be->rows_cap * d.Ip * 2));
+  CKC(cudaMalloc(&be->obuf, (size_t)be->rows_cap * H * 2));
+  CKC(cudaMemset(be->xp, 0, (size_t)be->rows_cap * H * 2));
+  CKC(cudaMemset(be->hbuf, 0, (size_t)be->rows_cap * d.Ip * 2));
+  CKC(cudaMalloc(&be->logits, T * E * 4));
+  CKC(cudaMalloc(&be->weights, T * K * 4));
+  CKC(cudaMalloc(&be->bias_scratch, E * 4));
+  CKC(cudaMalloc(&be->ids, T * K * 4));
+  CKC(cudaMalloc(&be->counts, E * 4));
+  CKC(cudaMalloc(&be->offsets, (E + 1) * 4));
+  CKC(cudaMalloc(&be->perm, T * K * 4));
+  CKC(cudaMalloc(&be->inv, T * K * 4));
+  CKC(cudaMalloc(&be->chunks, sizeof(ChunkDesc) * be->max_chunks));
+  CKC(cudaMalloc(&be->n_chunks, 4));
+  CKC(cudaMalloc(&be->status, sizeof(DevStatus)));
+  CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
+  CKC(cudaMallocHost(&be->h_status, sizeof(DevStatus)));
+  CKC(cudaMallocHost(&be->h_chunks, sizeof(ChunkDesc) * 1024));
+  CKC(cudaMalloc(&be->maps, sizeof(CUtensorMap) * 8));
+  be->h_cap = T * H * 2;
+  CKC(cudaMallocHost(&be->h_x, be->h_cap));
+  CKC(cudaMallocHost(&be->h_y, be->h_cap));
+#undef CKC
+  int rc = make_maps(be);
+  if (rc != EK_OK) return cleanup_fail(rc);
+  const char* impl = getenv("EK_B200_FFN_IMPL");
+  if (impl && std::string(impl) == "simt") be->ffn_impl = 1;
+  *out = be;
+  return EK_OK;
+}
+
+void ek_backend_destroy(ek_backend_t* be) {
+  if (!be) return;
+  cudaSetDevice(be->cfg.device);
+  if (be->own_stream) cudaStreamSynchronize(be->own_stream);
+  if (be->load_stream) cudaStreamSynchronize(be->load_stream);
+  for (auto& kv : be->layers) free_layer(kv.second);
+  cudaFree(be->x_dev); cudaFree(be->y_dev); cudaFree(be->xp); cudaFree(be->hbuf); cudaFree(be->obuf);
+  cudaFree(be->tk_dev);
+  cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->ids); cudaFree(be->counts);
+  cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
+  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->maps);
+  cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
+  cudaFreeHost(be->h_tk);
+  for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
+  cudaFree(be->stage_cvt);
+  for (auto& e : be->ev) if (e) cudaEventDestroy(e);
+  if (be->fwd_done) cudaEventDestroy(be->fwd_done);
+  if (be->own_stream) cudaStreamDestroy(be->own_stream);
+  if (be->load_stream) cudaStreamDestroy(be->load_stream);
+  delete be;
+}
+
+// ---- registry --------------------------------------------------------------------------------
+
+int32_t ek_expert_mark_loading(ek_backend_t* be, const char* id, int32_t* fresh) {
+  if (!be || !id) return EK_INVALID_INPUT;
+  std::unique_lock<std::shared_mutex> g(be->reg_mu);
+  bool was = be->loading.count(id) > 0;
+  be->loading.insert(id);
+  if (fresh) *fresh = was ? 0 : 1;
+  return EK_OK;
+}
+
+int32_t ek_expert_has(const ek_backend_t* be, const char* id) {
+  if (!be || !id) return 0;
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  return (be->loading.count(id) || be->experts.count(id)) ? 1 : 0;
+}
+int32_t ek_expert_loaded(const ek_backend_t* be) {
+  if (!be) return 0;
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  return (int32_t)be->experts.size();
+}
+int32_t ek_expert_loading(const ek_backend_t* be) {
+  if (!be) return 0;
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  return (int32_t)be->loading.size();
+}
+int32_t ek_expert_keys(const ek_backend_t* be, char* buf, size_t cap, size_t* needed) {
+  if (!be) return EK_INVALID_INPUT;
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  std::string all;
+  for (auto& kv : be->experts) {
+    if (!all.empty()) all.push_back('\n');
+    all += kv.first;
+  }
+  if (needed) *needed = all.size() + 1;
+  if (!buf || cap < all.size() + 1) return EK_INVALID_INPUT;
+  memcpy(buf, all.c_str(), all.size() + 1);
+  return EK_OK;
+}
+
+int32_t ek_expert_evict(ek_backend_t* be, const char* id) {
+  if (!be || !id) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::unique_lock<std::shared_mutex> g(be->reg_mu);
+  auto it = be->experts.find(id);
+  if (it == be->experts.end()) return EK_OK;   // ExpertDB::remove ignores unknown ids
+  Layer& L = be->layers[it->second.layer];
+  const int slot = it->second.slot;
+  L.host_registered[slot] = 0;
+  // forwards already queued keep reading the slot; the flag flips behind them on the same stream
+  const int32_t zero = 0;
+  cudaMemcpyAsync(L.registered + slot, &zero, sizeof zero, cudaMemcpyHostToDevice, be->stream);
+  cudaStreamSynchronize(be->stream);
+  be->experts.erase(it);
+  return EK_OK;
+}
+
+int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_view_t* t, int32_t n) {
+  if (!be || !id || (!t && n > 0)) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  const ek_config_t& c = be->cfg;
+  const Dims& d = be->d;
+  std::string model;
+  int layer = 0, expert = 0;
+  bool shared = false;
+  if (!parse_id(id, model, layer, expert, shared)) return fail(be, EK_INVALID_INPUT, "invalid expert id: %s", id);
+  if (c.model_name[0] && model != c.model_name)
+    return fail(be, EK_INVALID_INPUT, "expert id %s does not belong to model %s", id, c.model_name);
+  if (shared && c.n_shared_experts == 0) return fail(be, EK_INVALID_INPUT, "layer has no shared expert: %s", id);
+  if (!shared && (expert < be->e_lo || expert >= be->e_hi))
+    return fail(be, EK_INVALID_INPUT, "expert %d is not in this rank's range [%d,%d)", expert, be->e_lo, be->e_hi);
+
+  // ExpertWeight::from_safetensor (ek-computation/src/ffn/meta.rs:57-75)
+  const ek_tensor_view_t* up = find_suffix(t, n, "w1.weight", "up_proj.weight");
+  if (!up) return fail(be, EK_EXPERT_WEIGHT_NOT_FOUND, "w1/up_w");
+  const ek_tensor_view_t* down = find_suffix(t, n, "w2.weight", "down_proj.weight");
+  if (!down) return fail(be, EK_EXPERT_WEIGHT_NOT_FOUND, "w2/down_w");
+  const ek_tensor_view_t* gate = find_suffix(t, n, "w3.weight", "gate_proj.weight");
+  if (!gate) return fail(be, EK_EXPERT_WEIGHT_NOT_FOUND, "w3/gate_w");
+  const ek_tensor_view_t* w[3] = {gate, up, down};
+  const int I_e = shared ? c.intermediate * c.n_shared_experts : c.intermediate;
+  const int64_t want[3][2] = {{I_e, c.hidden}, {I_e, c.hidden}, {c.hidden, I_e}};
+  const ek_tensor_view_t* sc[3] = {nullptr, nullptr, nullptr};
+  for (int i = 0; i < 3; ++i) {
+    if (w[i]->ndim != 2 || w[i]->shape[0] != want[i][0] || w[i]->shape[1] != want[i][1])
+      return fail(be, EK_INVALID_INPUT, "%s has shape [%lld,%lld], expected [%lld,%lld]", w[i]->name,
+                  (long long)w[i]->shape[0], (long long)(w[i]->ndim > 1 ? w[i]->shape[1] : 0),
+                  (long long)want[i][0], (long long)want[i][1]);
+    if (!w[i]->data) return fail(be, EK_INVALID_INPUT, "%s has no data", w[i]->name);
+    if (c.quant == EK_QUANT_BF16) {
+      if (w[i]->dtype != EK_BF16 && w[i]->dtype != EK_F16)
+        return fail(be, EK_INVALID_INPUT, "%s: dtype %d not accepted by a bf16 backend", w[i]->name, w[i]->dtype);
+    } else {
+      const int wantdt = c.quant == EK_QUANT_FP8_BLOCK128 ? EK_F8_E4M3 : EK_I8;
+      if (w[i]->dtype != wantdt)
+        return fail(be, EK_INVALID_INPUT, "%s: dtype %d does not match the backend's quantisation", w[i]->name, w[i]->dtype);
+      sc[i] = find_exact(t, n, std::string(w[i]->name) + "_scale_inv");
+      if (!sc[i]) sc[i] = find_exact(t, n, std::string(w[i]->name) + "_scale");
+      if (!sc[i]) return fail(be, EK_EXPERT_WEIGHT_NOT_FOUND, "%s_scale_inv", w[i]->name);
+      const int64_t sr = (want[i][0] + 127) / 128, scn = (want[i][1] + 127) / 128;
+      if (sc[i]->dtype != EK_F32 || sc[i]->ndim != 2 || sc[i]->shape[0] != sr || sc[i]->shape[1] != scn)
+        return fail(be, EK_INVALID_INPUT, "%s must be F32 [%lld,%lld]", sc[i]->name, (long long)sr, (long long)scn);
+      if (!sc[i]->data) return fail(be, EK_INVALID_INPUT, "%s has no data", sc[i]->name);
+    }
+  }
+
+  std::lock_guard<std::mutex> lg(be->load_mu);
+  Layer* L = nullptr;
+  {
+    std::unique_lock<std::shared_mutex> g(be->reg_mu);
+    int rc = ensure_layer(be, layer, &L);
+    if (rc != EK_OK) return rc;
+  }
+  cudaStream_t ls = be->load_stream;
+  // the slot may still be read by forwards queued before an eviction
+  CK(cudaEventRecord(be->fwd_done, be->stream));
+  CK(cudaStreamWaitEvent(ls, be->fwd_done, 0));
+
+  const int esz = elem_bytes(c.quant);
+  const void* src[3];
+  for (int i = 0; i < 3; ++i) {
+    const size_t elems = (size_t)want[i][0] * want[i][1];
+    const size_t in_bytes = elems * (w[i]->dtype == EK_F16 ? 2 : esz);
+    const void* p = w[i]->data;
+    if (!is_device_ptr(p)) {
+      int rc = grow(be, &be->stage[i], &be->stage_cap[i], in_bytes);
+      if (rc != EK_OK) return rc;
+      CK(cudaMemcpyAsync(be->stage[i], p, in_bytes, cudaMemcpyHostToDevice, ls));
+      p = be->stage[i];
+    }
+    if (w[i]->dtype == EK_F16) {
+      // one staging buffer for converted copies: serialise by syncing between matrices
+      int rc = grow(be, &be->stage_cvt, &be->stage_cvt_cap, elems * 2 * 3);
+      if (rc != EK_OK) return rc;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(be->stage_cvt) + (size_t)i * elems;
+      be->launches += launch_f16_to_bf16(p, dst, (int64_t)elems, ls);
+      p = dst;
+    }
+    src[i] = p;
+  }
+  const float* ssrc[3] = {nullptr, nullptr, nullptr};
+  if (c.quant != EK_QUANT_BF16) {
+    for (int i = 0; i < 3; ++i) {
+      const size_t bytes = (size_t)sc[i]->shape[0] * sc[i]->shape[1] * 4;
+      const void* p = sc[i]->data;
+      if (!is_device_ptr(p)) {
+        int rc = grow(be, (void**)&be->stage_scale[i], &be->stage_scale_cap[i], bytes);
+        if (rc != EK_OK) return rc;
+        CK(cudaMemcpyAsync(be->stage_scale[i], p, bytes, cudaMemcpyHostToDevice, ls));
+        p = be->stage_scale[i];
+      }
+      ssrc[i] = reinterpret_cast<const float*>(p);
+    }
+  }
+
+  const int n_virtual = shared ? c.n_shared_experts : 1;
+  for (int v = 0; v < n_virtual; ++v) {
+    const int slot = shared ? be->n_local + v : expert - be->e_lo;
+    uint8_t* gu0 = L->gu + (size_t)slot * d.it * d.kt_gu * 2 * kTileBytes;
+    uint8_t* dn0 = L->dn + (size_t)slot * d.ht * d.kt_dn * kTileBytes;
+    for (int m = 0; m < 2; ++m) {   // 0 gate, 1 up
+      RetileParams rp;
+      rp.src = src[m]; rp.rows = I_e; rp.cols = c.hidden;
+      rp.row0 = v * c.intermediate; rp.n_rows = c.intermediate;
+      rp.col0 = 0; rp.n_cols = c.hidden;
+      rp.esz = esz;
+      rp.dst = gu0 + (size_t)m * kTileBytes;
+      rp.rt_stride = (int64_t)d.kt_gu * 2 * kTileBytes;
+      rp.kt_stride = 2 * kTileBytes;
+      rp.n_rt = d.it; rp.n_kt = d.kt_gu;
+      be->launches += launch_retile(rp, ls);
+      if (c.quant != EK_QUANT_BF16) {
+        ScaleRetileParams sp;
+        sp.src = ssrc[m]; sp.src_cols = (int)sc[m]->shape[1]; sp.src_rows = (int)sc[m]->shape[0];
+        sp.rb0 = v * c.intermediate / 128; sp.kb0 = 0;
+        sp.n_rt = d.it; sp.n_kt = d.kt_gu;
+        sp.dst = L->gu_scale + (size_t)slot * d.it * d.kt_gu * 2;
+        sp.stride = 2; sp.lane = m;
+        be->launches += launch_scale_retile(sp, ls);
+      }
+    }
+    RetileParams rp;
+    rp.src = src[2]; rp.rows = c.hidden; rp.cols = I_e;
+    rp.row0 = 0; rp.n_rows = c.hidden;
+    rp.col0 = v * c.intermediate; rp.n_cols = c.intermediate;
+    rp.esz = esz;
+    rp.dst = dn0;
+    rp.rt_stride = (int64_t)d.kt_dn * kTileBytes;
+    rp.kt_stride = kTileBytes;
+    rp.n_rt = d.ht; rp.n_kt = d.kt_dn;
+    be->launches += launch_retile(rp, ls);
+    if (c.quant != EK_QUANT_BF16) {
+      ScaleRetileParams sp;
+      sp.src = ssrc[2]; sp.src_cols = (int)sc[2]->shape[1]; sp.src_rows = (int)sc[2]->shape[0];
+      sp.rb0 = 0; sp.kb0 = v * c.intermediate / 128;
+      sp.n_rt = d.ht; sp.n_kt = d.kt_dn;
+      sp.dst = L->dn_scale + (size_t)slot * d.ht * d.kt_dn;
+      sp.stride = 1; sp.lane = 0;
+      be->launches += launch_scale_retile(sp, ls);
+    }
+    const int32_t one = 1;
+    CK(cudaMemcpyAsync(L->registered + slot, &one, sizeof one, cudaMemcpyHostToDevice, ls));
+  }
+  CK(cudaStreamSynchronize(ls));
+  CK(cudaGetLastError());
+  {
+    std::unique_lock<std::shared_mutex> g(be->reg_mu);
+    for (int v = 0; v < n_virtual; ++v) L->host_registered[shared ? be->n_local + v : expert - be->e_lo] = 1;
+    be->loading.erase(id);
+    ExpertRef ref{layer, shared ? be->n_local : expert - be->e_lo};
+    be->experts[id] = ref;
+  }
+  return EK_OK;
+}
+
+int32_t ek_expert_register_safetensors(ek_backend_t* be, const char* id, const void* blob, size_t len) {
+  if (!be || !id || !blob) return EK_INVALID_INPUT;
+  std::vector<ekst::Entry> ent;
+  std::string err;
+  if (!ekst::parse_blob(blob, len, ent, err)) return fail(be, EK_SAFETENSOR, "%s", err.c_str());
+  // bundle order = order of data offsets (what SafeTensors::names()/tensors() iterate)
+  std::sort(ent.begin(), ent.end(), [](const ekst::Entry& a, const ekst::Entry& b) { return a.begin < b.begin; });
+  std::vector<ek_tensor_view_t> views(ent.size());
+  for (size_t i = 0; i < ent.size(); ++i) {
+    views[i].name = ent[i].name.c_str();
+    views[i].dtype = ekst::dtype_from_string(ent[i].dtype);
+    views[i].ndim = (int)std::min<size_t>(ent[i].shape.size(), 4);
+    for (int j = 0; j < 4; ++j) views[i].shape[j] = j < (int)ent[i].shape.size() ? ent[i].shape[j] : 1;
+    views[i].data = ent[i].data;
+  }
+  return ek_expert_register(be, id, views.data(), (int)views.size());
+}
+
+int32_t ek_router_register(ek_backend_t* be, int32_t layer, const void* weight, int32_t dt, const float* bias) {
+  if (!be || !weight) return EK_INVALID_INPUT;
+  if (dt != EK_BF16 && dt != EK_F32) return fail(be, EK_INVALID_INPUT, "router weight must be BF16 or F32");
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> lg(be->load_mu);
+  std::unique_lock<std::shared_mutex> g(be->reg_mu);
+  Layer* L = nullptr;
+  int rc = ensure_layer(be, layer, &L);
+  if (rc != EK_OK) return rc;
+  CK(cudaStreamSynchronize(be->stream));
+  const size_t bytes = (size_t)be->cfg.n_experts * be->cfg.hidden * (dt == EK_F32 ? 4 : 2);
+  if (L->router_w) cudaFree(L->router_w);
+  L->router_w = nullptr;
+  CK(cudaMalloc(&L->router_w, bytes));
+  CK(cudaMemcpy(L->router_w, weight, bytes, cudaMemcpyDefault));
+  L->router_f32 = dt == EK_F32;
+  if (L->router_bias) { cudaFree(L->router_bias); L->router_bias = nullptr; }
+  if (bias) {
+    CK(cudaMalloc(&L->router_bias, sizeof(float) * be->cfg.n_experts));
+    CK(cudaMemcpy(L->router_bias, bias, sizeof(float) * be->cfg.n_experts, cudaMemcpyDefault));
+  }
+  return EK_OK;
+}
+
+// ---- forward ---------------------------------------------------------------------------------
+
+int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x, int32_t n, void* y) {
+  if (!be || !id || !x || !y) return EK_INVALID_INPUT;
+  if (n < 1) return fail(be, EK_INVALID_INPUT, "empty batch");   // core.rs:55 asserts non-empty
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto it = be->experts.find(id);
+  if (it == be->experts.end()) return fail(be, EK_EXPERT_NOT_FOUND, "%s", id);
+  const ek_config_t& c = be->cfg;
+  std::string model; int layer, expert; bool shared;
+  parse_id(id, model, layer, expert, shared);
+  const int n_virtual = shared ? c.n_shared_experts : 1;
+  if ((int64_t)n * n_virtual > be->rows_cap - 128) return fail(be, EK_INVALID_INPUT, "batch of %d rows exceeds the workspace", n);
+  Layer& L = be->layers[it->second.layer];
+  const size_t H = c.hidden;
+  cudaStream_t s = be->stream;
+  // rows [0,n) of the permuted buffer are the request
+  CK(cudaMemcpyAsync(be->xp, x, (size_t)n * H * 2, cudaMemcpyDefault, s));
+  const int nmax = n <= 32 ? 32 : n <= 64 ? 64 : 128;
+  const int chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
+  const int per = (n + chunk_rows - 1) / chunk_rows;
+  if (per * n_virtual > 1024) return fail(be, EK_INVALID_INPUT, "batch too large for a single-expert call");
+  for (int v = 0; v < n_virtual; ++v)
+    for (int cidx = 0; cidx < per; ++cidx) {
+      ChunkDesc cd;
+      cd.slot = it->second.slot + v;
+      cd.in_row = cidx * chunk_rows;
+      cd.out_row = v * n + cidx * chunk_rows;
+      cd.n_rows = std::min(chunk_rows, n - cidx * chunk_rows);
+      be->h_chunks[v * per + cidx] = cd;
+    }
+  const int32_t total = per * n_virtual;
+  CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * total, cudaMemcpyHostToDevice, s));
+  be->h_status->aux1 = total;   // reuse pinned word as the source of the count
+  CK(cudaMemcpyAsync(be->n_chunks, &be->h_status->aux1, 4, cudaMemcpyHostToDevice, s));
+  run_ffn(be, L, nmax, 0);
+  run_ffn(be, L, nmax, 1);
+  __nv_bfloat16* res = be->obuf;
+  if (n_virtual > 1) {
+    // sum the virtual shared experts' partial outputs with the combine kernel (weights unused)
+    CombineParams cp;
+    cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
+    cp.T = n; cp.k = 0; cp.H = c.hidden; cp.n_shared = n_virtual; cp.Tk = 0; cp.bf16_products = 0;
+    be->launches += launch_combine(cp, s);
+    res = be->y_dev;
+  }
+  CK(cudaMemcpyAsync(y, res, (size_t)n * H * 2, cudaMemcpyDefault, s));
+  int rc = check_status(be);
+  if (rc != EK_OK) return rc;
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+static int stage_in(ek_backend* be, const void* x, size_t bytes, const __nv_bfloat16** dev) {
+  if (is_device_ptr(x)) {
+    *dev = reinterpret_cast<const __nv_bfloat16*>(x);
+    return EK_OK;
+  }
+  // pageable host memory -> pinned staging -> device, all inside the call
+  memcpy(be->h_x, x, bytes);
+  CK(cudaMemcpyAsync(be->x_dev, be->h_x, bytes, cudaMemcpyHostToDevice, be->stream));
+  *dev = be->x_dev;
+  return EK_OK;
+}
+
+int32_t ek_moe_forward_fused(ek_backend_t* be, int32_t layer, const void* x, int32_t T, void* y,
+                             const ek_route_debug_t* dbg) {
+  if (!be || !x || !y) return EK_INVALID_INPUT;
+  if (T < 1 || T > be->cfg.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, be->cfg.max_tokens);
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end() || !li->second.router_w)
+    return fail(be, EK_NOT_FOUND, "layer %d has no router weight registered", layer);
+  const ek_config_t& c = be->cfg;
+  const size_t bytes = (size_t)T * c.hidden * 2;
+  const __nv_bfloat16* xd;
+  int rc = stage_in(be, x, bytes, &xd);
+  if (rc != EK_OK) return rc;
+  const bool y_dev = is_device_ptr(y);
+  __nv_bfloat16* yd = y_dev ? reinterpret_cast<__nv_bfloat16*>(y) : be->y_dev;
+  rc = run_layer(be, li->second, xd, T, c.top_k, nullptr, yd, nullptr);
+  if (rc != EK_OK) return rc;
+  cudaStream_t s = be->stream;
+  if (!y_dev) CK(cudaMemcpyAsync(be->h_y, be->y_dev, bytes, cudaMemcpyDeviceToHost, s));
+  if (dbg) {
+    const size_t E = c.n_experts, K = c.top_k;
+    if (dbg->logits) CK(cudaMemcpyAsync(dbg->logits, be->logits, T * E * 4, cudaMemcpyDefault, s));
+    if (dbg->ids) CK(cudaMemcpyAsync(dbg->ids, be->ids, T * K * 4, cudaMemcpyDefault, s));
+    if (dbg->weights) CK(cudaMemcpyAsync(dbg->weights, be->weights, T * K * 4, cudaMemcpyDefault, s));
+    if (dbg->counts) CK(cudaMemcpyAsync(dbg->counts, be->counts, E * 4, cudaMemcpyDefault, s));
+    if (dbg->offsets) CK(cudaMemcpyAsync(dbg->offsets, be->offsets, (E + 1) * 4, cudaMemcpyDefault, s));
+    if (dbg->perm) CK(cudaMemcpyAsync(dbg->perm, be->perm, T * K * 4, cudaMemcpyDefault, s));
+  }
+  rc = check_status(be);
+  if (rc != EK_OK) return rc;
+  if (!y_dev) memcpy(y, be->h_y, bytes);
+  return finish_timing(be);
+}
+
+int32_t ek_moe_forward_fused_async(ek_backend_t* be, int32_t layer, const void* x, int32_t T, void* y) {
+  if (!be || !x || !y) return EK_INVALID_INPUT;
+  if (T < 1 || T > be->cfg.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, be->cfg.max_tokens);
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end() || !li->second.router_w)
+    return fail(be, EK_NOT_FOUND, "layer %d has no router weight registered", layer);
+  return run_layer(be, li->second, reinterpret_cast<const __nv_bfloat16*>(x), T, be->cfg.top_k, nullptr,
+                   reinterpret_cast<__nv_bfloat16*>(y), nullptr);
+}
+
+int32_t ek_sync(ek_backend_t* be) {
+  if (!be) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  int rc = check_status(be);
+  if (rc != EK_OK) return rc;
+  return finish_timing(be);
+}
+
+int32_t ek_set_stream(ek_backend_t* be, void* stream) {
+  if (!be) return EK_INVALID_INPUT;
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  cudaStreamSynchronize(be->stream);
+  be->stream = stream ? reinterpret_cast<cudaStream_t>(stream) : be->own_stream;
+  return EK_OK;
+}
+
+int32_t ek_moe_forward(ek_backend_t* be, int32_t layer, const void* x, int32_t T, const int32_t* ids, int32_t k,
+                       void* out) {
+  if (!be || !x || !ids || !out) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (T < 1 || T > c.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, c.max_tokens);
+  if (k < 1 || k > c.top_k) return fail(be, EK_INVALID_INPUT, "k=%d outside [1,%d]", k, c.top_k);
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end()) return fail(be, EK_EXPERT_NOT_FOUND, "layer %d holds no experts", layer);
+  const size_t bytes = (size_t)T * c.hidden * 2, obytes = bytes * k;
+  const __nv_bfloat16* xd;
+  int rc = stage_in(be, x, bytes, &xd);
+  if (rc != EK_OK) return rc;
+  cudaStream_t s = be->stream;
+  CK(cudaMemcpyAsync(be->ids, ids, (size_t)T * k * 4, cudaMemcpyDefault, s));
+  const bool out_dev = is_device_ptr(out);
+  __nv_bfloat16* od = reinterpret_cast<__nv_bfloat16*>(out);
+  if (!out_dev) {
+    if (be->tk_cap < obytes) {
+      cudaStreamSynchronize(s);
+      rc = grow(be, (void**)&be->tk_dev, &be->tk_cap, obytes);
+      if (rc != EK_OK) return rc;
+    }
+    if (be->h_tk_cap < obytes) {
+      if (be->h_tk) cudaFreeHost(be->h_tk);
+      be->h_tk = nullptr; be->h_tk_cap = 0;
+      CK(cudaMallocHost(&be->h_tk, obytes));
+      be->h_tk_cap = obytes;
+    }
+    od = be->tk_dev;
+  }
+  rc = run_layer(be, li->second, xd, T, k, be->ids, nullptr, od);
+  if (rc != EK_OK) return rc;
+  if (!out_dev) CK(cudaMemcpyAsync(be->h_tk, od, obytes, cudaMemcpyDeviceToHost, s));
+  rc = check_status(be);
+  if (rc != EK_OK) return rc;
+  if (!out_dev) memcpy(out, be->h_tk, obytes);
+  return finish_timing(be);
+}
+
+int32_t ek_route_from_logits(ek_backend_t* be, const float* logits, int32_t T, const float* bias, int32_t* ids,
+                             float* weights, int32_t* counts, int32_t* offsets, int32_t* perm) {
+  if (!be || !logits) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (T < 1 || T > c.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, c.max_tokens);
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  cudaStream_t s = be->stream;
+  const size_t E = c.n_experts, K = c.top_k;
+  CK(cudaMemcpyAsync(be->logits, logits, T * E * 4, cudaMemcpyDefault, s));
+  float* bias_dev = nullptr;
+  if (bias) {
+    bias_dev = be->bias_scratch;
+    CK(cudaMemcpyAsync(bias_dev, bias, E * 4, cudaMemcpyDefault, s));
+  }
+  RouteParams rp;
+  rp.x = nullptr; rp.wg = nullptr; rp.wg_f32 = 0; rp.bias = bias_dev;
+  rp.logits = be->logits; rp.ids = be->ids; rp.weights = be->weights; rp.counts = be->counts;
+  rp.T = T; rp.H = c.hidden; rp.E = c.n_experts; rp.k = c.top_k;
+  rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
+  rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling; rp.bf16_weights = c.bf16_combine;
+  be->launches += launch_route_select(rp, s);
+  PermuteParams pp;
+  pp.ids = be->ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
+  pp.T = T; pp.k = c.top_k; pp.E = c.n_experts; pp.e_lo = 0; pp.e_hi = c.n_experts;
+  be->launches += launch_permute(pp, s);
+  if (ids) CK(cudaMemcpyAsync(ids, be->ids, T * K * 4, cudaMemcpyDefault, s));
+  if (weights) CK(cudaMemcpyAsync(weights, be->weights, T * K * 4, cudaMemcpyDefault, s));
+  if (counts) CK(cudaMemcpyAsync(counts, be->counts, E * 4, cudaMemcpyDefault, s));
+  if (offsets) CK(cudaMemcpyAsync(offsets, be->offsets, (E + 1) * 4, cudaMemcpyDefault, s));
+  if (perm) CK(cudaMemcpyAsync(perm, be->perm, T * K * 4, cudaMemcpyDefault, s));
+  CK(cudaStreamSynchronize(s));
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_combine(ek_backend_t* be, const void* out, const float* weights, int32_t T, int32_t k,
+                   const void* shared, void* y) {
+  if (!be || !out || !weights || !y) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (T < 1 || T > c.max_tokens || k < 1 || k > c.top_k) return fail(be, EK_INVALID_INPUT, "T or k out of range");
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  cudaStream_t s = be->stream;
+  const size_t H = c.hidden;
+  // rows [0,T*k) of the output buffer in (token,slot) order, shared rows behind them
+  CK(cudaMemcpyAsync(be->obuf, out, (size_t)T * k * H * 2, cudaMemcpyDefault, s));
+  if (shared) CK(cudaMemcpyAsync(be->obuf + (size_t)T * k * H, shared, (size_t)T * H * 2, cudaMemcpyDefault, s));
+  CK(cudaMemcpyAsync(be->weights, weights, (size_t)T * k * 4, cudaMemcpyDefault, s));
+  std::vector<int32_t> ident((size_t)T * k);
+  for (size_t i = 0; i < ident.size(); ++i) ident[i] = (int32_t)i;
+  CK(cudaMemcpyAsync(be->inv, ident.data(), ident.size() * 4, cudaMemcpyHostToDevice, s));
+  CK(cudaStreamSynchronize(s));
+  CombineParams cp;
+  cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
+  cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = shared ? 1 : 0; cp.Tk = T * k;
+  cp.bf16_products = c.bf16_combine;
+  be->launches += launch_combine(cp, s);
+  CK(cudaMemcpyAsync(y, be->y_dev, (size_t)T * H * 2, cudaMemcpyDefault, s));
+  CK(cudaStreamSynchronize(s));
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_w8a16_activate(ek_backend_t* be, const void* w, int32_t w_dtype, const float* scale, int32_t rows,
+                          int32_t cols, void* out) {
+  if (!be || !w || !scale || !out) return EK_INVALID_INPUT;
+  if (w_dtype != EK_F8_E4M3 && w_dtype != EK_I8) return fail(be, EK_INVALID_INPUT, "payload must be F8_E4M3 or I8");
+  // the reference reshapes into whole 128x128 blocks (expert_torch.rs:28-46)
+  if (rows < 128 || cols < 128 || rows % 128 || cols % 128)
+    return fail(be, EK_INVALID_INPUT, "rows and cols must be multiples of 128");
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> lg(be->load_mu);
+  cudaStream_t s = be->load_stream;
+  const size_t n = (size_t)rows * cols, sn = (size_t)(rows / 128) * (cols / 128) * 4;
+  int rc = grow(be, &be->stage[0], &be->stage_cap[0], n);
+  if (rc != EK_OK) return rc;
+  rc = grow(be, (void**)&be->stage_scale[0], &be->stage_scale_cap[0], sn);
+  if (rc != EK_OK) return rc;
+  rc = grow(be, &be->stage_cvt, &be->stage_cvt_cap, n * 2);
+  if (rc != EK_OK) return rc;
+  CK(cudaMemcpyAsync(be->stage[0], w, n, cudaMemcpyDefault, s));
+  CK(cudaMemcpyAsync(be->stage_scale[0], scale, sn, cudaMemcpyDefault, s));
+  be->launches += launch_dequant(be->stage[0], w_dtype, be->stage_scale[0], rows, cols,
+                                 reinterpret_cast<__nv_bfloat16*>(be->stage_cvt), s);
+  CK(cudaMemcpyAsync(out, be->stage_cvt, n * 2, cudaMemcpyDefault, s));
+  CK(cudaStreamSynchronize(s));
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_worker_forward_wire(ek_backend_t* be, const char* expert_id, const void* req, size_t req_len, void* resp,
+                               size_t resp_cap, size_t* resp_len) {
+  if (!be || !expert_id || !req || !resp_len) return EK_INVALID_INPUT;
+  std::vector<ekst::Entry> ent;
+  std::string err;
+  if (!ekst::parse_blob(req, req_len, ent, err)) return fail(be, EK_SAFETENSOR, "%s", err.c_str());
+  const ekst::Entry* data = nullptr;
+  for (auto& e : ent)
+    if (e.name == "data") data = &e;
+  if (!data) return fail(be, EK_SAFETENSOR, "tensor name not found: data");   // EKError::SafeTensorNotFound
+  if (data->dtype != "BF16") return fail(be, EK_INVALID_INPUT, "request tensor must be BF16, got %s", data->dtype.c_str());
+  if (data->shape.size() != 2) return fail(be, EK_INVALID_INPUT, "request tensor must be 2-D");   // ffn/mod.rs:45
+  if (data->shape[1] != be->cfg.hidden) return fail(be, EK_INVALID_INPUT, "request hidden size %lld != %d", (long long)data->shape[1], be->cfg.hidden);
+  const int64_t n = data->shape[0];
+  if (n < 1 || n > be->cfg.max_tokens) return fail(be, EK_INVALID_INPUT, "request rows %lld outside [1,%d]", (long long)n, be->cfg.max_tokens);
+  const std::string hdr = ekst::single_header(n, be->cfg.hidden);
+  const size_t payload = (size_t)n * be->cfg.hidden * 2;
+  const size_t need = 8 + hdr.size() + payload;
+  *resp_len = need;
+  if (!resp || resp_cap < need) return fail(be, EK_INVALID_INPUT, "response buffer too small: need %zu bytes", need);
+  uint8_t* o = reinterpret_cast<uint8_t*>(resp);
+  const uint64_t hl = hdr.size();
+  memcpy(o, &hl, 8);
+  memcpy(o + 8, hdr.data(), hdr.size());
+  // the payload may be unaligned inside the blob; cudaMemcpy from pageable memory does not care
+  return ek_expert_forward(be, expert_id, data->data, (int32_t)n, o + 8 + hdr.size());
+}
+
+// ---- observability -----------------------------------------------------------------------------
+
+int32_t ek_expert_counts(ek_backend_t* be, int32_t layer, int32_t* counts) {
+  if (!be || !counts) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end() || !li->second.have_counts) return fail(be, EK_NOT_FOUND, "no forward has run on layer %d", layer);
+  CK(cudaMemcpyAsync(counts, li->second.last_counts, sizeof(int32_t) * be->cfg.n_experts, cudaMemcpyDefault, be->stream));
+  CK(cudaStreamSynchronize(be->stream));
+  return EK_OK;
+}
+
+int32_t ek_stage_timing_enable(ek_backend_t* be, int32_t on) {
+  if (!be) return EK_INVALID_INPUT;
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  be->timing = on != 0;
+  return EK_OK;
+}
+int32_t ek_stage_times(ek_backend_t* be, float* ms) {
+  if (!be || !ms) return EK_INVALID_INPUT;
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  for (int i = 0; i < EK_STAGE_COUNT; ++i) ms[i] = be->stage_ms[i];
+  return EK_OK;
+}
+int64_t ek_kernel_launches(const ek_backend_t* be) { return be ? be->launches.load() : 0; }
+
+int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl) {
+  if (!be || impl < 0 || impl > 1) return EK_INVALID_INPUT;
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  be->ffn_impl = impl;
+  return EK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+// Weighted unpermute-combine and the plain unpermute.
+//
+// combine: y[t] = sum_k w[t,k] * out[t,k] (+ shared(x)[t]) -- the frontend's step after the
+// expert outputs return (expertkit_torch/models/deepseek_v3/model.py:96-104,152;
+// expertkit_torch/models/qwen3_moe.py:102-104).
+// unpermute: out[t,s,:] = row of (t,s) -- NaiveExecutor's scatter + two-level stack
+// (ek-computation/src/controller/executor.rs:203-251).
+#include "ek_internal.h"
+
+namespace ek {
+
+namespace {
+
+constexpr int kMaxK = 32;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+__device__ __forceinline__ float round_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// One CTA per token, 128-bit loads of the k expert rows, fp32 accumulation in slot order.
+__global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
+  __shared__ int s_row[kMaxK];
+  __shared__ float s_w[kMaxK];
+  const int t = blockIdx.x;
+  if (threadIdx.x < p.k) {
+    s_row[threadIdx.x] = p.inv[(size_t)t * p.k + threadIdx.x];
+    s_w[threadIdx.x] = p.weights[(size_t)t * p.k + threadIdx.x];
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < p.H / 8; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.k; ++s) {
+      const int row = s_row[s];
+      if (row < 0) continue;
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.obuf + (size_t)row * p.H + v * 8), f);
+      const float w = s_w[s];
+      if (p.bf16_products) {
+        // routing weights were rounded to bf16 upstream; products are bf16 tensors
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], round_bf16(__fmul_rn(w, f[j])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(w, f[j]));
+      }
+    }
+    if (p.n_shared > 0) {
+      // the routed sum is a bf16 tensor before the shared expert's bf16 output is added
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = round_bf16(acc[j]);
+      float sh[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sh[j] = 0.f;
+      for (int q = 0; q < p.n_shared; ++q) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(
+                    p.obuf + ((size_t)p.Tk + (size_t)q * p.T + t) * p.H + v * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sh[j] += f[j];
+      }
+      if (p.n_shared > 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sh[j] = round_bf16(sh[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += sh[j];
+    }
+    *reinterpret_cast<uint4*>(p.y + (size_t)t * p.H + v * 8) = pack8(acc);
+  }
+}
+
+__global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __restrict__ obuf,
+                                                        const int32_t* __restrict__ inv,
+                                                        __nv_bfloat16* __restrict__ out, int32_t H) {
+  const int i = blockIdx.x;  // token*k + slot
+  const int row = inv[i];
+  uint4* d = reinterpret_cast<uint4*>(out + (size_t)i * H);
+  if (row < 0) {
+    for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(obuf + (size_t)row * H);
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
+}
+
+}  // namespace
+
+int launch_combine(const CombineParams& p, cudaStream_t s) {
+  if (p.T > 0) combine_kernel<<<p.T, 256, 0, s>>>(p);
+  return p.T > 0 ? 1 : 0;
+}
+
+int launch_unpermute(const __nv_bfloat16* obuf, const int32_t* inv, __nv_bfloat16* out, int32_t T,
+                     int32_t k, int32_t H, cudaStream_t s) {
+  if (T * k > 0) unpermute_kernel<<<T * k, 128, 0, s>>>(obuf, inv, out, H);
+  return T * k > 0 ? 1 : 0;
+}
+
+}  // namespace ek

@@ -1,0 +1,184 @@
+// Internal declarations shared by the host side (backend.cu) and the kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/ek_b200.h"
+
+namespace ek {
+
+// ---- weight tile geometry ----------------------------------------------------------------
+// Expert weights live in HBM as 16 KiB tiles of 128 weight rows x 128 bytes of K
+// (128 fp8/int8 elements or 64 bf16 elements).  Inside a tile the 16-byte chunk j of row r
+// sits at byte (j*128 + r)*16, so that thread r of a converter warpgroup reads its own row
+// with conflict-free 16-byte shared-memory loads after a plain bulk copy of the tile.
+// Tiles of one (expert, row tile) are contiguous along K in exactly the order the kernel's
+// K loop consumes them (gate and up tiles of the same K step adjacent), so every CTA streams
+// one contiguous HBM range.
+constexpr int kTileRows = 128;
+constexpr int kTileBytes = 16384;
+constexpr int kChunksPerRow = 8;  // 16-byte chunks per tile row
+
+__host__ __device__ inline int tile_k_elems(int quant) { return quant == EK_QUANT_BF16 ? 64 : 128; }
+__host__ __device__ inline int elem_bytes(int quant) { return quant == EK_QUANT_BF16 ? 2 : 1; }
+__host__ __device__ inline int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+// One contiguous run of rows that all go through the same expert slot.
+struct ChunkDesc {
+  int32_t slot;      // expert slot in the layer slab
+  int32_t in_row;    // first row in the permuted activation buffer (GEMM B operand)
+  int32_t out_row;   // first row in the output buffer
+  int32_t n_rows;    // valid rows (1..chunk size)
+};
+
+// Device-side error word: {code, where}.  Kernels only ever write non-zero values.
+struct DevStatus {
+  int32_t code;
+  int32_t where;
+  int32_t aux0;
+  int32_t aux1;
+};
+enum { DEV_OK = 0, DEV_TIMEOUT = 1, DEV_MISSING_EXPERT = 2, DEV_BOUNDS = 3 };
+
+// Layer slab (device pointers).
+struct LayerWeights {
+  const uint8_t* gu_tiles;   // [slot][it][kt][gate|up][16 KiB]
+  const uint8_t* dn_tiles;   // [slot][ht][kt][16 KiB]
+  const float* gu_scale;     // [slot][it][kt][2]   (quantised only; K tile == 128-wide scale block)
+  const float* dn_scale;     // [slot][ht][kt]
+  const int32_t* registered; // [slots] 1 when the slot holds weights
+  int32_t n_slots;
+};
+
+struct Dims {
+  int32_t H, I;          // logical sizes
+  int32_t Hp, Ip;        // padded to multiples of 128
+  int32_t quant;
+  int32_t kt_gu;         // K tiles of the gate/up GEMM  = Hp / tile_k
+  int32_t kt_dn;         // K tiles of the down GEMM     = Ip / tile_k
+  int32_t it;            // row tiles of gate/up         = Ip / 128
+  int32_t ht;            // row tiles of down            = Hp / 128
+};
+
+// ---- kernel launchers (each returns the number of kernels it launched) ---------------------
+struct RouteParams {
+  const __nv_bfloat16* x;      // [T,H]
+  const void* wg;              // [E,H] bf16 or f32
+  int32_t wg_f32;
+  const float* bias;           // [E] or null
+  float* logits;               // [T,E]
+  int32_t* ids;                // [T,k]
+  float* weights;              // [T,k]
+  int32_t* counts;             // [E] (zeroed by the launcher)
+  int32_t T, H, E, k;
+  int32_t scoring, n_group, topk_group, norm;
+  float scaling;
+  int32_t bf16_weights;        // round routing weights to bf16 (Qwen3 combine)
+};
+int launch_router_logits(const RouteParams& p, cudaStream_t s);
+int launch_route_select(const RouteParams& p, cudaStream_t s);
+int launch_histogram(const int32_t* ids, int32_t n, int32_t E, int32_t* counts, DevStatus* st,
+                     cudaStream_t s);
+
+struct PermuteParams {
+  const int32_t* ids;     // [T*k]
+  const int32_t* counts;  // [E]
+  int32_t* offsets;       // [E+1]
+  int32_t* perm;          // [T*k]
+  int32_t* inv;           // [T*k]
+  int32_t T, k, E;
+  // expert-parallel window: experts [e_lo, e_hi) are local; rows of other experts are left out
+  int32_t e_lo, e_hi;
+};
+int launch_permute(const PermuteParams& p, cudaStream_t s);
+
+struct WorklistParams {
+  const int32_t* counts;     // [E]
+  const int32_t* offsets;    // [E+1]
+  const int32_t* registered; // [slots]
+  ChunkDesc* chunks;         // out
+  int32_t* n_chunks;         // out (single int)
+  int32_t E, e_lo, e_hi;     // local expert window; slot = e - e_lo
+  int32_t chunk_rows;        // rows per chunk
+  int32_t n_shared, T;       // shared virtual experts: slot = (e_hi-e_lo)+j, in_row = Tk, out_row = Tk+j*T
+  int32_t Tk;
+  int32_t max_chunks;
+  DevStatus* status;
+};
+int launch_worklist(const WorklistParams& p, cudaStream_t s);
+
+// rows [0,Tk): xp[r] = x[perm[r]/k]; rows [Tk, Tk+T) = x (only when with_shared)
+// `n_routed` (device) = number of permuted rows that exist on this rank (offsets[E]).
+int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_routed,
+                  __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t with_shared,
+                  cudaStream_t s);
+
+struct FfnParams {
+  Dims d;
+  LayerWeights w;
+  const ChunkDesc* chunks;
+  const int32_t* n_chunks;
+  const __nv_bfloat16* xp;   // [rows, H]
+  __nv_bfloat16* hbuf;       // [rows, Ip]
+  __nv_bfloat16* obuf;       // [rows, H]
+  int32_t rows_cap;
+  int32_t max_chunks;        // capacity of `chunks`
+  DevStatus* status;
+  int32_t chunk_rows;
+  // TMA descriptors (tcgen05 path): index 0..3 <-> box rows 16,32,64,128
+  const CUtensorMap* x_maps;   // device array[4]
+  const CUtensorMap* h_maps;   // device array[4]
+  int32_t n_sm;
+};
+// Straightforward CUDA-core evaluation of the same tiled weights; used by the tests as an
+// independent check of the tensor-core path at sizes the CPU oracle cannot reach.
+// `which`: 0 = gate/up + SwiGLU (xp -> hbuf), 1 = down projection (hbuf -> obuf).
+int launch_ffn_simt(const FfnParams& p, int which, cudaStream_t s);
+// tcgen05 / TMEM / TMA grouped GEMMs.
+int launch_ffn_tc(const FfnParams& p, int nmax, int which, cudaStream_t s);
+
+struct CombineParams {
+  const __nv_bfloat16* obuf;   // [rows, H]
+  const int32_t* inv;          // [T*k]  row of (token,slot); <0 = not local (skipped)
+  const float* weights;        // [T,k]
+  __nv_bfloat16* y;            // [T,H]
+  int32_t T, k, H;
+  int32_t n_shared, Tk;        // shared rows at Tk + j*T + t
+  int32_t bf16_products;
+};
+int launch_combine(const CombineParams& p, cudaStream_t s);
+// out[t,s,:] = obuf[inv[t*k+s]]
+int launch_unpermute(const __nv_bfloat16* obuf, const int32_t* inv, __nv_bfloat16* out, int32_t T,
+                     int32_t k, int32_t H, cudaStream_t s);
+
+// Registration-time layout kernels.
+struct RetileParams {
+  const void* src;        // [rows, cols] row-major, element size 1 or 2
+  int32_t rows, cols;     // logical matrix
+  int32_t row0, n_rows;   // source row window written as tiles (virtual shared experts)
+  int32_t col0, n_cols;   // source column window
+  int32_t esz;            // 1 or 2
+  uint8_t* dst;           // first tile of (row tile 0, k tile 0)
+  int64_t rt_stride;      // bytes between consecutive row tiles
+  int64_t kt_stride;      // bytes between consecutive K tiles
+  int32_t n_rt, n_kt;     // tiles to write (padding tiles are zero-filled)
+};
+int launch_retile(const RetileParams& p, cudaStream_t s);
+struct ScaleRetileParams {
+  const float* src;       // [ceil(rows/128), ceil(cols/128)]
+  int32_t src_cols;
+  int32_t rb0, kb0;       // window origin in blocks
+  int32_t n_rt, n_kt;
+  float* dst;             // dst[(rt*n_kt + kt)*stride + lane]
+  int32_t stride, lane;
+  int32_t src_rows;
+};
+int launch_scale_retile(const ScaleRetileParams& p, cudaStream_t s);
+int launch_fill_f32(float* dst, float v, int64_t n, cudaStream_t s);
+int launch_dequant(const void* w, int32_t w_dtype, const float* scale, int32_t rows, int32_t cols,
+                   __nv_bfloat16* out, cudaStream_t s);
+int launch_f16_to_bf16(const void* src, __nv_bfloat16* dst, int64_t n, cudaStream_t s);
+
+}  // namespace ek

@@ -1,0 +1,384 @@
+// Grouped SwiGLU expert FFN on the 5th-generation tensor cores (tcgen05 + tensor memory),
+// fed by TMA, for sm_100a.  Replaces the three libtorch matmuls of TorchFFN::forward
+// (ek-computation/src/ffn/expert_torch.rs:80-85) and the block dequantisation of
+// w8a16_activate (expert_torch.rs:24-53) for ALL experts of a layer in two launches.
+//
+// Formulation ("weights as the M operand"): for one work item (chunk of <= NMAX activation
+// rows of one expert, one tile of 128 weight rows)
+//        D[128 weight rows, N rows of x] (+)= W_tile[128, K] * X_chunk[N, K]^T
+// so the MMA always runs at M = 128 no matter how few tokens an expert received, and the
+// weight stream - the thing that is HBM-bound at decode batch sizes - is read exactly once.
+//
+//   producer warp   : bulk-copies the next 16 KiB weight tile(s) (fp8 / int8 / bf16, already
+//                     laid out for conflict-free reads) and TMA-loads the matching [N, K]
+//                     activation tile (128-byte swizzle) into a ring of shared-memory stages
+//   converter warps : thread r reads weight row r of the tile from shared memory, dequantises
+//                     it to bf16 (block scale applied in fp32, one rounding - the reference
+//                     formula) and stores it into tensor memory with tcgen05.st as the A operand
+//   MMA warp        : one thread issues tcgen05.mma (A from tensor memory, B from shared
+//                     memory through a swizzled descriptor, fp32 accumulators in tensor memory)
+//   epilogue        : the converter warps read the accumulators with tcgen05.ld; gate/up mode
+//                     applies silu(gate) * up in fp32 and writes h (bf16); down mode writes
+//                     the expert output rows (bf16)
+//
+// Every mbarrier wait is bounded (see ptx.cuh); on a timeout the CTA records DEV_TIMEOUT in
+// the status word, drains what it has in flight and leaves, so a protocol error can never
+// hang the device.
+#include "ek_internal.h"
+#include "ptx.cuh"
+
+namespace ek {
+
+namespace {
+
+using namespace ekptx;
+
+constexpr int kConvWarps = 8;
+constexpr int kThreads = (kConvWarps + 2) * 32;
+constexpr int kASlots = 4;       // A-operand staging slots in tensor memory
+constexpr int kASlotCols = 64;   // columns per slot (128 bf16 along K)
+constexpr int kABaseCol = 256;   // accumulators live in columns [0, 256)
+constexpr int kTmemCols = 512;
+constexpr int kSmemLimit = 232448 - 4096;
+
+template <int QUANT, bool GATEUP, int NMAX>
+struct Cfg {
+  static constexpr int TKE = QUANT == EK_QUANT_BF16 ? 64 : 128;   // K elements per tile
+  static constexpr int NT = GATEUP ? 2 : 1;                       // weight tiles per stage
+  static constexpr int W_BYTES = NT * kTileBytes;
+  static constexpr int X_BYTES = NMAX * TKE * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int STAGES_RAW = kSmemLimit / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int MMAS = TKE / 16;                           // MMA instructions per tile
+  static constexpr int NCH = GATEUP ? 8 : 4;                      // 16-byte chunks per thread
+  static constexpr int WPC = QUANT == EK_QUANT_BF16 ? 4 : 8;      // 32-bit A words per chunk
+  static constexpr int NW = NCH * WPC;
+  static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
+  static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
+};
+
+__device__ __forceinline__ void report(DevStatus* st, int code, int where, int a0, int a1) {
+  if (atomicCAS(&st->code, DEV_OK, code) == DEV_OK) {
+    st->where = where;
+    st->aux0 = a0;
+    st->aux1 = a1;
+  }
+}
+
+// ---- dequantisation of one 16-byte chunk into packed bf16 pairs ---------------------------
+// fp8 e4m3: the byte [s eeee mmm] placed as fp32 bits s<<31 | (eeeemmm)<<20 is the value
+// times 2^-120 exactly (subnormals included); multiplying by 2^120 restores it, then the fp32
+// block scale is applied and the product rounded to bf16 once: bf16_rne(float(w) * scale).
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void cvt_fp8_word(uint32_t w, float scale, uint32_t* out) {
+  const float k = 0x1p120f;
+  float f0 = __uint_as_float(((w << 24) & 0x80000000u) | ((w << 20) & 0x07F00000u));
+  float f1 = __uint_as_float(((w << 16) & 0x80000000u) | ((w << 12) & 0x07F00000u));
+  float f2 = __uint_as_float(((w << 8) & 0x80000000u) | ((w << 4) & 0x07F00000u));
+  float f3 = __uint_as_float((w & 0x80000000u) | ((w >> 4) & 0x07F00000u));
+  out[0] = pack_bf16(__fmul_rn(__fmul_rn(f0, k), scale), __fmul_rn(__fmul_rn(f1, k), scale));
+  out[1] = pack_bf16(__fmul_rn(__fmul_rn(f2, k), scale), __fmul_rn(__fmul_rn(f3, k), scale));
+}
+__device__ __forceinline__ void cvt_int8_word(uint32_t w, float scale, uint32_t* out) {
+  float f0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w & 0xff)));
+  float f1 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 8) & 0xff)));
+  float f2 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 16) & 0xff)));
+  float f3 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 24) & 0xff)));
+  out[0] = pack_bf16(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
+  out[1] = pack_bf16(__fmul_rn(f2, scale), __fmul_rn(f3, scale));
+}
+template <int QUANT>
+__device__ __forceinline__ void cvt_chunk(const uint4& raw, float scale, uint32_t* out) {
+  if (QUANT == EK_QUANT_BF16) {
+    out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
+  } else if (QUANT == EK_QUANT_FP8_BLOCK128) {
+    cvt_fp8_word(raw.x, scale, out + 0);
+    cvt_fp8_word(raw.y, scale, out + 2);
+    cvt_fp8_word(raw.z, scale, out + 4);
+    cvt_fp8_word(raw.w, scale, out + 6);
+  } else {
+    cvt_int8_word(raw.x, scale, out + 0);
+    cvt_int8_word(raw.y, scale, out + 2);
+    cvt_int8_word(raw.z, scale, out + 4);
+    cvt_int8_word(raw.w, scale, out + 6);
+  }
+}
+
+__device__ __forceinline__ int pick_n(int rows, int nmax) {
+  int n = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128;
+  return n > nmax ? nmax : n;
+}
+__device__ __forceinline__ int map_index(int n) { return n == 16 ? 0 : n == 32 ? 1 : n == 64 ? 2 : 3; }
+
+template <int QUANT, bool GATEUP, int NMAX>
+__global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
+  using C = Cfg<QUANT, GATEUP, NMAX>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_afull[kASlots], bar_aempty[kASlots];
+  __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile int* abortp = &s_abort;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < C::STAGES; ++i) {
+      mbar_init(smem_u32(&bar_full[i]), 1);
+      mbar_init(smem_u32(&bar_empty[i]), kConvWarps + 1);
+    }
+    for (int i = 0; i < kASlots; ++i) {
+      mbar_init(smem_u32(&bar_afull[i]), GATEUP ? 4 : 8);
+      mbar_init(smem_u32(&bar_aempty[i]), 1);
+    }
+    mbar_init(smem_u32(&bar_accfull), 1);
+    mbar_init(smem_u32(&bar_accempty), kConvWarps);
+    mbar_init(smem_u32(&bar_drain), 1);
+    mbar_init_fence();
+  }
+  if (warp == kConvWarps + 1) {
+    tmem_alloc(smem_u32(&s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  const int n_chunks = *p.n_chunks;
+  const int n_rt = GATEUP ? p.d.it : p.d.ht;
+  const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;
+  const int total = n_chunks * n_rt;
+
+  if (warp == kConvWarps) {
+    // =============================== producer ==============================================
+    if (lane == 0) {
+      const CUtensorMap* maps = GATEUP ? p.x_maps : p.h_maps;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        const ChunkDesc cd = p.chunks[item / n_rt];
+        const int rt = item % n_rt;
+        const int N = pick_n(cd.n_rows, NMAX);
+        const CUtensorMap* map = maps + map_index(N);
+        const uint8_t* wsrc =
+            GATEUP ? p.w.gu_tiles + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * C::W_BYTES
+                   : p.w.dn_tiles + ((size_t)cd.slot * p.d.ht + rt) * (size_t)p.d.kt_dn * C::W_BYTES;
+        const int brow = GATEUP ? cd.in_row : cd.out_row;
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp)) {
+            report(p.status, DEV_TIMEOUT, 100, item, kt);
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t dst = stage0 + s * C::STAGE_BYTES;
+          mbar_arrive_expect_tx(full, C::W_BYTES + N * C::TKE * 2);
+          bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
+#pragma unroll
+          for (int a = 0; a < C::TKE / 64; ++a)
+            tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
+        }
+      }
+      // never leave with copies in flight: wait (bounded) for every stage armed in the last lap
+      const uint32_t lo = it > (uint32_t)C::STAGES ? it - C::STAGES : 0;
+      for (uint32_t i = lo; i < it; ++i) {
+        const uint32_t bar = smem_u32(&bar_full[i % C::STAGES]);
+        for (uint32_t poll = 0; poll < (1u << 20); ++poll) {
+          if (mbar_try_wait(bar, (i / C::STAGES) & 1u)) break;
+          __nanosleep(64);
+        }
+      }
+    }
+  } else if (warp == kConvWarps + 1) {
+    // =============================== MMA issuer ============================================
+    if (lane == 0) {
+      uint32_t it = 0, items_done = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
+        const ChunkDesc cd = p.chunks[item / n_rt];
+        const int N = pick_n(cd.n_rows, NMAX);
+        const uint32_t idesc = umma_idesc_bf16(N);
+        if (!mbar_wait(smem_u32(&bar_accempty), (items_done & 1u) ^ 1u, abortp)) {
+          report(p.status, DEV_TIMEOUT, 200, item, 0);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kt = 0; kt < KT && ok; ++kt, ++it) {
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
+            report(p.status, DEV_TIMEOUT, 201, item, kt);
+            ok = false;
+            break;
+          }
+          const uint32_t xbase = stage0 + s * C::STAGE_BYTES + C::W_BYTES;
+#pragma unroll
+          for (int q = 0; q < C::NT; ++q) {
+            const uint32_t tcount = it * C::NT + q;
+            const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
+            if (!mbar_wait(smem_u32(&bar_afull[a]), aph, abortp)) {
+              report(p.status, DEV_TIMEOUT, 202, item, kt);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + q * NMAX;
+            const uint32_t a_tmem = tmem + kABaseCol + a * kASlotCols;
+#pragma unroll
+            for (int j = 0; j < C::MMAS; ++j) {
+              const uint64_t bdesc = umma_desc_sw128(xbase + (j / 4) * N * 128 + (j % 4) * 32);
+              umma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (kt > 0 || j > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&bar_aempty[a]));
+          }
+          if (!ok) break;
+          tc_commit(smem_u32(&bar_empty[s]));
+        }
+        if (ok) tc_commit(smem_u32(&bar_accfull));
+      }
+      // drain: every MMA issued by this thread has completed before tensor memory is freed
+      tc_commit(smem_u32(&bar_drain));
+      for (uint32_t poll = 0; poll < (1u << 20); ++poll) {
+        if (mbar_try_wait(smem_u32(&bar_drain), 0)) break;
+        __nanosleep(64);
+      }
+    }
+  } else {
+    // =============================== converters + epilogue =================================
+    const int wg = warp >> 2, q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+    uint32_t it = 0, items_done = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
+      const ChunkDesc cd = p.chunks[item / n_rt];
+      const int rt = item % n_rt;
+      const int N = pick_n(cd.n_rows, NMAX);
+      const float* sc = nullptr;
+      if (QUANT != EK_QUANT_BF16) {
+        sc = GATEUP ? p.w.gu_scale + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * 2 + wg
+                    : p.w.dn_scale + ((size_t)cd.slot * p.d.ht + rt) * (size_t)p.d.kt_dn;
+      }
+      float scale_next = 1.f;
+      if (QUANT != EK_QUANT_BF16) scale_next = __ldg(sc);
+      for (int kt = 0; kt < KT; ++kt, ++it) {
+        const float scale = scale_next;
+        if (QUANT != EK_QUANT_BF16 && kt + 1 < KT) scale_next = __ldg(sc + (size_t)(kt + 1) * (GATEUP ? 2 : 1));
+        const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
+          report(p.status, DEV_TIMEOUT, 300, item, kt);
+          ok = false;
+          break;
+        }
+        const uint32_t tcount = GATEUP ? it * 2 + wg : it;
+        const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
+        if (!mbar_wait(smem_u32(&bar_aempty[a]), aph ^ 1u, abortp)) {
+          report(p.status, DEV_TIMEOUT, 301, item, kt);
+          ok = false;
+          break;
+        }
+        const uint8_t* tile = smem_raw + (stage0 - smem_u32(smem_raw)) + s * C::STAGE_BYTES +
+                              (GATEUP ? wg * kTileBytes : 0);
+        const int ch0 = GATEUP ? 0 : wg * 4;
+        uint4 raw[C::NCH];
+#pragma unroll
+        for (int j = 0; j < C::NCH; ++j)
+          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)((ch0 + j) * kTileRows + r) * 16);
+        uint32_t aw[C::NW];
+#pragma unroll
+        for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT>(raw[j], scale, aw + j * C::WPC);
+        const uint32_t col0 = kABaseCol + a * kASlotCols + (GATEUP ? 0 : wg * (C::NW));
+        tc_fence_after();
+        if (C::NW >= 32) {
+#pragma unroll
+          for (int w0 = 0; w0 < C::NW; w0 += 32) tmem_st32(lane_base + col0 + w0, aw + w0);
+        } else {
+          tmem_st16(lane_base + col0, aw);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&bar_afull[a]));
+          mbar_arrive(smem_u32(&bar_empty[s]));
+        }
+      }
+      if (!ok) break;
+      // ---- epilogue ----
+      if (!mbar_wait(smem_u32(&bar_accfull), items_done & 1u, abortp)) {
+        report(p.status, DEV_TIMEOUT, 302, item, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int feat = rt * kTileRows + r;
+      for (int cb = wg; cb < N / 8; cb += 2) {
+        if (cb * 8 >= cd.n_rows) break;
+        uint32_t g[8], u[8];
+        tmem_ld8(lane_base + cb * 8, g);
+        if (GATEUP) tmem_ld8(lane_base + NMAX + cb * 8, u);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int col = cb * 8 + i;
+          if (col < cd.n_rows) {
+            const float gv = __uint_as_float(g[i]);
+            if (GATEUP) {
+              const float uv = __uint_as_float(u[i]);
+              const float h = uv * (gv / (1.f + __expf(-gv)));
+              p.hbuf[(size_t)(cd.out_row + col) * p.d.Ip + feat] = __float2bfloat16_rn(h);
+            } else if (feat < p.d.H) {
+              p.obuf[(size_t)(cd.out_row + col) * p.d.H + feat] = __float2bfloat16_rn(gv);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_accempty));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kConvWarps + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <int QUANT, bool GATEUP, int NMAX>
+int launch_one(const FfnParams& p, cudaStream_t s) {
+  using C = Cfg<QUANT, GATEUP, NMAX>;
+  const int smem = C::STAGES * C::STAGE_BYTES + 1024;
+  cudaFuncSetAttribute(ffn_tc_kernel<QUANT, GATEUP, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  ffn_tc_kernel<QUANT, GATEUP, NMAX><<<p.n_sm, kThreads, smem, s>>>(p);
+  return 1;
+}
+
+template <int QUANT>
+int launch_quant(const FfnParams& p, int nmax, int which, cudaStream_t s) {
+  if (nmax <= 32) return which == 0 ? launch_one<QUANT, true, 32>(p, s) : launch_one<QUANT, false, 32>(p, s);
+  if (nmax <= 64) return which == 0 ? launch_one<QUANT, true, 64>(p, s) : launch_one<QUANT, false, 64>(p, s);
+  return which == 0 ? launch_one<QUANT, true, 128>(p, s) : launch_one<QUANT, false, 128>(p, s);
+}
+
+}  // namespace
+
+int launch_ffn_tc(const FfnParams& p, int nmax, int which, cudaStream_t s) {
+  switch (p.d.quant) {
+    case EK_QUANT_BF16: return launch_quant<EK_QUANT_BF16>(p, nmax, which, s);
+    case EK_QUANT_FP8_BLOCK128: return launch_quant<EK_QUANT_FP8_BLOCK128>(p, nmax, which, s);
+    default: return launch_quant<EK_QUANT_INT8_BLOCK128>(p, nmax, which, s);
+  }
+}
+
+}  // namespace ek

@@ -1,0 +1,207 @@
+// Bucketing: exclusive scan of the per-expert histogram, stable ranking of the flattened
+// [T*k] assignments by expert (ascending token order inside an expert), the inverse map, the
+// chunk work list for the grouped GEMMs and the row gather.
+//
+// Semantics follow NaiveExecutor::break_down_to_egress / assemble_seq_tensors
+// (ek-computation/src/controller/executor.rs:283-299,112-133): a stable counting sort.
+#include "ek_internal.h"
+
+namespace ek {
+
+namespace {
+
+// One CTA per expert: offsets[e] = sum of counts of local experts below e, then one ordered
+// pass over all assignments, ranking the matches with warp scans.
+__global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
+  __shared__ int s_red[8];
+  __shared__ int s_base;
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool local = e >= p.e_lo && e < p.e_hi;
+
+  // exclusive prefix over the local window
+  int part = 0;
+  for (int j = p.e_lo + tid; j < min(e, p.e_hi); j += 256) part += p.counts[j];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) s_red[warp] = part;
+  __syncthreads();
+  if (tid == 0) {
+    int b = 0;
+    for (int w = 0; w < 8; ++w) b += s_red[w];
+    s_base = b;
+    p.offsets[e] = b;
+    if (e == p.E - 1) p.offsets[p.E] = b + (local ? p.counts[e] : 0);
+  }
+  __syncthreads();
+  int running = s_base;
+  const int n = p.T * p.k;
+  const bool empty = p.counts[e] == 0;
+  if (empty) return;
+
+  for (int base = 0; base < n; base += 1024) {
+    const int i0 = base + tid * 4;
+    int id[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) id[j] = (i0 + j < n) ? p.ids[i0 + j] : -1;
+    int c = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c += (id[j] == e);
+    // inclusive warp scan
+    int inc = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    __syncthreads();  // protects s_red from the previous round
+    if (lane == 31) s_red[warp] = inc;
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      int v = s_red[w];
+      if (w < warp) before += v;
+      total += v;
+    }
+    int pos = running + before + inc - c;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (id[j] == e) {
+        if (local) {
+          p.perm[pos] = i0 + j;
+          p.inv[i0 + j] = pos;
+          ++pos;
+        } else {
+          p.inv[i0 + j] = -1;
+        }
+      }
+    }
+    running += total;
+  }
+}
+
+// Chunk descriptors: every local expert's row range cut into pieces of `chunk_rows`, followed
+// by the virtual shared experts (all T tokens each).
+__global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
+  __shared__ int s_scan[1024];
+  __shared__ int s_total;
+  const int tid = threadIdx.x;
+  const int n_local = p.e_hi - p.e_lo;
+  int running = 0;
+  for (int e0 = 0; e0 < n_local; e0 += 1024) {
+    const int le = e0 + tid;
+    int cnt = 0, nch = 0;
+    if (le < n_local) {
+      cnt = p.counts[p.e_lo + le];
+      nch = (cnt + p.chunk_rows - 1) / p.chunk_rows;
+      if (cnt > 0 && !p.registered[le]) {
+        if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
+          p.status->where = 2;
+          p.status->aux0 = p.e_lo + le;
+        }
+        nch = 0;
+      }
+    }
+    s_scan[tid] = nch;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      int v = tid >= o ? s_scan[tid - o] : 0;
+      __syncthreads();
+      s_scan[tid] += v;
+      __syncthreads();
+    }
+    int first = running + s_scan[tid] - nch;
+    if (tid == 1023) s_total = s_scan[tid];
+    if (le < n_local && nch > 0) {
+      const int off = p.offsets[p.e_lo + le];
+      for (int c = 0; c < nch; ++c) {
+        if (first + c >= p.max_chunks) break;
+        ChunkDesc d;
+        d.slot = le;
+        d.in_row = off + c * p.chunk_rows;
+        d.out_row = d.in_row;
+        d.n_rows = min(p.chunk_rows, cnt - c * p.chunk_rows);
+        p.chunks[first + c] = d;
+      }
+    }
+    __syncthreads();
+    running += s_total;
+    __syncthreads();
+  }
+  // shared virtual experts
+  const int per_shared = (p.T + p.chunk_rows - 1) / p.chunk_rows;
+  for (int i = tid; i < p.n_shared * per_shared; i += 1024) {
+    const int j = i / per_shared, c = i % per_shared;
+    if (running + i >= p.max_chunks) break;
+    ChunkDesc d;
+    d.slot = n_local + j;
+    d.in_row = p.Tk + c * p.chunk_rows;
+    d.out_row = p.Tk + j * p.T + c * p.chunk_rows;
+    d.n_rows = min(p.chunk_rows, p.T - c * p.chunk_rows);
+    p.chunks[running + i] = d;
+    if (c == 0 && !p.registered[d.slot]) {
+      if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
+        p.status->where = 3;
+        p.status->aux0 = -1 - j;
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int total = running + p.n_shared * per_shared;
+    if (total > p.max_chunks) {
+      if (atomicCAS(&p.status->code, DEV_OK, DEV_BOUNDS) == DEV_OK) {
+        p.status->where = 4;
+        p.status->aux0 = total;
+      }
+      total = p.max_chunks;
+    }
+    // a missing expert cancels the GEMMs altogether
+    *p.n_chunks = (*reinterpret_cast<volatile int32_t*>(&p.status->code) == DEV_OK) ? total : 0;
+  }
+}
+
+// xp[r,:] = x[perm[r] / k, :] for permuted rows, then (optionally) a straight copy of x for
+// the shared expert.  16-byte vectors.
+__global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __restrict__ x,
+                                                     const int32_t* __restrict__ perm,
+                                                     const int32_t* __restrict__ n_routed,
+                                                     __nv_bfloat16* __restrict__ xp, int32_t T,
+                                                     int32_t k, int32_t H) {
+  const int r = blockIdx.x;
+  const int Tk = T * k;
+  int src;
+  if (r < Tk) {
+    if (r >= *n_routed) return;   // rows of non-local experts are not materialised
+    src = perm[r] / k;
+  } else {
+    src = r - Tk;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(x + (size_t)src * H);
+  uint4* d = reinterpret_cast<uint4*>(xp + (size_t)r * H);
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
+}
+
+}  // namespace
+
+int launch_permute(const PermuteParams& p, cudaStream_t s) {
+  if (p.E > 0) permute_kernel<<<p.E, 256, 0, s>>>(p);
+  return 1;
+}
+
+int launch_worklist(const WorklistParams& p, cudaStream_t s) {
+  worklist_kernel<<<1, 1024, 0, s>>>(p);
+  return 1;
+}
+
+int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_routed,
+                  __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t with_shared,
+                  cudaStream_t s) {
+  const int rows = T * k + (with_shared ? T : 0);
+  if (rows > 0) gather_kernel<<<rows, 128, 0, s>>>(x, perm, n_routed, xp, T, k, H);
+  return rows > 0 ? 1 : 0;
+}
+
+}  // namespace ek

@@ -1,0 +1,238 @@
+/*
+ * ek_b200.h -- C ABI of the B200 (sm_100a) expert-worker compute backend for Expert Kit.
+ *
+ * This is the only boundary between the Expert Kit worker (Rust, `ek-computation`) or the
+ * Python integration packages and the CUDA code.  Plain pointers and sizes only.  Every
+ * entry point names the reference interface it stands in for (paths are relative to the
+ * expert-kit repository root).
+ *
+ * Conventions
+ *   - Every function returns an ek_status_t; nothing throws or aborts across the boundary.
+ *     (The reference panics on malformed requests: ek-computation/src/worker/core.rs:52-56;
+ *     here those become EK_INVALID_INPUT.)
+ *   - `x`, `y`, `out` buffers may be HOST or DEVICE pointers; the library looks at the
+ *     pointer attributes and stages host buffers through its own pinned/device workspace.
+ *   - Weights are copied (and re-tiled) at registration; the caller's bytes may be freed as
+ *     soon as the call returns (the reference aliases them instead:
+ *     ek-computation/src/backend/torch/mod.rs:119-130).
+ *   - All workspace is sized from `max_tokens` at create time; forward calls allocate nothing.
+ *   - A backend may be used from many host threads; forward calls on one backend are
+ *     serialised on the backend's stream, registration/eviction may run concurrently.
+ */
+#ifndef EK_B200_H_
+#define EK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; the first group mirrors EKError (ek-base/src/error.rs:13-72). */
+typedef enum ek_status {
+  EK_OK = 0,
+  EK_EXPERT_NOT_FOUND = 1,        /* EKError::ExpertNotFound        error.rs:26-27 */
+  EK_EXPERT_WEIGHT_NOT_FOUND = 2, /* EKError::ExpertWeightNotFound  error.rs:29-30 */
+  EK_INVALID_INPUT = 3,           /* EKError::InvalidInput          error.rs:50-51 */
+  EK_SAFETENSOR = 4,              /* EKError::SafeTensorError       error.rs:14-15 */
+  EK_NOT_FOUND = 5,               /* EKError::NotFound              error.rs:32-33 */
+  EK_CUDA = 16,                   /* a CUDA runtime/driver call failed */
+  EK_TIMEOUT = 17,                /* a bounded device-side wait ran out; context stays usable */
+  EK_BOUNDS = 18,                 /* device-side index check failed (debug builds) */
+  EK_NO_MEMORY = 19,
+  EK_UNSUPPORTED = 20
+} ek_status_t;
+
+/* Element types; mirrors DType (ek-computation/src/backend/mod.rs:6-15) and the safetensors
+ * dtype strings the weight server emits. */
+typedef enum ek_dtype {
+  EK_BF16 = 0,    /* "BF16" */
+  EK_F32 = 1,     /* "F32"  */
+  EK_F8_E4M3 = 2, /* "F8_E4M3" */
+  EK_I8 = 3,      /* "I8" */
+  EK_I32 = 4,     /* "I32" */
+  EK_F16 = 5,     /* "F16" (accepted for weights, converted to bf16 at registration) */
+  EK_U8 = 6,
+  EK_I64 = 7
+} ek_dtype_t;
+
+/* A named tensor view: what `safetensors::tensor::TensorView` carries
+ * (ek-computation/src/backend/mod.rs:22-29, torch/mod.rs:137-153). */
+typedef struct ek_tensor_view {
+  const char* name;     /* e.g. "model.layers.3.mlp.experts.17.up_proj.weight" */
+  int32_t dtype;        /* ek_dtype_t */
+  int32_t ndim;
+  int64_t shape[4];
+  const void* data;     /* host or device, row-major, contiguous */
+} ek_tensor_view_t;
+
+enum { EK_SCORE_SOFTMAX = 0, EK_SCORE_SIGMOID = 1 };
+enum { EK_QUANT_BF16 = 0, EK_QUANT_FP8_BLOCK128 = 1, EK_QUANT_INT8_BLOCK128 = 2 };
+
+/* Layer/instance configuration.  Stands in for EKInstance{hidden, intermediate, backend}
+ * (ek-computation/src/x.rs:27-43, filled from `inference.*`, ek-base/src/config.rs:26-31) plus
+ * the routing hyper-parameters the Python frontends read from the HF model config
+ * (expertkit_torch/models/qwen3_moe.py:61-63; deepseek_v3/model.py:56). */
+typedef struct ek_config {
+  int32_t hidden;            /* H */
+  int32_t intermediate;      /* I of a routed expert */
+  int32_t n_experts;         /* routed experts per layer (global count) */
+  int32_t top_k;
+  int32_t scoring;           /* EK_SCORE_* */
+  int32_t n_group;           /* 1 = no group limit */
+  int32_t topk_group;
+  int32_t norm_topk_prob;    /* renormalise the selected weights */
+  float routed_scaling;      /* multiplied into the weights after renormalisation */
+  int32_t n_shared_experts;  /* shared expert intermediate = intermediate * n_shared_experts */
+  int32_t bf16_combine;      /* 1: routing weights rounded to bf16, bf16 products (Qwen3 path) */
+  int32_t quant;             /* EK_QUANT_* : storage form of expert weights */
+  int32_t max_tokens;        /* largest T of one forward call; sizes the workspace */
+  int32_t max_layers;        /* number of distinct layer indices that may hold experts */
+  int32_t device;            /* CUDA device ordinal */
+  int32_t ep_rank;           /* expert-parallel rank of this process */
+  int32_t ep_size;           /* number of expert-parallel ranks; experts e with
+                                e / (n_experts/ep_size) == ep_rank are local */
+  char model_name[64];       /* prefix of expert ids: "<model_name>/l<layer>-e<expert>" */
+} ek_config_t;
+
+typedef struct ek_backend ek_backend_t;
+
+/* ---- lifetime ------------------------------------------------------------------------- */
+
+/* ExpertBackend::build's environment (ek-computation/src/ffn/mod.rs:22-35) + the global
+ * ExpertDB (ek-computation/src/worker/manager.rs:32-44). */
+int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out);
+void ek_backend_destroy(ek_backend_t* be);
+
+/* Why the last ek_backend_create on this thread's process failed (no handle exists yet). */
+const char* ek_create_error(void);
+/* Message of the last failure on this backend (handle-local, valid until the next call). */
+const char* ek_last_error(const ek_backend_t* be);
+const char* ek_status_name(int32_t status);
+
+/* ---- expert registry: ExpertDB (ek-computation/src/worker/manager.rs:13-23) ------------- */
+
+/* ExpertDB::insert after ExpertBackend::build -> ExpertWeight::from_safetensor
+ * (ek-computation/src/worker/x.rs:13-34, ffn/meta.rs:57-75).  `id` is
+ * ExpertKey::as_object_key, "model/l{L}-e{E}" (ek-db/src/safetensor/mod.rs:57-91); a shared
+ * expert uses "model/l{L}-shared".  Tensors are picked by the reference's suffix rule:
+ * "w1.weight"|"up_proj.weight", "w2.weight"|"down_proj.weight", "w3.weight"|"gate_proj.weight",
+ * first match wins (torch/mod.rs:137-153); quantised payloads additionally take
+ * "<weight name>_scale_inv" (F32, [ceil(rows/128), ceil(cols/128)];
+ * ek-db/src/safetensor/transformer.rs:258-270). */
+int32_t ek_expert_register(ek_backend_t* be, const char* id,
+                           const ek_tensor_view_t* tensors, int32_t n_tensors);
+
+/* Same, from the serialised bundle the weight server returns for GET /expert/{m}/{l}/{e}
+ * (ek-db/src/safetensor/transformer.rs:282-296; SafeTensorDB::load, mod.rs:136-173). */
+int32_t ek_expert_register_safetensors(ek_backend_t* be, const char* id,
+                                       const void* blob, size_t blob_len);
+
+/* ExpertDB::mark_loading (manager.rs:60-70): *fresh = 1 when this call claimed the id. */
+int32_t ek_expert_mark_loading(ek_backend_t* be, const char* id, int32_t* fresh);
+/* ExpertDB::remove (manager.rs:71-74; caller: worker/state.rs:157-165).  Removing an unknown id
+ * is not an error, as in the reference.  Device memory of the slot is reused by later
+ * registrations once forwards in flight have drained. */
+int32_t ek_expert_evict(ek_backend_t* be, const char* id);
+/* ExpertDB::has / loaded / loading / keys (manager.rs:46-58,86-88). */
+int32_t ek_expert_has(const ek_backend_t* be, const char* id);
+int32_t ek_expert_loaded(const ek_backend_t* be);
+int32_t ek_expert_loading(const ek_backend_t* be);
+/* Writes the ids in ascending string order (BTreeMap order), '\n'-separated, NUL-terminated;
+ * returns EK_INVALID_INPUT and sets *needed when `cap` is too small. */
+int32_t ek_expert_keys(const ek_backend_t* be, char* buf, size_t cap, size_t* needed);
+
+/* Router weight of one layer: `gate.weight` [E,H] (BF16 or F32) and, for sigmoid scoring, the
+ * optional `e_score_correction_bias` [E] F32 (expertkit_torch/models/qwen3_moe.py:65;
+ * deepseek_v3/model.py:56).  Needed only by ek_moe_forward_fused. */
+int32_t ek_router_register(ek_backend_t* be, int32_t layer, const void* weight, int32_t weight_dtype,
+                           const float* bias /* may be NULL */);
+
+/* ---- forward -------------------------------------------------------------------------- */
+
+/* Worker level: EKInstanceGate::forward -> ExpertBackend::forward -> TorchFFN::forward
+ * (ek-computation/src/worker/core.rs:47-74, ffn/mod.rs:39-52, ffn/expert_torch.rs:80-101):
+ * y[n,H] = down( up(x) * silu(gate(x)) ) for one registered expert, bf16 in, bf16 out. */
+int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x_bf16, int32_t n,
+                          void* y_bf16);
+
+/* Controller level: NaiveExecutor submit/exec/output
+ * (ek-computation/src/controller/executor.rs:85-110,135-262,283-299): `ids[T,k]` names one local
+ * expert per (token, slot); `out[T,k,H]` receives the UNWEIGHTED bf16 expert outputs in the
+ * request's slot order -- the payload of ForwardResp (ek-proto/ek/worker/v1/expert.proto:14-17). */
+int32_t ek_moe_forward(ek_backend_t* be, int32_t layer, const void* x_bf16, int32_t T,
+                       const int32_t* ids, int32_t k, void* out_bf16);
+
+/* Optional outputs of the fused call; any pointer may be NULL.  All are written in the
+ * canonical order "descending score, ties towards the lower expert index". */
+typedef struct ek_route_debug {
+  float* logits;      /* [T,E]  fp32 (softmax scoring: the bf16-rounded logits, widened) */
+  int32_t* ids;       /* [T,k]  */
+  float* weights;     /* [T,k]  fp32 (bf16_combine: the bf16-rounded weights, widened) */
+  int32_t* counts;    /* [E]    rows per expert */
+  int32_t* offsets;   /* [E+1]  exclusive prefix sum of counts */
+  int32_t* perm;      /* [T*k]  perm[offsets[e]+r] = token*k+slot of expert e's r-th row */
+} ek_route_debug_t;
+
+/* Frontend + controller + worker in one call: router (qwen3_moe.py:161-169 or the
+ * DeepSeek-V3 router called at deepseek_v3/model.py:142), bucketing (executor.rs:283-299),
+ * expert FFNs (expert_torch.rs:80-85), weighted combine (model.py:96-104, qwen3_moe.py:102-104)
+ * and shared expert (model.py:152):  y[T,H] = shared(x) + sum_k w[t,k] * expert_{ids[t,k]}(x[t]). */
+int32_t ek_moe_forward_fused(ek_backend_t* be, int32_t layer, const void* x_bf16, int32_t T,
+                             void* y_bf16, const ek_route_debug_t* debug /* may be NULL */);
+
+/* Frontend routing alone on caller-supplied logits [T,E] fp32 (same canonical order). */
+int32_t ek_route_from_logits(ek_backend_t* be, const float* logits, int32_t T,
+                             const float* bias /* may be NULL */, int32_t* ids, float* weights,
+                             int32_t* counts, int32_t* offsets, int32_t* perm);
+
+/* Weighted combine alone: y[T,H] = sum_k w[t,k]*out[t,k,:] (+ shared[T,H] if non-NULL), the
+ * frontend's step after ForwardResp (model.py:96-104,152; qwen3_moe.py:102-104). */
+int32_t ek_combine(ek_backend_t* be, const void* out_bf16, const float* weights, int32_t T,
+                   int32_t k, const void* shared_bf16 /* may be NULL */, void* y_bf16);
+
+/* w8a16_activate (ek-computation/src/ffn/expert_torch.rs:24-53):
+ * out_bf16[i,j] = bf16_rne(float(w[i,j]) * scale[i/128, j/128]); rows, cols multiples of 128. */
+int32_t ek_w8a16_activate(ek_backend_t* be, const void* w, int32_t w_dtype, const float* scale,
+                          int32_t rows, int32_t cols, void* out_bf16);
+
+/* Wire level: the worker's handling of one ForwardReq (worker/core.rs:47-74): `req_tensor` is
+ * the safetensors blob holding the single key "data" ([n,H] BF16); `expert_id` is
+ * sequences[0].experts[0]; the reply blob (key "data", [n,H] BF16) is written to `resp`.
+ * *resp_len receives the needed size; EK_INVALID_INPUT if `resp_cap` is too small. */
+int32_t ek_worker_forward_wire(ek_backend_t* be, const char* expert_id, const void* req_tensor,
+                               size_t req_len, void* resp, size_t resp_cap, size_t* resp_len);
+
+/* ---- observability -------------------------------------------------------------------- */
+
+/* Rows per expert seen by the last fused/controller-level call on `layer`: the quantity the
+ * worker exports as `worker_expert_activation` (ek-computation/src/metrics.rs:22-71). */
+int32_t ek_expert_counts(ek_backend_t* be, int32_t layer, int32_t* counts /* [n_experts] */);
+
+enum { EK_STAGE_ROUTE = 0, EK_STAGE_PERMUTE = 1, EK_STAGE_GATEUP = 2, EK_STAGE_DOWN = 3,
+       EK_STAGE_COMBINE = 4, EK_STAGE_COUNT = 5 };
+/* Device time (ms, CUDA events on the backend's stream) of each stage of the last forward
+ * call when stage timing is enabled; the analogue of PerfTimer (ek-base/src/utils.rs:4-45). */
+int32_t ek_stage_timing_enable(ek_backend_t* be, int32_t on);
+int32_t ek_stage_times(ek_backend_t* be, float* ms /* [EK_STAGE_COUNT] */);
+
+/* Number of kernels this library launched on the backend since creation. */
+int64_t ek_kernel_launches(const ek_backend_t* be);
+
+/* Test hook: 0 = tensor-core kernels (default), 1 = the CUDA-core evaluation of the same
+ * tiled weights that the tests use as a second opinion at large sizes.  Not a tuning knob. */
+int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl);
+
+/* ---- device-resident fast path (no host staging, used by the Python integration, the
+ *      benchmark and expert-parallel drivers; stream is a cudaStream_t or NULL) ----------- */
+int32_t ek_set_stream(ek_backend_t* be, void* cuda_stream);
+/* Same as ek_moe_forward_fused with device pointers, asynchronous on the backend stream. */
+int32_t ek_moe_forward_fused_async(ek_backend_t* be, int32_t layer, const void* x_dev, int32_t T,
+                                   void* y_dev);
+int32_t ek_sync(ek_backend_t* be);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EK_B200_H_ */
