@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE expert-layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl reference]
+
+One "step" is one pass of a DeepSeek-V3-shape MoE layer (hidden 7168, intermediate 2048, 256
+routed experts + 1 shared, top-8, group-limited sigmoid routing, FP8-e4m3 weights with
+128x128 fp32 block scales, bf16 activations) over a batch of T tokens: route -> bucket ->
+gather -> grouped gate/up + SwiGLU -> grouped down -> weighted combine + shared expert.
+Weights are random (seeded, generated on the device) and the activations synthetic ~N(0,1).
+
+Prints ONE JSON line.  `value` is tokens/s with inputs and outputs resident in HBM; `e2e` is
+the same pass through the host-buffer entry point of the C ABI (pinned host -> device copy of
+the activations and device -> host read of the result inside the timed region).
+`--impl reference` times the CPU restatement of the reference's torch expert path on the host
+cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "expert-kit_b200"))
+
+import torch  # noqa: E402
+
+METRIC = "MoE expert-layer tokens/s (DSV3 FP8-W/bf16-A)"
+UNIT = "tokens/s"
+H, I, E, K, NSHARED = 7168, 2048, 256, 8, 1
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1590.0
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            j = json.load(open(p))
+            return dict(hbm=float(j["hbm_gbs"]), tf=float(j["bf16_tflops"]),
+                        tf_sus=float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), src="measured")
+        except Exception:
+            pass
+    return dict(hbm=FALLBACK_HBM_GBS, tf=FALLBACK_TFLOPS, tf_sus=1400.0, src="fallback")
+
+
+# ---- clocks ---------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-i", str(gpu_index), "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return None
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.f.name)
+        except OSError:
+            pass
+        if not sm:
+            return None
+        busy = [s for s in sm if s > 0.5 * max(sm)]
+        return {"sm_mhz": statistics.median(busy or sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- synthetic layer on the device ----------------------------------------------------------
+def quantize_fp8_block_dev(w: torch.Tensor):
+    r, c = w.shape
+    b = w.view(r // 128, 128, c // 128, 128)
+    amax = b.abs().amax(dim=(1, 3)).clamp_min(1e-12)
+    s = (amax / 448.0).float()
+    q = (b / s[:, None, :, None]).to(torch.float8_e4m3fn).view(r, c)
+    return q.contiguous(), s.contiguous()
+
+
+def build_backend(T_max: int, rank: int = 0, seed: int = 3000, n_experts: int = E):
+    import ek_b200
+    from ek_b200.backend import expert_tensors
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = ek_b200.BackendConfig(hidden=H, intermediate=I, n_experts=n_experts, top_k=K, scoring=1, n_group=8,
+                                topk_group=4, norm_topk_prob=True, routed_scaling=2.5, n_shared_experts=NSHARED,
+                                bf16_combine=False, quant=1, max_tokens=T_max, max_layers=1,
+                                device=dev.index, model_name="dsv3")
+    be = ek_b200.Backend(cfg)
+    g = torch.Generator(device=dev).manual_seed(seed + rank)
+    wg = (torch.randn(n_experts, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    be.register_router(0, wg, torch.zeros(n_experts, device=dev))
+    for e in list(range(n_experts)) + ["shared"]:
+        mats = []
+        for shape in ((I, H), (I, H), (H, I)):
+            w = torch.randn(shape, generator=g, device=dev) * 0.02
+            mats.append(quantize_fp8_block_dev(w))
+        (up, us), (gate, gs), (down, ds) = mats
+        if e == "shared":
+            be.register_expert(be.shared_id(0), expert_tensors(0, None, up, gate, down, us, gs, ds, shared=True))
+        else:
+            be.register_expert(be.expert_id(0, e), expert_tensors(0, e, up, gate, down, us, gs, ds))
+    return be, dev
+
+
+def algorithmic(T: int, active: int):
+    sc = 12 * (I // 128) * (H // 128)
+    per = 3 * H * I + sc
+    bytes_layer = (active + NSHARED) * per + 2 * H * E + 4 * T * H
+    flops_layer = 2 * T * H * E + 6 * H * I * T * K + 6 * H * I * NSHARED * T
+    rows = T * K + NSHARED * T
+    gu_bytes = (active + NSHARED) * (2 * H * I + 8 * (I // 128) * (H // 128)) + rows * H * 2 + rows * I * 2
+    gu_flops = 4 * H * I * rows
+    return bytes_layer, flops_layer, gu_bytes, gu_flops
+
+
+# ---- CPU baseline (oracle port of the reference's torch expert path) -------------------------
+def cpu_baseline(T: int, budget_s: float = 15.0, seed: int = 5):
+    """Times route + bucket + per-expert bf16 FFN loop + weighted combine + shared expert on the
+    host cores, on a sample of distinct experts (weights dequantised once at load, as the
+    reference's load_module would hold them), and scales the expert loop to the number of
+    experts the routing actually activates."""
+    from oracle import ek_oracle as O
+    from oracle import configs as OC
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = OC.config(3)
+    g = torch.Generator().manual_seed(seed)
+    wg = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    logits, ids, w = O.route(cfg, x, wg, torch.zeros(E))
+    counts, offsets, perm = O.bucket(ids, E)
+    t_route = time.perf_counter() - t0
+    active = int((counts > 0).sum())
+    n_sample = 4
+    experts = []
+    for _ in range(n_sample):
+        ws = [torch.randn(s, generator=g).mul_(0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
+        experts.append(ws)
+    rows_per = max(1, round(T * K / max(active, 1)))
+    xe = x[:rows_per] if rows_per <= T else x.repeat((rows_per + T - 1) // T, 1)[:rows_per]
+    O.expert_ffn(xe, *experts[0])   # warm-up
+    n_calls, t_ffn = 0, 0.0
+    while t_ffn < budget_s * 0.6 and n_calls < 64:
+        ws = experts[n_calls % n_sample]
+        t0 = time.perf_counter()
+        O.expert_ffn(xe, *ws)
+        t_ffn += time.perf_counter() - t0
+        n_calls += 1
+    per_call = t_ffn / n_calls
+    t0 = time.perf_counter()
+    O.expert_ffn(x, *experts[0])    # shared expert: all T rows
+    t_shared = time.perf_counter() - t0
+    outs = torch.zeros(T, K, H, dtype=torch.bfloat16)
+    t0 = time.perf_counter()
+    O.combine(outs, w, False)
+    t_comb = time.perf_counter() - t0
+    step = t_route + active * per_call + t_shared + t_comb
+    return dict(value=T / step, unit=UNIT, cores=cores, kind="port",
+                sample=(f"router+bucket, {n_calls} single-expert FFN calls of {rows_per} rows on {n_sample} distinct "
+                        f"bf16 experts (scaled to the {active} active experts), shared expert, combine; T={T}; "
+                        f"{per_call * 1e3:.2f} ms per expert call"),
+                ms_per_step=step * 1e3)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T = args.tokens
+    vals = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(T, budget_s=max(2.0, 30.0 / max(1, args.warmup + args.steps)), seed=5 + i)
+        if i >= args.warmup:
+            vals.append(base)
+    v = statistics.mean(b["value"] for b in vals)
+    ms = statistics.mean(b["ms_per_step"] for b in vals)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(T, args.gpus),
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": base["cores"], "kind": "port", "sample": base["sample"]},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(T: int, n_gpus: int):
+    return {"workload": f"cfg3 DeepSeek-V3-shape MoE layer, W8A16 (fp8 e4m3 + 128x128 fp32 block scales), T={T} tokens per GPU",
+            "hidden": H, "intermediate": I, "experts": E, "shared_experts": NSHARED, "top_k": K,
+            "routing": "sigmoid, 8 groups, top-4 groups, renormalised, x2.5", "tokens_per_gpu": T,
+            "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} data-parallel replicas (weak scaling)",
+            "l2": "weights streamed per step (11.3 GB) exceed the 126 MB L2; no flush needed"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=256)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--sweep", default="", help="comma-separated extra token counts reported under 'sweep'")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    T = args.tokens
+    sweep = [int(t) for t in args.sweep.split(",") if t]
+    be, dev = build_backend(max([T] + sweep), rank)
+    # the library launches on this stream, so torch's events bracket exactly its kernels
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    be.set_stream(stream.cuda_stream)
+    g = torch.Generator(device=dev).manual_seed(17 + rank)
+
+    def timed(Tn: int, steps: int, warmup: int):
+        xs = [torch.randn(Tn, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(4)]
+        y = torch.empty(Tn, H, dtype=torch.bfloat16, device=dev)
+        for i in range(warmup):
+            be.moe_forward_fused_async(0, xs[i % 4], y)
+        be.sync()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        l0 = be.kernel_launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            be.moe_forward_fused_async(0, xs[i % 4], y)
+        e1.record()
+        be.sync()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        launches = be.kernel_launches() - l0
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = float(t.item())
+        return ms, launches, xs
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, launches, xs = timed(T, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_step = ms / args.steps
+    value = world * T * args.steps / (ms / 1e3)
+
+    # dominant kernel: per-launch duration from CUDA events on the launching stream
+    be.stage_timing(True)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    stage = {}
+    n_prof = min(args.steps, 10)
+    for i in range(n_prof):
+        be.moe_forward_fused_async(0, xs[i % 4], y)
+        be.sync()
+        for k_, v in be.stage_times().items():
+            stage[k_] = stage.get(k_, 0.0) + v / n_prof
+    be.stage_timing(False)
+    counts = be.expert_counts(0)
+    active = int((counts > 0).sum())
+    P = peaks()
+    bytes_layer, flops_layer, gu_bytes, gu_flops = algorithmic(T, active)
+    gu_s = stage["gateup"] / 1e3
+    t_hbm, t_tc = gu_bytes / (P["hbm"] * 1e9), gu_flops / (P["tf"] * 1e12)
+    if t_hbm >= t_tc:
+        roof = {"bound": "hbm", "achieved": gu_bytes / gu_s / 1e9, "peak": P["hbm"], "unit": "GB/s"}
+    else:
+        roof = {"bound": "tensor", "achieved": gu_flops / gu_s / 1e12, "peak": P["tf"], "unit": "TFLOP/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = None
+    roof["kernel"] = "ffn_tc_kernel<fp8, gate/up + SwiGLU>"
+    roof["peak_source"] = P["src"]
+    roof["launch_ms"] = stage["gateup"]
+    roof["algorithmic_bytes"] = gu_bytes
+    layer_roof_s = max(bytes_layer / (P["hbm"] * 1e9), flops_layer / (P["tf_sus"] * 1e12))
+    layer = {"roofline_tokens_per_s": T / layer_roof_s, "frac": (T / (ms_step / 1e3)) / (T / layer_roof_s),
+             "bound": "hbm" if bytes_layer / (P["hbm"] * 1e9) >= flops_layer / (P["tf_sus"] * 1e12) else "tensor",
+             "bytes": bytes_layer, "flops": flops_layer, "active_experts": active, "stage_ms": stage}
+
+    # end to end through the host-buffer entry point of the C ABI
+    xh = [x.cpu().pin_memory() for x in xs]
+    yh = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    for i in range(2):
+        be._check(be._lib.ek_moe_forward_fused(be._h, 0, xh[i].data_ptr(), T, yh.data_ptr(), None))
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        be._check(be._lib.ek_moe_forward_fused(be._h, 0, xh[i % 4].data_ptr(), T, yh.data_ptr(), None))
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * T * e2e_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
+           "d2h_bytes_per_step": T * H * 2, "steps": e2e_steps}
+
+    sweep_out = {}
+    for Tn in sweep:
+        ms_n, _, _ = timed(Tn, max(3, args.steps // 2), 3)
+        st = ms_n / max(3, args.steps // 2)
+        c = be.expert_counts(0)
+        a = int((c > 0).sum())
+        bl, fl, _, _ = algorithmic(Tn, a)
+        rs = max(bl / (P["hbm"] * 1e9), fl / (P["tf_sus"] * 1e12))
+        sweep_out[str(Tn)] = {"tokens_per_s": world * Tn / (st / 1e3), "ms_per_step": st, "active_experts": a,
+                              "layer_roofline_frac": (rs * 1e3) / st}
+
+    if rank == 0:
+        base = None
+        if not args.no_cpu_baseline:
+            b = cpu_baseline(T)
+            base = {k_: b[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(T, world),
+                "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+                "layer_roofline": layer, "cpu_baseline": base}
+        if sweep_out:
+            line["sweep"] = sweep_out
+        print(json.dumps(line))
+    be.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

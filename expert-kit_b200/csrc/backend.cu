@@ -123,6 +123,15 @@ bool is_device_ptr(const void* p) {
   return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
+bool is_pinned_host(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeHost;
+}
+
 bool ends_with(const std::string& s, const char* suf) {
   size_t n = strlen(suf);
   return s.size() >= n && memcmp(s.data() + s.size() - n, suf, n) == 0;
@@ -351,6 +360,8 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
     be->launches += launch_route_select(rp, s);
     ids = be->ids;
   } else {
+    // caller-supplied ids may be invalid: rows that no expert claims must read as "absent"
+    cudaMemsetAsync(be->inv, 0xFF, sizeof(int32_t) * Tk, s);
     be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
   }
   mark(be, 1);
@@ -875,9 +886,14 @@ static int stage_in(ek_backend* be, const void* x, size_t bytes, const __nv_bflo
     *dev = reinterpret_cast<const __nv_bfloat16*>(x);
     return EK_OK;
   }
-  // pageable host memory -> pinned staging -> device, all inside the call
-  memcpy(be->h_x, x, bytes);
-  CK(cudaMemcpyAsync(be->x_dev, be->h_x, bytes, cudaMemcpyHostToDevice, be->stream));
+  // pageable host memory -> pinned staging -> device, all inside the call; memory the caller
+  // already pinned is copied from directly
+  const void* src = x;
+  if (!is_pinned_host(x)) {
+    memcpy(be->h_x, x, bytes);
+    src = be->h_x;
+  }
+  CK(cudaMemcpyAsync(be->x_dev, src, bytes, cudaMemcpyHostToDevice, be->stream));
   *dev = be->x_dev;
   return EK_OK;
 }
@@ -902,7 +918,8 @@ int32_t ek_moe_forward_fused(ek_backend_t* be, int32_t layer, const void* x, int
   rc = run_layer(be, li->second, xd, T, c.top_k, nullptr, yd, nullptr);
   if (rc != EK_OK) return rc;
   cudaStream_t s = be->stream;
-  if (!y_dev) CK(cudaMemcpyAsync(be->h_y, be->y_dev, bytes, cudaMemcpyDeviceToHost, s));
+  const bool y_pinned = !y_dev && is_pinned_host(y);
+  if (!y_dev) CK(cudaMemcpyAsync(y_pinned ? y : be->h_y, be->y_dev, bytes, cudaMemcpyDeviceToHost, s));
   if (dbg) {
     const size_t E = c.n_experts, K = c.top_k;
     if (dbg->logits) CK(cudaMemcpyAsync(dbg->logits, be->logits, T * E * 4, cudaMemcpyDefault, s));
@@ -914,7 +931,7 @@ int32_t ek_moe_forward_fused(ek_backend_t* be, int32_t layer, const void* x, int
   }
   rc = check_status(be);
   if (rc != EK_OK) return rc;
-  if (!y_dev) memcpy(y, be->h_y, bytes);
+  if (!y_dev && !y_pinned) memcpy(y, be->h_y, bytes);
   return finish_timing(be);
 }
 
