@@ -136,11 +136,11 @@ def build_backend(T_max: int, rank: int = 0, seed: int = 3000, n_experts: int = 
     return be, dev
 
 
-def algorithmic(T: int, active: int):
+def algorithmic(T: int, active: int, n_exp: int = E):
     sc = 12 * (I // 128) * (H // 128)
     per = 3 * H * I + sc
-    bytes_layer = (active + NSHARED) * per + 2 * H * E + 4 * T * H
-    flops_layer = 2 * T * H * E + 6 * H * I * T * K + 6 * H * I * NSHARED * T
+    bytes_layer = (active + NSHARED) * per + 2 * H * n_exp + 4 * T * H
+    flops_layer = 2 * T * H * n_exp + 6 * H * I * T * K + 6 * H * I * NSHARED * T
     rows = T * K + NSHARED * T
     gu_bytes = (active + NSHARED) * (2 * H * I + 8 * (I // 128) * (H // 128)) + rows * H * 2 + rows * I * 2
     gu_flops = 4 * H * I * rows
@@ -219,9 +219,10 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def workload_config(T: int, n_gpus: int):
-    return {"workload": f"cfg3 DeepSeek-V3-shape MoE layer, W8A16 (fp8 e4m3 + 128x128 fp32 block scales), T={T} tokens per GPU",
-            "hidden": H, "intermediate": I, "experts": E, "shared_experts": NSHARED, "top_k": K,
+def workload_config(T: int, n_gpus: int, n_exp: int = E):
+    return {"workload": f"cfg3 DeepSeek-V3-shape MoE layer, W8A16 (fp8 e4m3 + 128x128 fp32 block scales), T={T} tokens per GPU"
+                        + ("" if n_exp == E else f" [REDUCED to {n_exp} routed experts: profiling case, not the benchmark]"),
+            "hidden": H, "intermediate": I, "experts": n_exp, "shared_experts": NSHARED, "top_k": K,
             "routing": "sigmoid, 8 groups, top-4 groups, renormalised, x2.5", "tokens_per_gpu": T,
             "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} data-parallel replicas (weak scaling)",
             "l2": "weights streamed per step (11.3 GB) exceed the 126 MB L2; no flush needed"}
@@ -236,6 +237,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--sweep", default="", help="comma-separated extra token counts reported under 'sweep'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=E,
+                    help="routed experts (default: the full 256; smaller values give profiler-sized cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     if args.impl == "reference":
@@ -255,7 +258,8 @@ def main():
 
     T = args.tokens
     sweep = [int(t) for t in args.sweep.split(",") if t]
-    be, dev = build_backend(max([T] + sweep), rank)
+    n_exp = args.experts
+    be, dev = build_backend(max([T] + sweep), rank, n_experts=n_exp)
     # the library launches on this stream, so torch's events bracket exactly its kernels
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
@@ -289,8 +293,9 @@ def main():
         return ms, launches, xs
 
     sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        time.sleep(1.0)   # nvidia-smi needs about a second before its first sample
     ms, launches, xs = timed(T, args.steps, args.warmup)
-    clocks = sampler.stop() if sampler else None
     ms_step = ms / args.steps
     value = world * T * args.steps / (ms / 1e3)
 
@@ -305,10 +310,17 @@ def main():
         for k_, v in be.stage_times().items():
             stage[k_] = stage.get(k_, 0.0) + v / n_prof
     be.stage_timing(False)
+    if sampler:
+        # keep the GPU under the same load until the sampler has seen it for half a second
+        t_end = time.perf_counter() + 0.6
+        while time.perf_counter() < t_end:
+            be.moe_forward_fused_async(0, xs[0], y)
+            be.sync()
+    clocks = sampler.stop() if sampler else None
     counts = be.expert_counts(0)
     active = int((counts > 0).sum())
     P = peaks()
-    bytes_layer, flops_layer, gu_bytes, gu_flops = algorithmic(T, active)
+    bytes_layer, flops_layer, gu_bytes, gu_flops = algorithmic(T, active, n_exp)
     gu_s = stage["gateup"] / 1e3
     t_hbm, t_tc = gu_bytes / (P["hbm"] * 1e9), gu_flops / (P["tf"] * 1e12)
     if t_hbm >= t_tc:
@@ -353,7 +365,7 @@ def main():
         st = ms_n / max(3, args.steps // 2)
         c = be.expert_counts(0)
         a = int((c > 0).sum())
-        bl, fl, _, _ = algorithmic(Tn, a)
+        bl, fl, _, _ = algorithmic(Tn, a, n_exp)
         rs = max(bl / (P["hbm"] * 1e9), fl / (P["tf_sus"] * 1e12))
         sweep_out[str(Tn)] = {"tokens_per_s": world * Tn / (st / 1e3), "ms_per_step": st, "active_experts": a,
                               "layer_roofline_frac": (rs * 1e3) / st}
@@ -365,7 +377,7 @@ def main():
             base = {k_: b[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(T, world),
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(T, world, n_exp),
                 "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
                 "layer_roofline": layer, "cpu_baseline": base}
         if sweep_out:

@@ -55,6 +55,7 @@ struct ek_backend {
   bool timing = false;
   float stage_ms[EK_STAGE_COUNT] = {};
   int ffn_impl = 0;                    // 0 tensor cores, 1 CUDA-core checker
+  int precise = 0;                     // fp8 block scales in fp32 inside the GEMM
 
   // workspace
   __nv_bfloat16 *x_dev = nullptr, *y_dev = nullptr, *xp = nullptr, *hbuf = nullptr, *obuf = nullptr;
@@ -280,6 +281,7 @@ FfnParams ffn_params(ek_backend* be, const Layer& L) {
   p.x_maps = be->maps;
   p.h_maps = be->maps + 4;
   p.n_sm = be->n_sm;
+  p.precise = be->precise;
   return p;
 }
 
@@ -543,6 +545,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   if (rc != EK_OK) return cleanup_fail(rc);
   const char* impl = getenv("EK_B200_FFN_IMPL");
   if (impl && std::string(impl) == "simt") be->ffn_impl = 1;
+  const char* prec = getenv("EK_B200_PRECISE_DEQUANT");
+  if (prec && prec[0] == '1') be->precise = 1;
   *out = be;
   return EK_OK;
 }
@@ -735,6 +739,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
       rp.row0 = v * c.intermediate; rp.n_rows = c.intermediate;
       rp.col0 = 0; rp.n_cols = c.hidden;
       rp.esz = esz;
+      rp.pair_interleave = c.quant == EK_QUANT_FP8_BLOCK128;
       rp.dst = gu0 + (size_t)m * kTileBytes;
       rp.rt_stride = (int64_t)d.kt_gu * 2 * kTileBytes;
       rp.kt_stride = 2 * kTileBytes;
@@ -755,6 +760,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     rp.row0 = 0; rp.n_rows = c.hidden;
     rp.col0 = v * c.intermediate; rp.n_cols = c.intermediate;
     rp.esz = esz;
+    rp.pair_interleave = c.quant == EK_QUANT_FP8_BLOCK128;
     rp.dst = dn0;
     rp.rt_stride = (int64_t)d.kt_dn * kTileBytes;
     rp.kt_stride = kTileBytes;
@@ -1153,6 +1159,13 @@ int32_t ek_stage_times(ek_backend_t* be, float* ms) {
   return EK_OK;
 }
 int64_t ek_kernel_launches(const ek_backend_t* be) { return be ? be->launches.load() : 0; }
+
+int32_t ek_set_precise_dequant(ek_backend_t* be, int32_t on) {
+  if (!be) return EK_INVALID_INPUT;
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  be->precise = on != 0;
+  return EK_OK;
+}
 
 int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl) {
   if (!be || impl < 0 || impl > 1) return EK_INVALID_INPUT;

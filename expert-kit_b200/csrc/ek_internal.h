@@ -131,6 +131,7 @@ struct FfnParams {
   const CUtensorMap* x_maps;   // device array[4]
   const CUtensorMap* h_maps;   // device array[4]
   int32_t n_sm;
+  int32_t precise;           // fp8: apply block scales in fp32 (bit-exact reference dequantisation)
 };
 // Straightforward CUDA-core evaluation of the same tiled weights; used by the tests as an
 // independent check of the tensor-core path at sizes the CPU oracle cannot reach.
@@ -160,6 +161,7 @@ struct RetileParams {
   int32_t row0, n_rows;   // source row window written as tiles (virtual shared experts)
   int32_t col0, n_cols;   // source column window
   int32_t esz;            // 1 or 2
+  int32_t pair_interleave;  // fp8: store K-consecutive pairs in the form the GEMM decodes cheaply
   uint8_t* dst;           // first tile of (row tile 0, k tile 0)
   int64_t rt_stride;      // bytes between consecutive row tiles
   int64_t kt_stride;      // bytes between consecutive K tiles

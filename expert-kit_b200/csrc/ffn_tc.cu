@@ -67,21 +67,51 @@ __device__ __forceinline__ void report(DevStatus* st, int code, int where, int a
 }
 
 // ---- dequantisation of one 16-byte chunk into packed bf16 pairs ---------------------------
-// fp8 e4m3: the byte [s eeee mmm] placed as fp32 bits s<<31 | (eeeemmm)<<20 is the value
-// times 2^-120 exactly (subnormals included); multiplying by 2^120 restores it, then the fp32
-// block scale is applied and the product rounded to bf16 once: bf16_rne(float(w) * scale).
+// fp8 e4m3 payloads are stored pair-interleaved (see layout.cu): for two K-consecutive
+// weights a, b the stored bytes are
+//     p = [sa . . . . ea3 ea2 ea1] | [. eb0 mb2 mb1 mb0 . . .]
+//     q = [sb . . . . eb3 eb2 eb1] | [. ea0 ma2 ma1 ma0 . . .]
+// so that with w1 = w << 1 one byte permute and one AND yield, per 16-bit lane,
+//     [s 0000 eeee mmm 0000]  =  bf16 bits of  value * 2^-120   (exact, subnormals included).
+// One shift per four weights, one permute + one AND per two: 1.25 integer ops per weight
+// instead of 4 for plain e4m3 bytes - the integer pipe is what bounds this kernel otherwise.
+//
+// The block scale is then applied either
+//   fast   : packed, with the scale split into two bf16 terms s = hi + lo (hi = bf16(s * 2^120),
+//            lo = bf16(s * 2^120 - hi)):  out = fma(y, hi, y * lo)  - two bf16x2 ops per two
+//            weights, 16 significant bits of the scale, one final rounding; differs from the
+//            reference formula only where the product lies within 2^-17 of a rounding boundary, or
+//   precise: in fp32, one rounding to bf16 - bit-exact bf16_rne(float(w) * scale), the reference
+//            formula (ek-computation/src/ffn/expert_torch.rs:24-53).
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ void cvt_fp8_word(uint32_t w, float scale, uint32_t* out) {
-  const float k = 0x1p120f;
-  float f0 = __uint_as_float(((w << 24) & 0x80000000u) | ((w << 20) & 0x07F00000u));
-  float f1 = __uint_as_float(((w << 16) & 0x80000000u) | ((w << 12) & 0x07F00000u));
-  float f2 = __uint_as_float(((w << 8) & 0x80000000u) | ((w << 4) & 0x07F00000u));
-  float f3 = __uint_as_float((w & 0x80000000u) | ((w >> 4) & 0x07F00000u));
-  out[0] = pack_bf16(__fmul_rn(__fmul_rn(f0, k), scale), __fmul_rn(__fmul_rn(f1, k), scale));
-  out[1] = pack_bf16(__fmul_rn(__fmul_rn(f2, k), scale), __fmul_rn(__fmul_rn(f3, k), scale));
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+template <bool PRECISE>
+__device__ __forceinline__ void cvt_fp8_word(uint32_t w, float scale, uint32_t s_hi, uint32_t s_lo, uint32_t* out) {
+  const uint32_t w1 = w << 1;
+  const uint32_t y0 = __byte_perm(w, w1, 0x1405) & 0x87F087F0u;
+  const uint32_t y1 = __byte_perm(w, w1, 0x3627) & 0x87F087F0u;
+  if (PRECISE) {
+    const float k = 0x1p120f;
+    out[0] = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(y0 << 16), k), scale),
+                       __fmul_rn(__fmul_rn(__uint_as_float(y0 & 0xFFFF0000u), k), scale));
+    out[1] = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(y1 << 16), k), scale),
+                       __fmul_rn(__fmul_rn(__uint_as_float(y1 & 0xFFFF0000u), k), scale));
+  } else {
+    out[0] = fma_bf16x2(y0, s_hi, mul_bf16x2(y0, s_lo));
+    out[1] = fma_bf16x2(y1, s_hi, mul_bf16x2(y1, s_lo));
+  }
 }
 __device__ __forceinline__ void cvt_int8_word(uint32_t w, float scale, uint32_t* out) {
   float f0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w & 0xff)));
@@ -91,15 +121,15 @@ __device__ __forceinline__ void cvt_int8_word(uint32_t w, float scale, uint32_t*
   out[0] = pack_bf16(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
   out[1] = pack_bf16(__fmul_rn(f2, scale), __fmul_rn(f3, scale));
 }
-template <int QUANT>
-__device__ __forceinline__ void cvt_chunk(const uint4& raw, float scale, uint32_t* out) {
+template <int QUANT, bool PRECISE>
+__device__ __forceinline__ void cvt_chunk(const uint4& raw, float scale, uint32_t s_hi, uint32_t s_lo, uint32_t* out) {
   if (QUANT == EK_QUANT_BF16) {
     out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
   } else if (QUANT == EK_QUANT_FP8_BLOCK128) {
-    cvt_fp8_word(raw.x, scale, out + 0);
-    cvt_fp8_word(raw.y, scale, out + 2);
-    cvt_fp8_word(raw.z, scale, out + 4);
-    cvt_fp8_word(raw.w, scale, out + 6);
+    cvt_fp8_word<PRECISE>(raw.x, scale, s_hi, s_lo, out + 0);
+    cvt_fp8_word<PRECISE>(raw.y, scale, s_hi, s_lo, out + 2);
+    cvt_fp8_word<PRECISE>(raw.z, scale, s_hi, s_lo, out + 4);
+    cvt_fp8_word<PRECISE>(raw.w, scale, s_hi, s_lo, out + 6);
   } else {
     cvt_int8_word(raw.x, scale, out + 0);
     cvt_int8_word(raw.y, scale, out + 2);
@@ -114,7 +144,7 @@ __device__ __forceinline__ int pick_n(int rows, int nmax) {
 }
 __device__ __forceinline__ int map_index(int n) { return n == 16 ? 0 : n == 32 ? 1 : n == 64 ? 2 : 3; }
 
-template <int QUANT, bool GATEUP, int NMAX>
+template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
 __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
   using C = Cfg<QUANT, GATEUP, NMAX>;
   extern __shared__ uint8_t smem_raw[];
@@ -160,6 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     // =============================== producer ==============================================
     if (lane == 0) {
       const CUtensorMap* maps = GATEUP ? p.x_maps : p.h_maps;
+      const uint64_t stream_once = policy_evict_first();   // weights are read exactly once per pass
       uint32_t it = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -181,7 +212,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
           mbar_arrive_expect_tx(full, C::W_BYTES + N * C::TKE * 2);
-          bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
+          bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
 #pragma unroll
           for (int a = 0; a < C::TKE / 64; ++a)
             tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
@@ -293,8 +324,17 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         for (int j = 0; j < C::NCH; ++j)
           raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)((ch0 + j) * kTileRows + r) * 16);
         uint32_t aw[C::NW];
+        uint32_t s_hi = 0, s_lo = 0;
+        if (QUANT == EK_QUANT_FP8_BLOCK128 && !PRECISE) {
+          const float sk = scale * 0x1p120f;
+          const __nv_bfloat16 hi = __float2bfloat16_rn(sk);
+          const __nv_bfloat162 h2 = __halves2bfloat162(hi, hi);
+          const __nv_bfloat162 l2 = __float2bfloat162_rn(sk - __bfloat162float(hi));
+          s_hi = *reinterpret_cast<const uint32_t*>(&h2);
+          s_lo = *reinterpret_cast<const uint32_t*>(&l2);
+        }
 #pragma unroll
-        for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT>(raw[j], scale, aw + j * C::WPC);
+        for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT, PRECISE>(raw[j], scale, s_hi, s_lo, aw + j * C::WPC);
         const uint32_t col0 = kABaseCol + a * kASlotCols + (GATEUP ? 0 : wg * (C::NW));
         tc_fence_after();
         if (C::NW >= 32) {
@@ -355,29 +395,33 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   }
 }
 
-template <int QUANT, bool GATEUP, int NMAX>
+template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
 int launch_one(const FfnParams& p, cudaStream_t s) {
   using C = Cfg<QUANT, GATEUP, NMAX>;
   const int smem = C::STAGES * C::STAGE_BYTES + 1024;
-  cudaFuncSetAttribute(ffn_tc_kernel<QUANT, GATEUP, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  ffn_tc_kernel<QUANT, GATEUP, NMAX><<<p.n_sm, kThreads, smem, s>>>(p);
+  cudaFuncSetAttribute(ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE><<<p.n_sm, kThreads, smem, s>>>(p);
   return 1;
 }
 
-template <int QUANT>
+template <int QUANT, bool PRECISE>
 int launch_quant(const FfnParams& p, int nmax, int which, cudaStream_t s) {
-  if (nmax <= 32) return which == 0 ? launch_one<QUANT, true, 32>(p, s) : launch_one<QUANT, false, 32>(p, s);
-  if (nmax <= 64) return which == 0 ? launch_one<QUANT, true, 64>(p, s) : launch_one<QUANT, false, 64>(p, s);
-  return which == 0 ? launch_one<QUANT, true, 128>(p, s) : launch_one<QUANT, false, 128>(p, s);
+  if (nmax <= 32)
+    return which == 0 ? launch_one<QUANT, true, 32, PRECISE>(p, s) : launch_one<QUANT, false, 32, PRECISE>(p, s);
+  if (nmax <= 64)
+    return which == 0 ? launch_one<QUANT, true, 64, PRECISE>(p, s) : launch_one<QUANT, false, 64, PRECISE>(p, s);
+  return which == 0 ? launch_one<QUANT, true, 128, PRECISE>(p, s) : launch_one<QUANT, false, 128, PRECISE>(p, s);
 }
 
 }  // namespace
 
 int launch_ffn_tc(const FfnParams& p, int nmax, int which, cudaStream_t s) {
   switch (p.d.quant) {
-    case EK_QUANT_BF16: return launch_quant<EK_QUANT_BF16>(p, nmax, which, s);
-    case EK_QUANT_FP8_BLOCK128: return launch_quant<EK_QUANT_FP8_BLOCK128>(p, nmax, which, s);
-    default: return launch_quant<EK_QUANT_INT8_BLOCK128>(p, nmax, which, s);
+    case EK_QUANT_BF16: return launch_quant<EK_QUANT_BF16, true>(p, nmax, which, s);
+    case EK_QUANT_FP8_BLOCK128:
+      return p.precise ? launch_quant<EK_QUANT_FP8_BLOCK128, true>(p, nmax, which, s)
+                       : launch_quant<EK_QUANT_FP8_BLOCK128, false>(p, nmax, which, s);
+    default: return launch_quant<EK_QUANT_INT8_BLOCK128, true>(p, nmax, which, s);
   }
 }
 

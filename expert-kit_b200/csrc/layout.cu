@@ -10,6 +10,23 @@ namespace ek {
 
 namespace {
 
+// Pair interleave of fp8 e4m3 bytes (decoded in ffn_tc.cu / ffn_simt.cu): for K-consecutive
+// weights a, b store
+//   p = (a & 0x80) | ((a >> 4) & 0x07) | ((b & 0x0F) << 3)
+//   q = (b & 0x80) | ((b >> 4) & 0x07) | ((a & 0x0F) << 3)
+// a lossless re-arrangement of the same 16 bits.
+__device__ __forceinline__ uint32_t interleave_word(uint32_t w) {
+  uint32_t out = 0;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t a = (w >> (16 * h)) & 0xFF, b = (w >> (16 * h + 8)) & 0xFF;
+    const uint32_t p = (a & 0x80) | ((a >> 4) & 0x07) | ((b & 0x0F) << 3);
+    const uint32_t q = (b & 0x80) | ((b >> 4) & 0x07) | ((a & 0x0F) << 3);
+    out |= (p | (q << 8)) << (16 * h);
+  }
+  return out;
+}
+
 // One CTA per tile; thread handles 4 of the tile's 1024 16-byte chunks.
 __global__ void __launch_bounds__(256) retile_kernel(RetileParams p) {
   const int rt = blockIdx.y, kt = blockIdx.x;
@@ -34,6 +51,12 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileParams p) {
         for (int b = 0; b < 16; ++b) tmp[b] = (lcb + b < win_bytes) ? s[b] : 0;
         v = *reinterpret_cast<uint4*>(tmp);
       }
+    }
+    if (p.pair_interleave) {
+      v.x = interleave_word(v.x);
+      v.y = interleave_word(v.y);
+      v.z = interleave_word(v.z);
+      v.w = interleave_word(v.w);
     }
     *reinterpret_cast<uint4*>(tile + (size_t)(j * kTileRows + r) * 16) = v;
   }

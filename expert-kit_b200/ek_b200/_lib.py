@@ -72,6 +72,7 @@ SIGNATURES = {
     "ek_stage_times": (C.c_int32, [C.c_void_p, C.POINTER(C.c_float)]),
     "ek_kernel_launches": (C.c_int64, [C.c_void_p]),
     "ek_debug_set_ffn_impl": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "ek_set_precise_dequant": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ek_set_stream": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "ek_moe_forward_fused_async": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "ek_sync": (C.c_int32, [C.c_void_p]),

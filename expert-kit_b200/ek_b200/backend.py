@@ -283,6 +283,10 @@ class Backend:
     def kernel_launches(self) -> int:
         return int(self._lib.ek_kernel_launches(self._h))
 
+    def set_precise_dequant(self, on: bool):
+        """fp8: apply block scales in fp32 inside the GEMM (bit-exact reference dequantisation)."""
+        self._check(self._lib.ek_set_precise_dequant(self._h, int(on)))
+
     def debug_set_ffn_impl(self, impl: int):
         self._check(self._lib.ek_debug_set_ffn_impl(self._h, impl))
 

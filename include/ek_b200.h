@@ -220,6 +220,13 @@ int32_t ek_stage_times(ek_backend_t* be, float* ms /* [EK_STAGE_COUNT] */);
 /* Number of kernels this library launched on the backend since creation. */
 int64_t ek_kernel_launches(const ek_backend_t* be);
 
+/* FP8 block scales inside the grouped GEMM.  0 (default): the scale is split into two bf16
+ * terms and applied with packed bf16 arithmetic (16 significant bits of the scale, one final
+ * rounding; equals the reference formula except within 2^-17 of a rounding boundary).  1: applied
+ * in fp32 with one rounding, bit-exact w8a16_activate (ek-computation/src/ffn/expert_torch.rs:24-53)
+ * at roughly a third of the weight-streaming rate.  ek_w8a16_activate itself is always exact. */
+int32_t ek_set_precise_dequant(ek_backend_t* be, int32_t on);
+
 /* Test hook: 0 = tensor-core kernels (default), 1 = the CUDA-core evaluation of the same
  * tiled weights that the tests use as a second opinion at large sizes.  Not a tuning knob. */
 int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl);
