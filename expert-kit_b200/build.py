@@ -15,8 +15,11 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OUT_DIR = os.path.join(HERE, "lib")
+# EK_B200_VARIANT=<name> with EK_B200_EXTRA_FLAGS builds a side-by-side variant (lib/<name>/...)
+VARIANT = os.environ.get("EK_B200_VARIANT", "")
+OUT_DIR = os.path.join(HERE, "lib", VARIANT) if VARIANT else os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libek_b200.so")
+EXTRA = os.environ.get("EK_B200_EXTRA_FLAGS", "").split()
 SOURCES = ["backend.cu", "route.cu", "permute.cu", "combine.cu", "layout.cu", "ffn_simt.cu", "ffn_tc.cu"]
 HEADERS = ["ek_internal.h", "ptx.cuh", "safetensors.hpp", os.path.join("..", "..", "include", "ek_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -48,7 +51,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(OUT_DIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + hdrs):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [nvcc] + NVCC_FLAGS + EXTRA + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):

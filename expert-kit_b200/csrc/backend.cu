@@ -66,6 +66,7 @@ struct ek_backend {
   ChunkDesc* chunks = nullptr;
   int32_t* n_chunks = nullptr;
   DevStatus* status = nullptr;
+  long long* prof = nullptr;           // 4 roles x 8 counters (profile builds)
   DevStatus* h_status = nullptr;       // pinned
   ChunkDesc* h_chunks = nullptr;       // pinned, worker-level call
   CUtensorMap* maps = nullptr;         // device: x_maps[4], h_maps[4]
@@ -282,6 +283,7 @@ FfnParams ffn_params(ek_backend* be, const Layer& L) {
   p.h_maps = be->maps + 4;
   p.n_sm = be->n_sm;
   p.precise = be->precise;
+  p.prof = be->prof;
   return p;
 }
 
@@ -534,6 +536,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMalloc(&be->n_chunks, 4));
   CKC(cudaMalloc(&be->status, sizeof(DevStatus)));
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
+  CKC(cudaMalloc(&be->prof, 32 * sizeof(long long)));
+  CKC(cudaMemset(be->prof, 0, 32 * sizeof(long long)));
   CKC(cudaMallocHost(&be->h_status, sizeof(DevStatus)));
   CKC(cudaMallocHost(&be->h_chunks, sizeof(ChunkDesc) * 1024));
   CKC(cudaMalloc(&be->maps, sizeof(CUtensorMap) * 8));
@@ -561,7 +565,7 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaFree(be->tk_dev);
   cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->ids); cudaFree(be->counts);
   cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
-  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->maps);
+  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->prof); cudaFree(be->maps);
   cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
@@ -1166,6 +1170,19 @@ int32_t ek_set_precise_dequant(ek_backend_t* be, int32_t on) {
   be->precise = on != 0;
   return EK_OK;
 }
+
+#ifdef EK_TC_PROFILE
+// Profile builds only: read and clear the per-role cycle counters of the tensor-core kernels.
+int32_t ek_debug_profile(ek_backend_t* be, long long* out32) {
+  if (!be || !out32) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  cudaStreamSynchronize(be->stream);
+  cudaMemcpy(out32, be->prof, 32 * sizeof(long long), cudaMemcpyDeviceToHost);
+  cudaMemset(be->prof, 0, 32 * sizeof(long long));
+  return EK_OK;
+}
+#endif
 
 int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl) {
   if (!be || impl < 0 || impl > 1) return EK_INVALID_INPUT;

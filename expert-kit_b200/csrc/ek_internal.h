@@ -132,6 +132,7 @@ struct FfnParams {
   const CUtensorMap* h_maps;   // device array[4]
   int32_t n_sm;
   int32_t precise;           // fp8: apply block scales in fp32 (bit-exact reference dequantisation)
+  long long* prof;           // cycle counters of a -DEK_TC_PROFILE build, else unused
 };
 // Straightforward CUDA-core evaluation of the same tiled weights; used by the tests as an
 // independent check of the tensor-core path at sizes the CPU oracle cannot reach.

@@ -34,7 +34,8 @@ namespace {
 using namespace ekptx;
 
 constexpr int kConvWarps = 8;
-constexpr int kThreads = (kConvWarps + 2) * 32;
+constexpr int kMmaWarps = 2;
+constexpr int kThreads = (kConvWarps + 1 + kMmaWarps) * 32;
 constexpr int kASlots = 4;       // A-operand staging slots in tensor memory
 constexpr int kASlotCols = 64;   // columns per slot (128 bf16 along K)
 constexpr int kABaseCol = 256;   // accumulators live in columns [0, 256)
@@ -57,6 +58,18 @@ struct Cfg {
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
 };
+
+// Optional per-role cycle accounting (build with -DEK_TC_PROFILE): where each role's time goes.
+#ifdef EK_TC_PROFILE
+#define PROF_DECL long long pt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pc_ = clock64();
+#define PROF_LAP(i) { long long n_ = clock64(); pt_[i] += n_ - pc_; pc_ = n_; }
+#define PROF_DUMP(role) \
+  if (p.prof) for (int i_ = 0; i_ < 8; ++i_) atomicAdd((unsigned long long*)&p.prof[(role) * 8 + i_], (unsigned long long)pt_[i_]);
+#else
+#define PROF_DECL
+#define PROF_LAP(i)
+#define PROF_DUMP(role)
+#endif
 
 __device__ __forceinline__ void report(DevStatus* st, int code, int where, int a0, int a1) {
   if (atomicCAS(&st->code, DEV_OK, code) == DEV_OK) {
@@ -149,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   using C = Cfg<QUANT, GATEUP, NMAX>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_afull[kASlots], bar_aempty[kASlots];
-  __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain;
+  __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
 
@@ -161,15 +174,15 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     s_abort = 0;
     for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(smem_u32(&bar_full[i]), 1);
-      mbar_init(smem_u32(&bar_empty[i]), kConvWarps + 1);
+      mbar_init(smem_u32(&bar_empty[i]), kConvWarps + (GATEUP ? 2 : 1));
     }
     for (int i = 0; i < kASlots; ++i) {
       mbar_init(smem_u32(&bar_afull[i]), GATEUP ? 4 : 8);
       mbar_init(smem_u32(&bar_aempty[i]), 1);
     }
-    mbar_init(smem_u32(&bar_accfull), 1);
+    mbar_init(smem_u32(&bar_accfull), kMmaWarps);
     mbar_init(smem_u32(&bar_accempty), kConvWarps);
-    mbar_init(smem_u32(&bar_drain), 1);
+    for (int i = 0; i < kMmaWarps; ++i) mbar_init(smem_u32(&bar_drain[i]), 1);
     mbar_init_fence();
   }
   if (warp == kConvWarps + 1) {
@@ -193,6 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       const uint64_t stream_once = policy_evict_first();   // weights are read exactly once per pass
       uint32_t it = 0;
       bool ok = true;
+      PROF_DECL
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
         const ChunkDesc cd = p.chunks[item / n_rt];
         const int rt = item % n_rt;
@@ -209,6 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
             ok = false;
             break;
           }
+          PROF_LAP(0)
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
           mbar_arrive_expect_tx(full, C::W_BYTES + N * C::TKE * 2);
@@ -216,8 +231,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
 #pragma unroll
           for (int a = 0; a < C::TKE / 64; ++a)
             tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
+          PROF_LAP(1)
         }
       }
+      PROF_DUMP(0)
       // never leave with copies in flight: wait (bounded) for every stage armed in the last lap
       const uint32_t lo = it > (uint32_t)C::STAGES ? it - C::STAGES : 0;
       for (uint32_t i = lo; i < it; ++i) {
@@ -228,57 +245,70 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
       }
     }
-  } else if (warp == kConvWarps + 1) {
-    // =============================== MMA issuer ============================================
+  } else if (warp > kConvWarps) {
+    // =============================== MMA issuers ===========================================
+    // Two issuing threads in two warps ("chains"), each with its own accumulator: one thread's
+    // instruction stream between MMAs (barrier polls, commits) costs about as much as the MMAs
+    // themselves take, so a single issuer leaves the tensor pipe idle half of the time.
+    //   gate/up : chain 0 issues the gate tile, chain 1 the up tile of every K step
+    //   down    : chain c issues the K steps with kt % 2 == c; the epilogue adds both accumulators
     if (lane == 0) {
-      uint32_t it = 0, items_done = 0;
+      const uint32_t chain = warp - (kConvWarps + 1);
+      uint32_t it = 0, items_done = 0, s = 0, ph = 0;
       bool ok = true;
+      PROF_DECL
+      const uint32_t d_tmem = tmem + chain * NMAX;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
         const ChunkDesc cd = p.chunks[item / n_rt];
         const int N = pick_n(cd.n_rows, NMAX);
         const uint32_t idesc = umma_idesc_bf16(N);
+        const uint32_t atom_step = (uint32_t)(N * 128) >> 4;   // descriptor units between 64-element K atoms
         if (!mbar_wait(smem_u32(&bar_accempty), (items_done & 1u) ^ 1u, abortp)) {
           report(p.status, DEV_TIMEOUT, 200, item, 0);
           ok = false;
           break;
         }
         tc_fence_after();
-        for (int kt = 0; kt < KT && ok; ++kt, ++it) {
-          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
+        PROF_LAP(0)
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const uint32_t cs = s, cph = ph;
+          if (++s == (uint32_t)C::STAGES) { s = 0; ph ^= 1u; }
+          if (!GATEUP && (uint32_t)(kt & 1) != chain) continue;
+          if (!mbar_wait(smem_u32(&bar_full[cs]), cph, abortp)) {
             report(p.status, DEV_TIMEOUT, 201, item, kt);
             ok = false;
             break;
           }
-          const uint32_t xbase = stage0 + s * C::STAGE_BYTES + C::W_BYTES;
+          // B descriptors of this stage's activation tile: one per 16-element K step
+          const uint64_t b0 = umma_desc_sw128(stage0 + cs * C::STAGE_BYTES + C::W_BYTES);
+          uint64_t bd[C::MMAS];
 #pragma unroll
-          for (int q = 0; q < C::NT; ++q) {
-            const uint32_t tcount = it * C::NT + q;
-            const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
-            if (!mbar_wait(smem_u32(&bar_afull[a]), aph, abortp)) {
-              report(p.status, DEV_TIMEOUT, 202, item, kt);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t d_tmem = tmem + q * NMAX;
-            const uint32_t a_tmem = tmem + kABaseCol + a * kASlotCols;
-#pragma unroll
-            for (int j = 0; j < C::MMAS; ++j) {
-              const uint64_t bdesc = umma_desc_sw128(xbase + (j / 4) * N * 128 + (j % 4) * 32);
-              umma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (kt > 0 || j > 0) ? 1u : 0u);
-            }
-            tc_commit(smem_u32(&bar_aempty[a]));
+          for (int j = 0; j < C::MMAS; ++j) bd[j] = b0 + (uint64_t)((j / 4) * atom_step + (j % 4) * 2);
+          PROF_LAP(1)
+          const uint32_t tcount = GATEUP ? it * 2 + chain : it;
+          const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
+          if (!mbar_wait(smem_u32(&bar_afull[a]), aph, abortp)) {
+            report(p.status, DEV_TIMEOUT, 202, item, kt);
+            ok = false;
+            break;
           }
-          if (!ok) break;
-          tc_commit(smem_u32(&bar_empty[s]));
+          tc_fence_after();
+          PROF_LAP(2)
+          const uint32_t a_tmem = tmem + kABaseCol + a * kASlotCols;
+          const uint32_t acc = GATEUP ? (kt > 0 ? 1u : 0u) : ((uint32_t)kt > chain ? 1u : 0u);
+          if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, acc);
+          else umma_ts_x4(d_tmem, a_tmem, bd, idesc, acc);
+          tc_commit(smem_u32(&bar_aempty[a]));
+          tc_commit(smem_u32(&bar_empty[cs]));
+          PROF_LAP(3)
         }
         if (ok) tc_commit(smem_u32(&bar_accfull));
       }
+      if (chain == 0) { PROF_DUMP(1) }
       // drain: every MMA issued by this thread has completed before tensor memory is freed
-      tc_commit(smem_u32(&bar_drain));
+      tc_commit(smem_u32(&bar_drain[chain]));
       for (uint32_t poll = 0; poll < (1u << 20); ++poll) {
-        if (mbar_try_wait(smem_u32(&bar_drain), 0)) break;
+        if (mbar_try_wait(smem_u32(&bar_drain[chain]), 0)) break;
         __nanosleep(64);
       }
     }
@@ -289,6 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
     uint32_t it = 0, items_done = 0;
     bool ok = true;
+    PROF_DECL
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
       const ChunkDesc cd = p.chunks[item / n_rt];
       const int rt = item % n_rt;
@@ -309,6 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           ok = false;
           break;
         }
+        PROF_LAP(0)
         const uint32_t tcount = GATEUP ? it * 2 + wg : it;
         const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
         if (!mbar_wait(smem_u32(&bar_aempty[a]), aph ^ 1u, abortp)) {
@@ -316,6 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           ok = false;
           break;
         }
+        PROF_LAP(1)
         const uint8_t* tile = smem_raw + (stage0 - smem_u32(smem_raw)) + s * C::STAGE_BYTES +
                               (GATEUP ? wg * kTileBytes : 0);
         const int ch0 = GATEUP ? 0 : wg * 4;
@@ -343,6 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         } else {
           tmem_st16(lane_base + col0, aw);
         }
+        PROF_LAP(2)
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -350,6 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           mbar_arrive(smem_u32(&bar_afull[a]));
           mbar_arrive(smem_u32(&bar_empty[s]));
         }
+        PROF_LAP(3)
       }
       if (!ok) break;
       // ---- epilogue ----
@@ -359,12 +394,13 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         break;
       }
       tc_fence_after();
+      PROF_LAP(4)
       const int feat = rt * kTileRows + r;
       for (int cb = wg; cb < N / 8; cb += 2) {
         if (cb * 8 >= cd.n_rows) break;
         uint32_t g[8], u[8];
         tmem_ld8(lane_base + cb * 8, g);
-        if (GATEUP) tmem_ld8(lane_base + NMAX + cb * 8, u);
+        if (GATEUP || KT > 1) tmem_ld8(lane_base + NMAX + cb * 8, u);   // second chain's accumulator
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -376,7 +412,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
               const float h = uv * (gv / (1.f + __expf(-gv)));
               p.hbuf[(size_t)(cd.out_row + col) * p.d.Ip + feat] = __float2bfloat16_rn(h);
             } else if (feat < p.d.H) {
-              p.obuf[(size_t)(cd.out_row + col) * p.d.H + feat] = __float2bfloat16_rn(gv);
+              const float v = KT > 1 ? gv + __uint_as_float(u[i]) : gv;
+              p.obuf[(size_t)(cd.out_row + col) * p.d.H + feat] = __float2bfloat16_rn(v);
             }
           }
         }
@@ -384,7 +421,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_accempty));
+      PROF_LAP(5)
     }
+    if (lane == 0 && (warp == 0 || warp == 4)) { PROF_DUMP(2 + wg) }
   }
 
   tc_fence_before();

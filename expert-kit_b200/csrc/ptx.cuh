@@ -210,6 +210,44 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
+// The MMAs of one weight tile in a single statement: the issuing thread's instruction stream is
+// latency-bound (one thread, no other warps to hide behind on its scheduler slot), so the
+// predicate set-up is shared and descriptors arrive precomputed.  D (+)= A[tmem + 8j] * B[desc_j];
+// only the first product may overwrite D (`accumulate_first` = 0).
+__device__ __forceinline__ void umma_ts_x8(uint32_t d, uint32_t a, const uint64_t* b, uint32_t idesc,
+                                           uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %19, 0;\n\t"
+      "setp.ne.b32 p1, %18, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %9, %18, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %10, %18, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %11, %18, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %18, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %18, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %18, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %18, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %18, p1;\n\t}" ::"r"(d),
+      "r"(a), "r"(a + 8), "r"(a + 16), "r"(a + 24), "r"(a + 32), "r"(a + 40), "r"(a + 48), "r"(a + 56),
+      "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]),
+      "r"(0), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_x4(uint32_t d, uint32_t a, const uint64_t* b, uint32_t idesc,
+                                           uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %10, 0;\n\t"
+      "setp.ne.b32 p1, %9, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %5, %9, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %6, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %7, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %9, p1;\n\t}" ::"r"(d),
+      "r"(a), "r"(a + 8), "r"(a + 16), "r"(a + 24), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc),
+      "r"(accumulate_first)
+      : "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

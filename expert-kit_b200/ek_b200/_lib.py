@@ -8,7 +8,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libek_b200.so")
+LIB_PATH = os.environ.get("EK_B200_LIB") or os.path.join(os.path.dirname(_HERE), "lib", "libek_b200.so")
 
 EK_OK = 0
 STATUS_NAMES = {
