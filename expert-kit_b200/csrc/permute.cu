@@ -4,6 +4,10 @@
 //
 // Semantics follow NaiveExecutor::break_down_to_egress / assemble_seq_tensors
 // (ek-computation/src/controller/executor.rs:283-299,112-133): a stable counting sort.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
 #include "ek_internal.h"
 
 namespace ek {
@@ -205,3 +209,103 @@ int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_
 }
 
 }  // namespace ek
+
+// =============================================================================================
+// Bucketing for callers that may not allocate device memory.
+//
+// Some hosts of this library are not allowed to call cudaMalloc at all: a worker whose device
+// memory is carved up front by its own pool and handed out by offset, or a plugin that runs
+// inside another runtime's step function where an allocation would synchronise the device or
+// break that runtime's memory accounting.  For them the bucketing step is offered in a form
+// that owns no handle and allocates nothing: its scratch (the inverse map the ranking kernel
+// writes, and the device status word) lives in a file-scope array that every GPU loading this
+// library holds until the process exits.
+//
+// Host code cannot use the array's name as a device address; its address is looked up once per
+// device with cudaGetSymbolAddress while that device is current.  The first call on a device
+// performs this look-up, so make that first call outside any stream capture.
+// All calls share the one array: two calls whose kernels overlap on the same GPU race on it.
+// =============================================================================================
+namespace {
+
+constexpr int kNoAllocMaxAssignments = EK_NOALLOC_MAX_ASSIGNMENTS;
+constexpr int kNoAllocStatusOffset = kNoAllocMaxAssignments * (int)sizeof(int32_t);
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_bucket_scratch[kNoAllocStatusOffset + 256];
+
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+void noalloc_msg(char* buf, size_t cap, const char* fmt, ...) {
+  if (!buf || cap == 0) return;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, cap, fmt, ap);
+  va_end(ap);
+}
+
+}  // namespace
+
+extern "C" int32_t ek_bucket_noalloc(const int32_t* ids_dev, int32_t T, int32_t k, int32_t n_experts,
+                                     int32_t* counts_dev, int32_t* offsets_dev, int32_t* perm_dev,
+                                     void* cuda_stream, char* errbuf, size_t errcap) {
+  using namespace ek;
+  if (!ids_dev || !counts_dev || !offsets_dev || !perm_dev) {
+    noalloc_msg(errbuf, errcap, "null pointer argument");
+    return EK_INVALID_INPUT;
+  }
+  if (T < 1 || k < 1 || n_experts < 1 || n_experts > 1024) {
+    noalloc_msg(errbuf, errcap, "T, k must be positive and n_experts in [1,1024]");
+    return EK_INVALID_INPUT;
+  }
+  if ((int64_t)T * k > kNoAllocMaxAssignments) {
+    noalloc_msg(errbuf, errcap, "T*k = %lld exceeds the built-in scratch of %d assignments",
+                (long long)T * k, kNoAllocMaxAssignments);
+    return EK_INVALID_INPUT;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    noalloc_msg(errbuf, errcap, "no current CUDA device");
+    return EK_CUDA;
+  }
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      // once per device, with that device current
+      cudaError_t e = cudaGetSymbolAddress(&g_noalloc_ptr[dev], g_bucket_scratch);
+      if (e != cudaSuccess) {
+        g_noalloc_ptr[dev] = nullptr;
+        noalloc_msg(errbuf, errcap, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return EK_CUDA;
+      }
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  int32_t* inv = reinterpret_cast<int32_t*>(scratch);
+  DevStatus* st = reinterpret_cast<DevStatus*>(reinterpret_cast<unsigned char*>(scratch) + kNoAllocStatusOffset);
+  // the array keeps the previous call's contents: the status word must start at zero
+  cudaError_t e = cudaMemsetAsync(st, 0, sizeof(DevStatus), s);
+  if (e == cudaSuccess) {
+    launch_histogram(ids_dev, T * k, n_experts, counts_dev, st, s);   // zeroes counts itself
+    PermuteParams pp;
+    pp.ids = ids_dev; pp.counts = counts_dev; pp.offsets = offsets_dev; pp.perm = perm_dev; pp.inv = inv;
+    pp.T = T; pp.k = k; pp.E = n_experts; pp.e_lo = 0; pp.e_hi = n_experts;
+    launch_permute(pp, s);
+    e = cudaGetLastError();
+  }
+  DevStatus host_st = {0, 0, 0, 0};
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&host_st, st, sizeof host_st, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    noalloc_msg(errbuf, errcap, "CUDA failure: %s", cudaGetErrorString(e));
+    return EK_CUDA;
+  }
+  if (host_st.code != DEV_OK) {
+    noalloc_msg(errbuf, errcap, "assignment %d names expert %d, outside [0,%d)", host_st.aux0, host_st.aux1, n_experts);
+    return EK_BOUNDS;
+  }
+  return EK_OK;
+}

@@ -239,6 +239,25 @@ int32_t ek_moe_forward_fused_async(ek_backend_t* be, int32_t layer, const void* 
                                    void* y_dev);
 int32_t ek_sync(ek_backend_t* be);
 
+/* ---- allocation-free bucketing ------------------------------------------------------------
+ * No counterpart in the reference.  Some callers are not allowed to allocate device memory (a
+ * worker whose memory is one pre-carved pool, a plugin running inside another runtime's step);
+ * this entry point needs no backend handle and calls no allocator: it buckets caller-supplied
+ * assignments with the library's own kernels, using a scratch array that is built into the
+ * library image (EK_NOALLOC_MAX_ASSIGNMENTS ints plus a status word per GPU, held until exit).
+ *
+ *   ids_dev[T*k] (device, values in [0,n_experts))  ->  counts_dev[n_experts],
+ *   offsets_dev[n_experts+1], perm_dev[T*k]  (device), same definition as ek_route_debug_t.
+ *
+ * Runs on `cuda_stream` of the CURRENT device and returns after it has completed.  T*k beyond
+ * EK_NOALLOC_MAX_ASSIGNMENTS is refused with EK_INVALID_INPUT; `errbuf` (may be NULL) receives a
+ * message.  The first call on a device resolves the scratch address: make it before any stream
+ * capture.  Calls share the scratch: do not overlap two of them on one GPU. */
+#define EK_NOALLOC_MAX_ASSIGNMENTS 65536
+int32_t ek_bucket_noalloc(const int32_t* ids_dev, int32_t T, int32_t k, int32_t n_experts,
+                          int32_t* counts_dev, int32_t* offsets_dev, int32_t* perm_dev,
+                          void* cuda_stream, char* errbuf, size_t errcap);
+
 #ifdef __cplusplus
 }
 #endif
