@@ -208,12 +208,12 @@ int ensure_layer(ek_backend* be, int layer, Layer** out) {
   Layer L;
   const Dims& d = be->d;
   const size_t gu_bytes = (size_t)be->n_slots * d.it * d.kt_gu * 2 * kTileBytes;
-  const size_t dn_bytes = (size_t)be->n_slots * d.ht * d.kt_dn * kTileBytes;
+  const size_t dn_bytes = (size_t)be->n_slots * d.hp * d.kt_dn * 2 * kTileBytes;
   CK(cudaMalloc(&L.gu, gu_bytes));
   CK(cudaMalloc(&L.dn, dn_bytes));
   if (d.quant != EK_QUANT_BF16) {
     CK(cudaMalloc(&L.gu_scale, (size_t)be->n_slots * d.it * d.kt_gu * 2 * sizeof(float)));
-    CK(cudaMalloc(&L.dn_scale, (size_t)be->n_slots * d.ht * d.kt_dn * sizeof(float)));
+    CK(cudaMalloc(&L.dn_scale, (size_t)be->n_slots * d.hp * d.kt_dn * 2 * sizeof(float)));
   }
   CK(cudaMalloc(&L.registered, sizeof(int32_t) * be->n_slots));
   CK(cudaMemset(L.registered, 0, sizeof(int32_t) * be->n_slots));
@@ -495,7 +495,7 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   d.Hp = round_up(c.hidden, 128); d.Ip = round_up(c.intermediate, 128);
   d.quant = c.quant;
   const int tk = tile_k_elems(c.quant);
-  d.kt_gu = d.Hp / tk; d.kt_dn = d.Ip / tk; d.it = d.Ip / 128; d.ht = d.Hp / 128;
+  d.kt_gu = d.Hp / tk; d.kt_dn = d.Ip / tk; d.it = d.Ip / 128; d.ht = d.Hp / 128; d.hp = (d.ht + 1) / 2;
   be->n_local = c.n_experts / c.ep_size;
   be->e_lo = c.ep_rank * be->n_local;
   be->e_hi = be->e_lo + be->n_local;
@@ -736,7 +736,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
   for (int v = 0; v < n_virtual; ++v) {
     const int slot = shared ? be->n_local + v : expert - be->e_lo;
     uint8_t* gu0 = L->gu + (size_t)slot * d.it * d.kt_gu * 2 * kTileBytes;
-    uint8_t* dn0 = L->dn + (size_t)slot * d.ht * d.kt_dn * kTileBytes;
+    uint8_t* dn0 = L->dn + (size_t)slot * d.hp * d.kt_dn * 2 * kTileBytes;
     for (int m = 0; m < 2; ++m) {   // 0 gate, 1 up
       RetileParams rp;
       rp.src = src[m]; rp.rows = I_e; rp.cols = c.hidden;
@@ -747,6 +747,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
       rp.dst = gu0 + (size_t)m * kTileBytes;
       rp.rt_stride = (int64_t)d.kt_gu * 2 * kTileBytes;
       rp.kt_stride = 2 * kTileBytes;
+      rp.rt_pairs = 0;
       rp.n_rt = d.it; rp.n_kt = d.kt_gu;
       be->launches += launch_retile(rp, ls);
       if (c.quant != EK_QUANT_BF16) {
@@ -755,7 +756,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
         sp.rb0 = v * c.intermediate / 128; sp.kb0 = 0;
         sp.n_rt = d.it; sp.n_kt = d.kt_gu;
         sp.dst = L->gu_scale + (size_t)slot * d.it * d.kt_gu * 2;
-        sp.stride = 2; sp.lane = m;
+        sp.stride = 2; sp.lane = m; sp.rt_pairs = 0;
         be->launches += launch_scale_retile(sp, ls);
       }
     }
@@ -766,17 +767,17 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     rp.esz = esz;
     rp.pair_interleave = c.quant == EK_QUANT_FP8_BLOCK128;
     rp.dst = dn0;
-    rp.rt_stride = (int64_t)d.kt_dn * kTileBytes;
-    rp.kt_stride = kTileBytes;
-    rp.n_rt = d.ht; rp.n_kt = d.kt_dn;
+    rp.rt_stride = 0; rp.kt_stride = 0;
+    rp.rt_pairs = 1;                       // row tiles 2j, 2j+1 adjacent per K tile; an odd tail is zero-filled
+    rp.n_rt = 2 * d.hp; rp.n_kt = d.kt_dn;
     be->launches += launch_retile(rp, ls);
     if (c.quant != EK_QUANT_BF16) {
       ScaleRetileParams sp;
       sp.src = ssrc[2]; sp.src_cols = (int)sc[2]->shape[1]; sp.src_rows = (int)sc[2]->shape[0];
       sp.rb0 = 0; sp.kb0 = v * c.intermediate / 128;
-      sp.n_rt = d.ht; sp.n_kt = d.kt_dn;
-      sp.dst = L->dn_scale + (size_t)slot * d.ht * d.kt_dn;
-      sp.stride = 1; sp.lane = 0;
+      sp.n_rt = 2 * d.hp; sp.n_kt = d.kt_dn;
+      sp.dst = L->dn_scale + (size_t)slot * d.hp * d.kt_dn * 2;
+      sp.stride = 1; sp.lane = 0; sp.rt_pairs = 1;
       be->launches += launch_scale_retile(sp, ls);
     }
     const int32_t one = 1;

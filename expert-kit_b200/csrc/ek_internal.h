@@ -45,9 +45,9 @@ enum { DEV_OK = 0, DEV_TIMEOUT = 1, DEV_MISSING_EXPERT = 2, DEV_BOUNDS = 3 };
 // Layer slab (device pointers).
 struct LayerWeights {
   const uint8_t* gu_tiles;   // [slot][it][kt][gate|up][16 KiB]
-  const uint8_t* dn_tiles;   // [slot][ht][kt][16 KiB]
+  const uint8_t* dn_tiles;   // [slot][hp][kt][row tile 2hp | 2hp+1][16 KiB]
   const float* gu_scale;     // [slot][it][kt][2]   (quantised only; K tile == 128-wide scale block)
-  const float* dn_scale;     // [slot][ht][kt]
+  const float* dn_scale;     // [slot][hp][kt][2]
   const int32_t* registered; // [slots] 1 when the slot holds weights
   int32_t n_slots;
 };
@@ -60,6 +60,7 @@ struct Dims {
   int32_t kt_dn;         // K tiles of the down GEMM     = Ip / tile_k
   int32_t it;            // row tiles of gate/up         = Ip / 128
   int32_t ht;            // row tiles of down            = Hp / 128
+  int32_t hp;            // row-tile pairs of down       = ceil(ht / 2)
 };
 
 // ---- kernel launchers (each returns the number of kernels it launched) ---------------------
@@ -163,6 +164,8 @@ struct RetileParams {
   int32_t col0, n_cols;   // source column window
   int32_t esz;            // 1 or 2
   int32_t pair_interleave;  // fp8: store K-consecutive pairs in the form the GEMM decodes cheaply
+  int32_t rt_pairs;         // 1: row tiles 2j and 2j+1 are stored next to each other per K tile:
+                            //    tile(rt,kt) at dst + (((rt>>1)*n_kt + kt)*2 + (rt&1)) * 16 KiB
   uint8_t* dst;           // first tile of (row tile 0, k tile 0)
   int64_t rt_stride;      // bytes between consecutive row tiles
   int64_t kt_stride;      // bytes between consecutive K tiles
@@ -177,6 +180,7 @@ struct ScaleRetileParams {
   float* dst;             // dst[(rt*n_kt + kt)*stride + lane]
   int32_t stride, lane;
   int32_t src_rows;
+  int32_t rt_pairs;       // 1: dst[(((rt>>1)*n_kt + kt)*2 + (rt&1))]
 };
 int launch_scale_retile(const ScaleRetileParams& p, cudaStream_t s);
 int launch_fill_f32(float* dst, float v, int64_t n, cudaStream_t s);

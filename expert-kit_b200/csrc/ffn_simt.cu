@@ -115,7 +115,8 @@ __global__ void __launch_bounds__(128) simt_down_kernel(FfnParams p) {
   float acc[kRows];
 #pragma unroll
   for (int t = 0; t < kRows; ++t) acc[t] = 0.f;
-  const size_t tile0 = ((size_t)cd.slot * p.d.ht + ht) * p.d.kt_dn;
+  // tile (ht, kt) of the pair-interleaved down layout
+  const size_t tile0 = ((size_t)cd.slot * p.d.hp + (ht >> 1)) * p.d.kt_dn * 2 + (ht & 1);
   for (int kt = 0; kt < p.d.kt_dn; ++kt) {
     __syncthreads();
     for (int i = threadIdx.x; i < kRows * TK; i += blockDim.x) {
@@ -125,9 +126,9 @@ __global__ void __launch_bounds__(128) simt_down_kernel(FfnParams p) {
       xs[t][i % TK] = v;
     }
     __syncthreads();
-    const uint8_t* tw = p.w.dn_tiles + (tile0 + kt) * kTileBytes;
+    const uint8_t* tw = p.w.dn_tiles + (tile0 + (size_t)kt * 2) * kTileBytes;
     float s = 1.f;
-    if (QUANT != EK_QUANT_BF16) s = p.w.dn_scale[tile0 + kt];
+    if (QUANT != EK_QUANT_BF16) s = p.w.dn_scale[tile0 + (size_t)kt * 2];
     row_times_x<QUANT>(tw, r, s, xs, acc);
   }
   const int hcol = ht * kTileRows + r;

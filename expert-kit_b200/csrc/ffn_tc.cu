@@ -45,19 +45,25 @@ constexpr int kSmemLimit = 232448 - 4096;
 template <int QUANT, bool GATEUP, int NMAX>
 struct Cfg {
   static constexpr int TKE = QUANT == EK_QUANT_BF16 ? 64 : 128;   // K elements per tile
-  static constexpr int NT = GATEUP ? 2 : 1;                       // weight tiles per stage
-  static constexpr int W_BYTES = NT * kTileBytes;
-  static constexpr int X_BYTES = NMAX * TKE * 2;
+  // A stage holds two weight tiles of the same K step, one per converter warpgroup / MMA chain,
+  // and the one activation tile both multiply:
+  //   gate/up : the gate and the up tile of intermediate-row tile rt
+  //   down    : the tiles of hidden-row tiles 2*rp and 2*rp+1
+  static constexpr int W_BYTES = 2 * kTileBytes;
+  static constexpr int X_ATOMS = TKE / 64;                        // 64-element swizzle atoms along K
+  static constexpr int X_BYTES = NMAX * X_ATOMS * 128;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
   static constexpr int STAGES_RAW = kSmemLimit / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int MMAS = TKE / 16;                           // MMA instructions per tile
-  static constexpr int NCH = GATEUP ? 8 : 4;                      // 16-byte chunks per thread
+  static constexpr int NCH = 8;                                   // 16-byte chunks per thread (one tile row)
   static constexpr int WPC = QUANT == EK_QUANT_BF16 ? 4 : 8;      // 32-bit A words per chunk
   static constexpr int NW = NCH * WPC;
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
 };
+
+
 
 // Optional per-role cycle accounting (build with -DEK_TC_PROFILE): where each role's time goes.
 #ifdef EK_TC_PROFILE
@@ -174,10 +180,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     s_abort = 0;
     for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(smem_u32(&bar_full[i]), 1);
-      mbar_init(smem_u32(&bar_empty[i]), kConvWarps + (GATEUP ? 2 : 1));
+      mbar_init(smem_u32(&bar_empty[i]), kConvWarps + kMmaWarps);
     }
     for (int i = 0; i < kASlots; ++i) {
-      mbar_init(smem_u32(&bar_afull[i]), GATEUP ? 4 : 8);
+      mbar_init(smem_u32(&bar_afull[i]), 4);
       mbar_init(smem_u32(&bar_aempty[i]), 1);
     }
     mbar_init(smem_u32(&bar_accfull), kMmaWarps);
@@ -195,8 +201,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   const uint32_t tmem = s_tmem;
 
   const int n_chunks = *p.n_chunks;
-  const int n_rt = GATEUP ? p.d.it : p.d.ht;
-  const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;
+  const int n_rt = GATEUP ? p.d.it : p.d.hp;   // work items per chunk
+  const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;   // K tiles of the GEMM = pipeline stages per work item
   const int total = n_chunks * n_rt;
 
   if (warp == kConvWarps) {
@@ -214,7 +220,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         const CUtensorMap* map = maps + map_index(N);
         const uint8_t* wsrc =
             GATEUP ? p.w.gu_tiles + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * C::W_BYTES
-                   : p.w.dn_tiles + ((size_t)cd.slot * p.d.ht + rt) * (size_t)p.d.kt_dn * C::W_BYTES;
+                   : p.w.dn_tiles + ((size_t)cd.slot * p.d.hp + rt) * (size_t)p.d.kt_dn * C::W_BYTES;
         const int brow = GATEUP ? cd.in_row : cd.out_row;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
@@ -226,10 +232,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           PROF_LAP(0)
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
-          mbar_arrive_expect_tx(full, C::W_BYTES + N * C::TKE * 2);
+          mbar_arrive_expect_tx(full, C::W_BYTES + C::X_ATOMS * N * 128);
           bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
 #pragma unroll
-          for (int a = 0; a < C::TKE / 64; ++a)
+          for (int a = 0; a < C::X_ATOMS; ++a)
             tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
           PROF_LAP(1)
         }
@@ -251,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     // instruction stream between MMAs (barrier polls, commits) costs about as much as the MMAs
     // themselves take, so a single issuer leaves the tensor pipe idle half of the time.
     //   gate/up : chain 0 issues the gate tile, chain 1 the up tile of every K step
-    //   down    : chain c issues the K steps with kt % 2 == c; the epilogue adds both accumulators
+    //   down    : chain c issues hidden-row tile 2*rp + c
     if (lane == 0) {
       const uint32_t chain = warp - (kConvWarps + 1);
       uint32_t it = 0, items_done = 0, s = 0, ph = 0;
@@ -273,19 +279,18 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const uint32_t cs = s, cph = ph;
           if (++s == (uint32_t)C::STAGES) { s = 0; ph ^= 1u; }
-          if (!GATEUP && (uint32_t)(kt & 1) != chain) continue;
           if (!mbar_wait(smem_u32(&bar_full[cs]), cph, abortp)) {
             report(p.status, DEV_TIMEOUT, 201, item, kt);
             ok = false;
             break;
           }
-          // B descriptors of this stage's activation tile: one per 16-element K step
+          // B descriptors of the stage's activation tile: one per 16-element K step
           const uint64_t b0 = umma_desc_sw128(stage0 + cs * C::STAGE_BYTES + C::W_BYTES);
           uint64_t bd[C::MMAS];
 #pragma unroll
           for (int j = 0; j < C::MMAS; ++j) bd[j] = b0 + (uint64_t)((j / 4) * atom_step + (j % 4) * 2);
           PROF_LAP(1)
-          const uint32_t tcount = GATEUP ? it * 2 + chain : it;
+          const uint32_t tcount = it * 2 + chain;
           const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
           if (!mbar_wait(smem_u32(&bar_afull[a]), aph, abortp)) {
             report(p.status, DEV_TIMEOUT, 202, item, kt);
@@ -295,9 +300,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           tc_fence_after();
           PROF_LAP(2)
           const uint32_t a_tmem = tmem + kABaseCol + a * kASlotCols;
-          const uint32_t acc = GATEUP ? (kt > 0 ? 1u : 0u) : ((uint32_t)kt > chain ? 1u : 0u);
-          if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, acc);
-          else umma_ts_x4(d_tmem, a_tmem, bd, idesc, acc);
+          if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
+          else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           tc_commit(smem_u32(&bar_aempty[a]));
           tc_commit(smem_u32(&bar_empty[cs]));
           PROF_LAP(3)
@@ -324,16 +328,17 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       const ChunkDesc cd = p.chunks[item / n_rt];
       const int rt = item % n_rt;
       const int N = pick_n(cd.n_rows, NMAX);
+      // block scale of this warpgroup's tile: [K step][warpgroup] in both modes
       const float* sc = nullptr;
       if (QUANT != EK_QUANT_BF16) {
         sc = GATEUP ? p.w.gu_scale + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * 2 + wg
-                    : p.w.dn_scale + ((size_t)cd.slot * p.d.ht + rt) * (size_t)p.d.kt_dn;
+                    : p.w.dn_scale + ((size_t)cd.slot * p.d.hp + rt) * (size_t)p.d.kt_dn * 2 + wg;
       }
       float scale_next = 1.f;
       if (QUANT != EK_QUANT_BF16) scale_next = __ldg(sc);
       for (int kt = 0; kt < KT; ++kt, ++it) {
         const float scale = scale_next;
-        if (QUANT != EK_QUANT_BF16 && kt + 1 < KT) scale_next = __ldg(sc + (size_t)(kt + 1) * (GATEUP ? 2 : 1));
+        if (QUANT != EK_QUANT_BF16 && kt + 1 < KT) scale_next = __ldg(sc + (size_t)(kt + 1) * 2);
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
         if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
           report(p.status, DEV_TIMEOUT, 300, item, kt);
@@ -341,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           break;
         }
         PROF_LAP(0)
-        const uint32_t tcount = GATEUP ? it * 2 + wg : it;
+        const uint32_t tcount = it * 2 + wg;
         const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
         if (!mbar_wait(smem_u32(&bar_aempty[a]), aph ^ 1u, abortp)) {
           report(p.status, DEV_TIMEOUT, 301, item, kt);
@@ -349,13 +354,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           break;
         }
         PROF_LAP(1)
-        const uint8_t* tile = smem_raw + (stage0 - smem_u32(smem_raw)) + s * C::STAGE_BYTES +
-                              (GATEUP ? wg * kTileBytes : 0);
-        const int ch0 = GATEUP ? 0 : wg * 4;
+        const uint8_t* tile = smem_raw + (stage0 - smem_u32(smem_raw)) + s * C::STAGE_BYTES + wg * kTileBytes;
         uint4 raw[C::NCH];
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j)
-          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)((ch0 + j) * kTileRows + r) * 16);
+          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)(j * kTileRows + r) * 16);
         uint32_t aw[C::NW];
         uint32_t s_hi = 0, s_lo = 0;
         if (QUANT == EK_QUANT_FP8_BLOCK128 && !PRECISE) {
@@ -368,14 +371,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT, PRECISE>(raw[j], scale, s_hi, s_lo, aw + j * C::WPC);
-        const uint32_t col0 = kABaseCol + a * kASlotCols + (GATEUP ? 0 : wg * (C::NW));
+        const uint32_t col0 = kABaseCol + a * kASlotCols;
         tc_fence_after();
-        if (C::NW >= 32) {
 #pragma unroll
-          for (int w0 = 0; w0 < C::NW; w0 += 32) tmem_st32(lane_base + col0 + w0, aw + w0);
-        } else {
-          tmem_st16(lane_base + col0, aw);
-        }
+        for (int w0 = 0; w0 < C::NW; w0 += 32) tmem_st32(lane_base + col0 + w0, aw + w0);
         PROF_LAP(2)
         tc_wait_st();
         tc_fence_before();
@@ -395,25 +394,27 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       }
       tc_fence_after();
       PROF_LAP(4)
-      const int feat = rt * kTileRows + r;
+      // gate/up: this thread owns intermediate feature rt*128 + r (gate in accumulator 0, up in 1);
+      // down: hidden features (2*rt)*128 + r (accumulator 0) and (2*rt+1)*128 + r (accumulator 1)
+      const int feat = (GATEUP ? rt : 2 * rt) * kTileRows + r;
       for (int cb = wg; cb < N / 8; cb += 2) {
         if (cb * 8 >= cd.n_rows) break;
         uint32_t g[8], u[8];
         tmem_ld8(lane_base + cb * 8, g);
-        if (GATEUP || KT > 1) tmem_ld8(lane_base + NMAX + cb * 8, u);   // second chain's accumulator
+        tmem_ld8(lane_base + NMAX + cb * 8, u);
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int col = cb * 8 + i;
           if (col < cd.n_rows) {
-            const float gv = __uint_as_float(g[i]);
+            const float gv = __uint_as_float(g[i]), uv = __uint_as_float(u[i]);
             if (GATEUP) {
-              const float uv = __uint_as_float(u[i]);
               const float h = uv * (gv / (1.f + __expf(-gv)));
               p.hbuf[(size_t)(cd.out_row + col) * p.d.Ip + feat] = __float2bfloat16_rn(h);
-            } else if (feat < p.d.H) {
-              const float v = KT > 1 ? gv + __uint_as_float(u[i]) : gv;
-              p.obuf[(size_t)(cd.out_row + col) * p.d.H + feat] = __float2bfloat16_rn(v);
+            } else {
+              __nv_bfloat16* o = p.obuf + (size_t)(cd.out_row + col) * p.d.H;
+              if (feat < p.d.H) o[feat] = __float2bfloat16_rn(gv);
+              if (feat + kTileRows < p.d.H) o[feat + kTileRows] = __float2bfloat16_rn(uv);
             }
           }
         }

@@ -30,7 +30,8 @@ __device__ __forceinline__ uint32_t interleave_word(uint32_t w) {
 // One CTA per tile; thread handles 4 of the tile's 1024 16-byte chunks.
 __global__ void __launch_bounds__(256) retile_kernel(RetileParams p) {
   const int rt = blockIdx.y, kt = blockIdx.x;
-  uint8_t* tile = p.dst + (int64_t)rt * p.rt_stride + (int64_t)kt * p.kt_stride;
+  uint8_t* tile = p.rt_pairs ? p.dst + ((int64_t)((rt >> 1) * p.n_kt + kt) * 2 + (rt & 1)) * kTileBytes
+                             : p.dst + (int64_t)rt * p.rt_stride + (int64_t)kt * p.kt_stride;
   const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src);
   const int64_t row_bytes = (int64_t)p.cols * p.esz;
   const bool vec_ok = (row_bytes % 16 == 0) && (((int64_t)p.col0 * p.esz) % 16 == 0) &&
@@ -69,7 +70,8 @@ __global__ void scale_retile_kernel(ScaleRetileParams p) {
   const int sr = p.rb0 + rt, scol = p.kb0 + kt;
   float v = 0.f;
   if (sr < p.src_rows && scol < p.src_cols) v = p.src[(size_t)sr * p.src_cols + scol];
-  p.dst[(size_t)i * p.stride + p.lane] = v;
+  if (p.rt_pairs) p.dst[((size_t)(rt >> 1) * p.n_kt + kt) * 2 + (rt & 1)] = v;
+  else p.dst[(size_t)i * p.stride + p.lane] = v;
 }
 
 __global__ void fill_f32_kernel(float* dst, float v, int64_t n) {
