@@ -300,16 +300,21 @@ def main():
     value = world * T * args.steps / (ms / 1e3)
 
     # dominant kernel: per-launch duration from CUDA events on the launching stream
-    be.stage_timing(True)
+    def stage_profile(Tn, xs_n, n_prof):
+        """Median per-stage device time (CUDA events on the launching stream) over n_prof passes."""
+        be.stage_timing(True)
+        yy = torch.empty(Tn, H, dtype=torch.bfloat16, device=dev)
+        samples = {}
+        for i in range(n_prof):
+            be.moe_forward_fused_async(0, xs_n[i % 4], yy)
+            be.sync()
+            for k_, v in be.stage_times().items():
+                samples.setdefault(k_, []).append(v)
+        be.stage_timing(False)
+        return {k_: statistics.median(v) for k_, v in samples.items()}
+
     y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    stage = {}
-    n_prof = min(args.steps, 10)
-    for i in range(n_prof):
-        be.moe_forward_fused_async(0, xs[i % 4], y)
-        be.sync()
-        for k_, v in be.stage_times().items():
-            stage[k_] = stage.get(k_, 0.0) + v / n_prof
-    be.stage_timing(False)
+    stage = stage_profile(T, xs, max(5, min(args.steps, 20)))
     if sampler:
         # keep the GPU under the same load until the sampler has seen it for half a second
         t_end = time.perf_counter() + 0.6
@@ -328,7 +333,9 @@ def main():
     else:
         roof = {"bound": "tensor", "achieved": gu_flops / gu_s / 1e12, "peak": P["tf"], "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = None
+    # DRAM bytes of one launch, scaled by active experts from the ncu capture of the same kernel on
+    # a 33-expert case (973.30 MB read + 3.47 MB written; profiles/ffn_tc_fp8_cfg3_32experts_T32.md)
+    roof["traffic"] = int((active + NSHARED) * 976.77e6 / 33)
     roof["kernel"] = "ffn_tc_kernel<fp8, gate/up + SwiGLU>"
     roof["peak_source"] = P["src"]
     roof["launch_ms"] = stage["gateup"]
@@ -361,14 +368,16 @@ def main():
 
     sweep_out = {}
     for Tn in sweep:
-        ms_n, _, _ = timed(Tn, max(3, args.steps // 2), 3)
+        ms_n, _, xs_n = timed(Tn, max(3, args.steps // 2), 3)
         st = ms_n / max(3, args.steps // 2)
+        stage_n = stage_profile(Tn, xs_n, 5)
         c = be.expert_counts(0)
         a = int((c > 0).sum())
         bl, fl, _, _ = algorithmic(Tn, a, n_exp)
         rs = max(bl / (P["hbm"] * 1e9), fl / (P["tf_sus"] * 1e12))
         sweep_out[str(Tn)] = {"tokens_per_s": world * Tn / (st / 1e3), "ms_per_step": st, "active_experts": a,
-                              "layer_roofline_frac": (rs * 1e3) / st}
+                              "layer_roofline_frac": (rs * 1e3) / st,
+                              "stage_ms": {k_: round(v, 4) for k_, v in stage_n.items()}}
 
     if rank == 0:
         base = None

@@ -29,6 +29,10 @@ struct Layer {
   std::vector<char> host_registered;
   void* router_w = nullptr;
   int router_f32 = 0;
+  __nv_bfloat16* router_bf16 = nullptr;   // bf16 view of the router weight for the tensor-core router
+  bool router_bf16_owned = false;
+  bool router_tc = false;
+  CUtensorMap router_map;
   float* router_bias = nullptr;
   int32_t* last_counts = nullptr;    // device [E]
   bool have_counts = false;
@@ -61,7 +65,9 @@ struct ek_backend {
   __nv_bfloat16 *x_dev = nullptr, *y_dev = nullptr, *xp = nullptr, *hbuf = nullptr, *obuf = nullptr;
   __nv_bfloat16* tk_dev = nullptr;     // [T,k,H] staging of the controller-level call (lazy)
   size_t tk_cap = 0;
-  float *logits = nullptr, *weights = nullptr, *bias_scratch = nullptr;
+  float *logits = nullptr, *weights = nullptr, *bias_scratch = nullptr, *partial = nullptr;
+  void* encode_fn = nullptr;           // cuTensorMapEncodeTiled
+  int32_t* flag_dev = nullptr;
   int32_t *ids = nullptr, *counts = nullptr, *offsets = nullptr, *perm = nullptr, *inv = nullptr;
   ChunkDesc* chunks = nullptr;
   int32_t* n_chunks = nullptr;
@@ -177,6 +183,7 @@ int make_maps(ek_backend* be) {
   if (!fn || qres != cudaDriverEntryPointSuccess)
     return fail(be, EK_CUDA, "cuTensorMapEncodeTiled not available from the driver");
   EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(fn);
+  be->encode_fn = fn;
   CUtensorMap host[8];
   const int rows_box[4] = {16, 32, 64, 128};
   for (int which = 0; which < 2; ++which) {
@@ -195,6 +202,19 @@ int make_maps(ek_backend* be) {
   }
   CK(cudaMemcpy(be->maps, host, sizeof host, cudaMemcpyHostToDevice));
   return EK_OK;
+}
+
+// 2-D bf16 tensor map [rows, inner] with a {64, box_rows} box and the 128-byte swizzle.
+bool encode_2d(ek_backend* be, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint32_t box_rows) {
+  if (!be->encode_fn || (reinterpret_cast<uintptr_t>(base) & 15) || (inner * 2) % 16) return false;
+  EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(be->encode_fn);
+  cuuint64_t gdim[2] = {inner, rows};
+  cuuint64_t gstride[1] = {inner * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int ensure_layer(ek_backend* be, int layer, Layer** out) {
@@ -232,6 +252,7 @@ void free_layer(Layer& L) {
   cudaFree(L.dn_scale);
   cudaFree(L.registered);
   cudaFree(L.router_w);
+  if (L.router_bf16_owned) cudaFree(L.router_bf16);
   cudaFree(L.router_bias);
   cudaFree(L.last_counts);
 }
@@ -360,7 +381,27 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
     rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
     rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling;
     rp.bf16_weights = c.bf16_combine;
-    be->launches += launch_router_logits(rp, s);
+    rp.partial = nullptr;
+    rp.n_partials = 0;
+    bool tc_done = false;
+    if (L.router_tc) {
+      RouterTcParams tp;
+      if (encode_2d(be, &tp.x_map, x, (uint64_t)c.hidden, (uint64_t)T, 128)) {
+        tp.w_map = L.router_map;
+        tp.partial = be->partial;
+        tp.status = be->status;
+        tp.T = T; tp.H = c.hidden; tp.E = c.n_experts;
+        tp.n_atoms = (c.hidden + 63) / 64;
+        router_tc_plan(T, c.hidden, be->n_sm, &tp.n_splits, &tp.atoms_per_split);
+        tp.tmem_cols = 32;
+        while (tp.tmem_cols < c.n_experts) tp.tmem_cols *= 2;
+        be->launches += launch_router_tc(tp, s);
+        rp.partial = be->partial;
+        rp.n_partials = tp.n_splits;
+        tc_done = true;
+      }
+    }
+    if (!tc_done) be->launches += launch_router_logits(rp, s);
     be->launches += launch_route_select(rp, s);
     ids = be->ids;
   } else {
@@ -527,6 +568,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMalloc(&be->logits, T * E * 4));
   CKC(cudaMalloc(&be->weights, T * K * 4));
   CKC(cudaMalloc(&be->bias_scratch, E * 4));
+  CKC(cudaMalloc(&be->partial, (size_t)be->n_sm * 128 * E * 4));
+  CKC(cudaMalloc(&be->flag_dev, 4));
   CKC(cudaMalloc(&be->ids, T * K * 4));
   CKC(cudaMalloc(&be->counts, E * 4));
   CKC(cudaMalloc(&be->offsets, (E + 1) * 4));
@@ -563,7 +606,7 @@ void ek_backend_destroy(ek_backend_t* be) {
   for (auto& kv : be->layers) free_layer(kv.second);
   cudaFree(be->x_dev); cudaFree(be->y_dev); cudaFree(be->xp); cudaFree(be->hbuf); cudaFree(be->obuf);
   cudaFree(be->tk_dev);
-  cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->ids); cudaFree(be->counts);
+  cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->partial); cudaFree(be->flag_dev); cudaFree(be->ids); cudaFree(be->counts);
   cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
   cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->prof); cudaFree(be->maps);
   cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
@@ -829,6 +872,31 @@ int32_t ek_router_register(ek_backend_t* be, int32_t layer, const void* weight, 
   CK(cudaMalloc(&L->router_w, bytes));
   CK(cudaMemcpy(L->router_w, weight, bytes, cudaMemcpyDefault));
   L->router_f32 = dt == EK_F32;
+  // tensor-core router: needs the weight in bf16 without loss
+  if (L->router_bf16_owned) cudaFree(L->router_bf16);
+  L->router_bf16 = nullptr; L->router_bf16_owned = false; L->router_tc = false;
+  if (router_tc_supported(be->cfg.n_experts, be->cfg.hidden) && !getenv("EK_B200_SIMT_ROUTER")) {
+    if (dt == EK_BF16) {
+      L->router_bf16 = reinterpret_cast<__nv_bfloat16*>(L->router_w);
+    } else {
+      const int64_t n = (int64_t)be->cfg.n_experts * be->cfg.hidden;
+      CK(cudaMalloc(&L->router_bf16, n * 2));
+      L->router_bf16_owned = true;
+      CK(cudaMemsetAsync(be->flag_dev, 0, 4, be->load_stream));
+      be->launches += launch_f32_to_bf16_check(reinterpret_cast<const float*>(L->router_w), L->router_bf16, n,
+                                              be->flag_dev, be->load_stream);
+      int32_t inexact = 1;
+      CK(cudaMemcpyAsync(&inexact, be->flag_dev, 4, cudaMemcpyDeviceToHost, be->load_stream));
+      CK(cudaStreamSynchronize(be->load_stream));
+      if (inexact) {   // fp32 weights that bf16 cannot hold: stay on the fp32 CUDA-core router
+        cudaFree(L->router_bf16);
+        L->router_bf16 = nullptr; L->router_bf16_owned = false;
+      }
+    }
+    if (L->router_bf16)
+      L->router_tc = encode_2d(be, &L->router_map, L->router_bf16, (uint64_t)be->cfg.hidden,
+                               (uint64_t)be->cfg.n_experts, (uint32_t)be->cfg.n_experts);
+  }
   if (L->router_bias) { cudaFree(L->router_bias); L->router_bias = nullptr; }
   if (bias) {
     CK(cudaMalloc(&L->router_bias, sizeof(float) * be->cfg.n_experts));
@@ -1039,6 +1107,7 @@ int32_t ek_route_from_logits(ek_backend_t* be, const float* logits, int32_t T, c
   rp.T = T; rp.H = c.hidden; rp.E = c.n_experts; rp.k = c.top_k;
   rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
   rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling; rp.bf16_weights = c.bf16_combine;
+  rp.partial = nullptr; rp.n_partials = 0;
   be->launches += launch_route_select(rp, s);
   PermuteParams pp;
   pp.ids = be->ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;

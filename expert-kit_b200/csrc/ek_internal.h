@@ -70,6 +70,8 @@ struct RouteParams {
   int32_t wg_f32;
   const float* bias;           // [E] or null
   float* logits;               // [T,E]
+  const float* partial;        // [n_partials][T,E] split-K partial logits, or null: logits are final
+  int32_t n_partials;
   int32_t* ids;                // [T,k]
   float* weights;              // [T,k]
   int32_t* counts;             // [E] (zeroed by the launcher)
@@ -79,6 +81,22 @@ struct RouteParams {
   int32_t bf16_weights;        // round routing weights to bf16 (Qwen3 combine)
 };
 int launch_router_logits(const RouteParams& p, cudaStream_t s);
+
+// Tensor-core router (router_tc.cu): split-K partial logits, summed by route_select.
+struct RouterTcParams {
+  CUtensorMap x_map;        // activations [T,H] bf16, box {64, 128}, 128-byte swizzle
+  CUtensorMap w_map;        // router weight [E,H] bf16, box {64, E}
+  float* partial;           // [n_splits][T][E]
+  DevStatus* status;
+  int32_t T, H, E;
+  int32_t n_atoms;          // ceil(H / 64)
+  int32_t n_splits, atoms_per_split;
+  int32_t tmem_cols;        // power of two >= max(32, E)
+};
+bool router_tc_supported(int E, int H);
+void router_tc_plan(int T, int H, int n_sm, int* n_splits, int* atoms_per_split);
+int launch_router_tc(const RouterTcParams& p, cudaStream_t s);
+int launch_f32_to_bf16_check(const float* src, __nv_bfloat16* dst, int64_t n, int32_t* inexact, cudaStream_t s);
 int launch_route_select(const RouteParams& p, cudaStream_t s);
 int launch_histogram(const int32_t* ids, int32_t n, int32_t E, int32_t* counts, DevStatus* st,
                      cudaStream_t s);

@@ -248,6 +248,22 @@ __device__ __forceinline__ void umma_ts_x4(uint32_t d, uint32_t a, const uint64_
       : "memory");
 }
 
+// Four K steps with both operands in shared memory.
+__device__ __forceinline__ void umma_ss_x4(uint32_t d, const uint64_t* a, const uint64_t* b, uint32_t idesc,
+                                           uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t"
+      "setp.ne.b32 p0, %10, 0;\n\t"
+      "setp.ne.b32 p1, %9, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, p1;\n\t}" ::"r"(d),
+      "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "r"(idesc),
+      "r"(accumulate_first)
+      : "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

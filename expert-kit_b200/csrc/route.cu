@@ -119,8 +119,19 @@ __global__ void __launch_bounds__(kSelWarps * 32) route_select_kernel(RouteParam
   if (t >= p.T) return;
   float* sc = s_score[warp];
   float* ch = s_choice[warp];
-  const float* lg = p.logits + (size_t)t * p.E;
+  float* lg = p.logits + (size_t)t * p.E;
   const int E = p.E;
+  if (p.partial) {
+    // add the split-K partial sums in split order; the softmax path works on bf16 logits like the
+    // reference's bf16 linear layer
+    for (int e = lane; e < E; e += 32) {
+      float v = 0.f;
+      for (int ks = 0; ks < p.n_partials; ++ks) v += p.partial[((size_t)ks * p.T + t) * E + e];
+      if (p.scoring == EK_SCORE_SOFTMAX) v = __bfloat162float(__float2bfloat16_rn(v));
+      lg[e] = v;
+    }
+    __syncwarp();
+  }
 
   if (p.scoring == EK_SCORE_SOFTMAX) {
     float m = -INFINITY;
