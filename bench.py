@@ -54,20 +54,66 @@ def peaks():
 
 # ---- clocks ---------------------------------------------------------------------------------
 class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the benchmark runs: a background
+    thread reading NVML every 200 ms (reading only; nothing is ever set).  An `nvidia-smi -lms`
+    child is the fallback when the NVML binding is missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        import threading
+        self.sm, self.reasons, self.max_mhz = [], set(), None
         self.p = None
+        self._stop = threading.Event()
+        self._thread = None
+        if os.environ.get("EK_BENCH_NO_CLOCKS"):
+            return
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[gpu_index]) if visible and visible.split(",")[gpu_index].isdigit() else gpu_index
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            names = {"hw_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                     "hw_thermal_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                     "sw_thermal_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                     "sw_power_cap": getattr(pynvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                        r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                        for n, bit in names.items():
+                            if r & bit:
+                                self.reasons.add(n)
+                    except Exception:
+                        pass
+                    self._stop.wait(0.2)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._thread = None
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-i", str(gpu_index), "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-i", str(gpu_index), "-lms", "500"], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.p = None
 
     def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            if not self.sm:
+                return None
+            busy = [v for v in self.sm if v > 0.5 * max(self.sm)]
+            return {"sm_mhz": statistics.median(busy or self.sm), "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(self.reasons), "samples": len(self.sm), "source": "nvml"}
         if self.p is None:
             return None
         self.p.terminate()
@@ -96,9 +142,9 @@ class ClockSampler:
             pass
         if not sm:
             return None
-        busy = [s for s in sm if s > 0.5 * max(sm)]
+        busy = [v for v in sm if v > 0.5 * max(sm)]
         return {"sm_mhz": statistics.median(busy or sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ---- synthetic layer on the device ----------------------------------------------------------
@@ -111,19 +157,24 @@ def quantize_fp8_block_dev(w: torch.Tensor):
     return q.contiguous(), s.contiguous()
 
 
-def build_backend(T_max: int, rank: int = 0, seed: int = 3000, n_experts: int = E):
+def build_backend(T_max: int, rank: int = 0, seed: int = 3000, n_experts: int = E, ep_rank: int = 0,
+                  ep_size: int = 1):
+    """Registers the router, the shared expert and the routed experts this rank owns
+    (all of them at ep_size 1).  The router weight is the same on every rank."""
     import ek_b200
     from ek_b200.backend import expert_tensors
     dev = torch.device("cuda", torch.cuda.current_device())
     cfg = ek_b200.BackendConfig(hidden=H, intermediate=I, n_experts=n_experts, top_k=K, scoring=1, n_group=8,
                                 topk_group=4, norm_topk_prob=True, routed_scaling=2.5, n_shared_experts=NSHARED,
                                 bf16_combine=False, quant=1, max_tokens=T_max, max_layers=1,
-                                device=dev.index, model_name="dsv3")
+                                device=dev.index, ep_rank=ep_rank, ep_size=ep_size, model_name="dsv3")
     be = ek_b200.Backend(cfg)
-    g = torch.Generator(device=dev).manual_seed(seed + rank)
+    g = torch.Generator(device=dev).manual_seed(seed)
     wg = (torch.randn(n_experts, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
     be.register_router(0, wg, torch.zeros(n_experts, device=dev))
-    for e in list(range(n_experts)) + ["shared"]:
+    g = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
+    el = n_experts // ep_size
+    for e in list(range(ep_rank * el, (ep_rank + 1) * el)) + ["shared"]:
         mats = []
         for shape in ((I, H), (I, H), (H, I)):
             w = torch.randn(shape, generator=g, device=dev) * 0.02
@@ -211,7 +262,8 @@ def run_reference(args):
     v = statistics.mean(b["value"] for b in vals)
     ms = statistics.mean(b["ms_per_step"] for b in vals)
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": workload_config(T, args.gpus),
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": base["cores"], "kind": "port", "sample": base["sample"]},
@@ -220,12 +272,140 @@ def run_reference(args):
 
 
 def workload_config(T: int, n_gpus: int, n_exp: int = E):
-    return {"workload": f"cfg3 DeepSeek-V3-shape MoE layer, W8A16 (fp8 e4m3 + 128x128 fp32 block scales), T={T} tokens per GPU"
+    return {"workload": f"cfg3 DeepSeek-V3-shape MoE layer, W8A16 (fp8 e4m3 + 128x128 fp32 block scales), global batch T={T} tokens"
                         + ("" if n_exp == E else f" [REDUCED to {n_exp} routed experts: profiling case, not the benchmark]"),
             "hidden": H, "intermediate": I, "experts": n_exp, "shared_experts": NSHARED, "top_k": K,
-            "routing": "sigmoid, 8 groups, top-4 groups, renormalised, x2.5", "tokens_per_gpu": T,
-            "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} data-parallel replicas (weak scaling)",
+            "routing": "sigmoid, 8 groups, top-4 groups, renormalised, x2.5", "global_tokens": T,
+            "tokens_per_gpu": T // n_gpus,
+            "parallelism": "single GPU" if n_gpus == 1 else
+            f"ep{n_gpus}: {n_exp // n_gpus} routed experts per GPU, shared expert and router replicated, "
+            "NCCL all-to-all dispatch/combine over NVLink, global batch fixed (strong scaling)",
             "l2": "weights streamed per step (11.3 GB) exceed the 126 MB L2; no flush needed"}
+
+
+
+def main_ep(args, rank: int, world: int, local: int):
+    """N > 1: the layer's experts are sharded over the ranks (expert parallel); the global batch of
+    --tokens tokens is split evenly over the ranks; dispatch and combine are NCCL all-to-alls."""
+    import torch.distributed as dist
+    import ek_b200
+    import datetime
+    os.environ["NCCL_DEBUG"] = os.environ.get("EK_BENCH_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
+    # a short collective timeout: a rank that fails must not keep the others (and the GPUs) waiting
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=90))
+    T = args.tokens
+    if T % world:
+        raise SystemExit("--tokens must be divisible by the number of GPUs")
+    Tl = T // world
+    n_exp = args.experts
+    be, dev = build_backend(max(T, 256), rank, n_experts=n_exp, ep_rank=rank, ep_size=world)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    be.set_stream(stream.cuda_stream)
+    moe = ek_b200.ExpertParallelMoE(ek_b200.BackendStages(be))
+    g = torch.Generator(device=dev).manual_seed(17 + rank)
+    xs = [torch.randn(Tl, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(4)]
+    for i in range(args.warmup):
+        moe.forward(0, xs[i % 4])
+    be.sync()
+    sampler = ClockSampler(local) if rank == 0 else None
+    dist.barrier()
+    torch.cuda.synchronize()
+    l0 = be.kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        moe.forward(0, xs[i % 4])
+    e1.record()
+    be.sync()
+    torch.cuda.synchronize()
+    launches = be.kernel_launches() - l0
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    ms = float(t.item())
+    ms_step = ms / args.steps
+    value = T * args.steps / (ms / 1e3)
+
+    # dominant kernel on this rank: gate/up over the local experts
+    be.stage_timing(True)
+    samples = {}
+    for i in range(max(5, min(args.steps, 20))):
+        moe.forward(0, xs[i % 4])
+        be.sync()
+        for k_, v in be.stage_times().items():
+            samples.setdefault(k_, []).append(v)
+    be.stage_timing(False)
+    stage = {k_: statistics.median(v) for k_, v in samples.items()}
+    counts_all = moe.last_counts_all
+    el = n_exp // world
+    mine = counts_all[:, rank * el:(rank + 1) * el].sum(0)
+    active = int((mine > 0).sum())
+    rows = int(mine.sum()) + NSHARED * Tl
+    # keep every GPU under the same load for about half a second so that the clock sampler sees it;
+    # the iteration count is the same on all ranks (forward is a collective)
+    for _ in range(int(600.0 / max(ms_step, 0.05)) + 1):
+        moe.forward(0, xs[0])
+    be.sync()
+    clocks = sampler.stop() if sampler else None
+    P = peaks()
+    gu_bytes = (active + NSHARED) * (2 * H * I + 8 * (I // 128) * (H // 128)) + rows * H * 2 + rows * I * 2
+    gu_flops = 4 * H * I * rows
+    gu_s = max(stage["gateup"], 1e-6) / 1e3
+    roof = {"bound": "hbm", "achieved": gu_bytes / gu_s / 1e9, "peak": P["hbm"], "unit": "GB/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = int((active + NSHARED) * 976.77e6 / 33)
+    roof["kernel"] = "ffn_tc_kernel<fp8, gate/up + SwiGLU> on rank 0's experts"
+    roof["peak_source"] = P["src"]
+    roof["launch_ms"] = stage["gateup"]
+    roof["algorithmic_bytes"] = gu_bytes
+    # per-GPU roofline of the sharded layer: each rank streams its own experts once
+    sc = 12 * (I // 128) * (H // 128)
+    bytes_rank = (active + NSHARED) * (3 * H * I + sc) + 2 * H * n_exp + 4 * Tl * H
+    flops_rank = 2 * Tl * H * n_exp + 6 * H * I * (rows)
+    roof_s = max(bytes_rank / (P["hbm"] * 1e9), flops_rank / (P["tf_sus"] * 1e12))
+    nvlink_bytes = 2 * Tl * K * H * 2 * (1 - 1 / world)
+    layer = {"roofline_tokens_per_s": T / roof_s, "frac": roof_s * 1e3 / ms_step, "bound": "hbm",
+             "bytes_per_gpu": bytes_rank, "flops_per_gpu": flops_rank, "active_experts_rank0": active,
+             "nvlink_bytes_per_gpu_per_step": int(nvlink_bytes), "stage_ms_rank0": stage}
+
+    # end to end: host batch in, host result out, through the public Python API of this package
+    xh = [x.cpu().pin_memory() for x in xs]
+    yh = torch.empty(Tl, H, dtype=torch.bfloat16).pin_memory()
+    xd = torch.empty(Tl, H, dtype=torch.bfloat16, device=dev)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step(i):
+        xd.copy_(xh[i % 4], non_blocking=True)
+        y = moe.forward(0, xd)
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step(0)
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    tt = torch.tensor([time.perf_counter() - t0], device=dev)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    e2e = {"value": T * e2e_steps / float(tt.item()), "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
+           "d2h_bytes_per_step": T * H * 2, "steps": e2e_steps}
+    if rank == 0:
+        base = None
+        if not args.no_cpu_baseline:
+            b = cpu_baseline(T)
+            base = {k_: b[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(T, world, n_exp),
+                "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+                "layer_roofline": layer, "cpu_baseline": base}
+        print(json.dumps(line))
+    be.close()
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def main():
@@ -250,11 +430,9 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local)
-    dist = None
     if world > 1:
-        import torch.distributed as dist_mod
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return main_ep(args, rank, world, local)
+    dist = None
 
     T = args.tokens
     sweep = [int(t) for t in args.sweep.split(",") if t]
@@ -293,8 +471,6 @@ def main():
         return ms, launches, xs
 
     sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        time.sleep(1.0)   # nvidia-smi needs about a second before its first sample
     ms, launches, xs = timed(T, args.steps, args.warmup)
     ms_step = ms / args.steps
     value = world * T * args.steps / (ms / 1e3)

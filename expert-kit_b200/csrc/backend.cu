@@ -59,6 +59,10 @@ struct ek_backend {
   bool timing = false;
   float stage_ms[EK_STAGE_COUNT] = {};
   int ffn_impl = 0;                    // 0 tensor cores, 1 CUDA-core checker
+  int ep_rows = 0, ep_T = 0;           // rows / tokens of the last ek_ep_ffn
+  cudaEvent_t ep_upload_done = nullptr;
+  bool ep_uploaded = false;
+  int32_t* h_ep_count = nullptr;       // pinned
   int precise = 0;                     // fp8 block scales in fp32 inside the GEMM
 
   // workspace
@@ -75,6 +79,10 @@ struct ek_backend {
   long long* prof = nullptr;           // 4 roles x 8 counters (profile builds)
   DevStatus* h_status = nullptr;       // pinned
   ChunkDesc* h_chunks = nullptr;       // pinned, worker-level call
+  int h_chunks_cap = 0;
+  RowSegment* segs = nullptr;          // device, expert-parallel regroup
+  RowSegment* h_segs = nullptr;        // pinned
+  int segs_cap = 0;
   CUtensorMap* maps = nullptr;         // device: x_maps[4], h_maps[4]
   void* h_x = nullptr;                 // pinned staging
   void* h_y = nullptr;
@@ -437,6 +445,7 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
     cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = y;
     cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = n_shared; cp.Tk = Tk;
     cp.bf16_products = c.bf16_combine;
+    cp.shared = nullptr;
     be->launches += launch_combine(cp, s);
   } else {
     be->launches += launch_unpermute(be->obuf, be->inv, out_tk, T, k, c.hidden, s);
@@ -556,6 +565,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   be->stream = be->own_stream;
   CKC(cudaStreamCreateWithFlags(&be->load_stream, cudaStreamNonBlocking));
   CKC(cudaEventCreateWithFlags(&be->fwd_done, cudaEventDisableTiming));
+  CKC(cudaEventCreateWithFlags(&be->ep_upload_done, cudaEventDisableTiming));
+  CKC(cudaMallocHost(&be->h_ep_count, 64));
   for (auto& e : be->ev) CKC(cudaEventCreate(&e));
   const size_t T = c.max_tokens, H = c.hidden, E = c.n_experts, K = c.top_k;
   CKC(cudaMalloc(&be->x_dev, T * H * 2));
@@ -582,7 +593,12 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMalloc(&be->prof, 32 * sizeof(long long)));
   CKC(cudaMemset(be->prof, 0, 32 * sizeof(long long)));
   CKC(cudaMallocHost(&be->h_status, sizeof(DevStatus)));
-  CKC(cudaMallocHost(&be->h_chunks, sizeof(ChunkDesc) * 1024));
+  be->h_chunks_cap = std::max(1024, be->max_chunks);
+  CKC(cudaMallocHost(&be->h_chunks, sizeof(ChunkDesc) * be->h_chunks_cap));
+  be->segs_cap = c.ep_size * be->n_local;
+  // forward (arrival -> expert order) and reverse lists side by side
+  CKC(cudaMalloc(&be->segs, sizeof(RowSegment) * be->segs_cap * 2));
+  CKC(cudaMallocHost(&be->h_segs, sizeof(RowSegment) * be->segs_cap * 2));
   CKC(cudaMalloc(&be->maps, sizeof(CUtensorMap) * 8));
   be->h_cap = T * H * 2;
   CKC(cudaMallocHost(&be->h_x, be->h_cap));
@@ -609,12 +625,14 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->partial); cudaFree(be->flag_dev); cudaFree(be->ids); cudaFree(be->counts);
   cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
   cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->prof); cudaFree(be->maps);
-  cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
+  cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_segs); cudaFree(be->segs); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
   cudaFree(be->stage_cvt);
   for (auto& e : be->ev) if (e) cudaEventDestroy(e);
   if (be->fwd_done) cudaEventDestroy(be->fwd_done);
+  if (be->ep_upload_done) cudaEventDestroy(be->ep_upload_done);
+  cudaFreeHost(be->h_ep_count);
   if (be->own_stream) cudaStreamDestroy(be->own_stream);
   if (be->load_stream) cudaStreamDestroy(be->load_stream);
   delete be;
@@ -950,6 +968,7 @@ int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x, int32
     CombineParams cp;
     cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
     cp.T = n; cp.k = 0; cp.H = c.hidden; cp.n_shared = n_virtual; cp.Tk = 0; cp.bf16_products = 0;
+    cp.shared = nullptr;
     be->launches += launch_combine(cp, s);
     res = be->y_dev;
   }
@@ -1040,7 +1059,8 @@ int32_t ek_set_stream(ek_backend_t* be, void* stream) {
   if (!be) return EK_INVALID_INPUT;
   std::lock_guard<std::mutex> fg(be->fwd_mu);
   cudaStreamSynchronize(be->stream);
-  be->stream = stream ? reinterpret_cast<cudaStream_t>(stream) : be->own_stream;
+  // (void*)-1 selects the backend's own stream again; NULL is CUDA's default stream
+  be->stream = stream == reinterpret_cast<void*>(-1) ? be->own_stream : reinterpret_cast<cudaStream_t>(stream);
   return EK_OK;
 }
 
@@ -1144,6 +1164,7 @@ int32_t ek_combine(ek_backend_t* be, const void* out, const float* weights, int3
   cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
   cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = shared ? 1 : 0; cp.Tk = T * k;
   cp.bf16_products = c.bf16_combine;
+  cp.shared = nullptr;
   be->launches += launch_combine(cp, s);
   CK(cudaMemcpyAsync(y, be->y_dev, (size_t)T * H * 2, cudaMemcpyDefault, s));
   CK(cudaStreamSynchronize(s));
@@ -1204,6 +1225,181 @@ int32_t ek_worker_forward_wire(ek_backend_t* be, const char* expert_id, const vo
   memcpy(o + 8, hdr.data(), hdr.size());
   // the payload may be unaligned inside the blob; cudaMemcpy from pageable memory does not care
   return ek_expert_forward(be, expert_id, data->data, (int32_t)n, o + 8 + hdr.size());
+}
+
+
+// ---- expert-parallel stages ------------------------------------------------------------------------
+// The reference shards experts over worker processes and moves rows by gRPC
+// (ek-computation/src/controller/executor.rs:141-226).  Here experts are sharded contiguously over
+// the GPUs of one box (expert e lives on rank e / (E / ep_size)); the caller moves rows between
+// ranks (all-to-all over NVLink) between these three stages, which all run on the backend stream.
+
+int32_t ek_ep_route(ek_backend_t* be, int32_t layer, const void* x_dev, int32_t T, void* send_rows_dev,
+                    int32_t* counts_dev) {
+  if (!be || !x_dev || !send_rows_dev || !counts_dev) return EK_INVALID_INPUT;
+  if (T < 1 || T > be->cfg.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, be->cfg.max_tokens);
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end() || !li->second.router_w)
+    return fail(be, EK_NOT_FOUND, "layer %d has no router weight registered", layer);
+  Layer& L = li->second;
+  const ek_config_t& c = be->cfg;
+  cudaStream_t s = be->stream;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_dev);
+  RouteParams rp;
+  rp.x = x; rp.wg = L.router_w; rp.wg_f32 = L.router_f32; rp.bias = L.router_bias;
+  rp.logits = be->logits; rp.ids = be->ids; rp.weights = be->weights; rp.counts = be->counts;
+  rp.T = T; rp.H = c.hidden; rp.E = c.n_experts; rp.k = c.top_k;
+  rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
+  rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling; rp.bf16_weights = c.bf16_combine;
+  rp.partial = nullptr; rp.n_partials = 0;
+  bool tc_done = false;
+  if (L.router_tc) {
+    RouterTcParams tp;
+    if (encode_2d(be, &tp.x_map, x, (uint64_t)c.hidden, (uint64_t)T, 128)) {
+      tp.w_map = L.router_map; tp.partial = be->partial; tp.status = be->status;
+      tp.T = T; tp.H = c.hidden; tp.E = c.n_experts; tp.n_atoms = (c.hidden + 63) / 64;
+      router_tc_plan(T, c.hidden, be->n_sm, &tp.n_splits, &tp.atoms_per_split);
+      tp.tmem_cols = 32;
+      while (tp.tmem_cols < c.n_experts) tp.tmem_cols *= 2;
+      be->launches += launch_router_tc(tp, s);
+      rp.partial = be->partial; rp.n_partials = tp.n_splits;
+      tc_done = true;
+    }
+  }
+  if (!tc_done) be->launches += launch_router_logits(rp, s);
+  be->launches += launch_route_select(rp, s);
+  // bucket over ALL experts: rows sorted by global expert id are already grouped by owner rank
+  PermuteParams pp;
+  pp.ids = be->ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
+  pp.T = T; pp.k = c.top_k; pp.E = c.n_experts; pp.e_lo = 0; pp.e_hi = c.n_experts;
+  be->launches += launch_permute(pp, s);
+  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, reinterpret_cast<__nv_bfloat16*>(send_rows_dev),
+                                T, c.top_k, c.hidden, 0, s);
+  CK(cudaMemcpyAsync(counts_dev, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s));
+  CK(cudaMemcpyAsync(L.last_counts, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s));
+  L.have_counts = true;
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_ep_ffn(ek_backend_t* be, int32_t layer, const void* rows_dev, const int32_t* counts_src_host,
+                  const void* x_dev, int32_t T, void* out_rows_dev) {
+  if (!be || !counts_src_host) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end()) return fail(be, EK_EXPERT_NOT_FOUND, "layer %d holds no experts", layer);
+  Layer& L = li->second;
+  const ek_config_t& c = be->cfg;
+  const int R = c.ep_size, EL = be->n_local, S = c.n_shared_experts;
+  if (S > 0 && (!x_dev || T < 1 || T > c.max_tokens)) return fail(be, EK_INVALID_INPUT, "shared expert needs the local tokens");
+  // the pinned staging areas are reused per call: wait until the previous call's uploads were consumed
+  if (be->ep_uploaded) CK(cudaEventSynchronize(be->ep_upload_done));
+  // rows per local expert and where each (source, expert) segment goes in expert order
+  std::vector<int> per_expert(EL, 0);
+  int64_t n_rows = 0;
+  for (int sidx = 0; sidx < R; ++sidx)
+    for (int e = 0; e < EL; ++e) {
+      const int v = counts_src_host[sidx * EL + e];
+      if (v < 0) return fail(be, EK_INVALID_INPUT, "negative row count");
+      per_expert[e] += v;
+      n_rows += v;
+    }
+  const int Tsh = S > 0 ? T : 0;
+  if (n_rows + (int64_t)S * Tsh > be->rows_cap - 128)
+    return fail(be, EK_INVALID_INPUT, "%lld rows arrived, workspace holds %d: raise max_tokens", (long long)n_rows, be->rows_cap);
+  if (n_rows > 0 && (!rows_dev || !out_rows_dev)) return EK_INVALID_INPUT;
+  std::vector<int> expert_off(EL + 1, 0);
+  for (int e = 0; e < EL; ++e) expert_off[e + 1] = expert_off[e] + per_expert[e];
+  std::vector<int> fill(EL, 0);
+  int n_segs = 0, arrival = 0, max_seg = 0;
+  for (int sidx = 0; sidx < R; ++sidx)
+    for (int e = 0; e < EL; ++e) {
+      const int v = counts_src_host[sidx * EL + e];
+      if (v == 0) continue;
+      if (!L.host_registered[e]) return fail(be, EK_EXPERT_NOT_FOUND, "expert %d received rows but is not registered", be->e_lo + e);
+      RowSegment sg;
+      sg.src = arrival; sg.dst = expert_off[e] + fill[e]; sg.n = v; sg.pad = 0;
+      be->h_segs[n_segs++] = sg;
+      arrival += v;
+      fill[e] += v;
+      max_seg = std::max(max_seg, v);
+    }
+  const int rows_total = (int)n_rows;
+  const int nmax = pick_nmax(rows_total, EL);
+  const int chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
+  int n_chunks = 0;
+  auto push = [&](int slot, int in_row, int out_row, int n) -> bool {
+    for (int c0 = 0; c0 < n; c0 += chunk_rows) {
+      if (n_chunks >= be->h_chunks_cap || n_chunks >= be->max_chunks) return false;
+      ChunkDesc cd;
+      cd.slot = slot; cd.in_row = in_row + c0; cd.out_row = out_row + c0; cd.n_rows = std::min(chunk_rows, n - c0);
+      be->h_chunks[n_chunks++] = cd;
+    }
+    return true;
+  };
+  for (int e = 0; e < EL; ++e)
+    if (per_expert[e] > 0 && !push(e, expert_off[e], expert_off[e], per_expert[e]))
+      return fail(be, EK_INVALID_INPUT, "too many chunks for the workspace");
+  for (int j = 0; j < S; ++j) {
+    if (!L.host_registered[EL + j]) return fail(be, EK_EXPERT_NOT_FOUND, "shared expert %d of the layer is not registered", j);
+    if (!push(EL + j, rows_total, rows_total + j * Tsh, Tsh)) return fail(be, EK_INVALID_INPUT, "too many chunks for the workspace");
+  }
+  cudaStream_t s = be->stream;
+  RowSegment* h_rev = be->h_segs + be->segs_cap;
+  RowSegment* d_rev = be->segs + be->segs_cap;
+  if (n_segs > 0) {
+    for (int i = 0; i < n_segs; ++i) {
+      h_rev[i] = be->h_segs[i];
+      std::swap(h_rev[i].src, h_rev[i].dst);   // back to arrival order
+    }
+    CK(cudaMemcpyAsync(be->segs, be->h_segs, sizeof(RowSegment) * n_segs, cudaMemcpyHostToDevice, s));
+    CK(cudaMemcpyAsync(d_rev, h_rev, sizeof(RowSegment) * n_segs, cudaMemcpyHostToDevice, s));
+    be->launches += launch_segment_copy(reinterpret_cast<const __nv_bfloat16*>(rows_dev), be->xp, be->segs, n_segs,
+                                        max_seg, c.hidden, s);
+  }
+  if (S > 0)
+    CK(cudaMemcpyAsync(be->xp + (size_t)rows_total * c.hidden, x_dev, (size_t)T * c.hidden * 2, cudaMemcpyDeviceToDevice, s));
+  CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * n_chunks, cudaMemcpyHostToDevice, s));
+  be->h_ep_count[0] = n_chunks;
+  CK(cudaMemcpyAsync(be->n_chunks, &be->h_ep_count[0], 4, cudaMemcpyHostToDevice, s));
+  CK(cudaEventRecord(be->ep_upload_done, s));
+  be->ep_uploaded = true;
+  be->ep_rows = rows_total;
+  be->ep_T = Tsh;
+  mark(be, 0); mark(be, 1); mark(be, 2);
+  if (n_chunks > 0) run_ffn(be, L, nmax, 0);
+  mark(be, 3);
+  if (n_chunks > 0) run_ffn(be, L, nmax, 1);
+  mark(be, 4);
+  if (n_segs > 0)
+    be->launches += launch_segment_copy(be->obuf, reinterpret_cast<__nv_bfloat16*>(out_rows_dev), d_rev, n_segs,
+                                        max_seg, c.hidden, s);
+  mark(be, 5);
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_ep_combine(ek_backend_t* be, int32_t layer, const void* returned_rows_dev, int32_t T, void* y_dev) {
+  if (!be || !returned_rows_dev || !y_dev) return EK_INVALID_INPUT;
+  if (T < 1 || T > be->cfg.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, be->cfg.max_tokens);
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  const ek_config_t& c = be->cfg;
+  if (c.n_shared_experts > 0 && be->ep_T != T) return fail(be, EK_INVALID_INPUT, "ek_ep_ffn must run on the same tokens first");
+  CombineParams cp;
+  cp.obuf = reinterpret_cast<const __nv_bfloat16*>(returned_rows_dev);
+  cp.inv = be->inv; cp.weights = be->weights; cp.y = reinterpret_cast<__nv_bfloat16*>(y_dev);
+  cp.T = T; cp.k = c.top_k; cp.H = c.hidden; cp.n_shared = c.n_shared_experts; cp.Tk = T * c.top_k;
+  cp.bf16_products = c.bf16_combine;
+  cp.shared = be->obuf + (size_t)be->ep_rows * c.hidden;   // shared expert rows of the last ek_ep_ffn
+  be->launches += launch_combine(cp, be->stream);
+  CK(cudaGetLastError());
+  return EK_OK;
 }
 
 // ---- observability -----------------------------------------------------------------------------

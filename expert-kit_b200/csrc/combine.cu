@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
       for (int j = 0; j < 8; ++j) sh[j] = 0.f;
       for (int q = 0; q < p.n_shared; ++q) {
         float f[8];
-        unpack8(*reinterpret_cast<const uint4*>(
-                    p.obuf + ((size_t)p.Tk + (size_t)q * p.T + t) * p.H + v * 8), f);
+        const __nv_bfloat16* sh_rows = p.shared ? p.shared : p.obuf + (size_t)p.Tk * p.H;
+        unpack8(*reinterpret_cast<const uint4*>(sh_rows + ((size_t)q * p.T + t) * p.H + v * 8), f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) sh[j] += f[j];
       }
@@ -101,7 +101,27 @@ __global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __r
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
 }
 
+// One CTA per (segment, row-in-segment): rows move between arrival order and expert order.
+__global__ void __launch_bounds__(128) segment_copy_kernel(const __nv_bfloat16* __restrict__ src,
+                                                           __nv_bfloat16* __restrict__ dst,
+                                                           const RowSegment* __restrict__ segs, int32_t H) {
+  const RowSegment sg = segs[blockIdx.y];
+  const int i = blockIdx.x;
+  if (i >= sg.n) return;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)(sg.src + i) * H);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)(sg.dst + i) * H);
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
+}
+
 }  // namespace
+
+int launch_segment_copy(const __nv_bfloat16* src, __nv_bfloat16* dst, const RowSegment* segs, int32_t n_segs,
+                        int32_t max_rows_per_seg, int32_t H, cudaStream_t s) {
+  if (n_segs <= 0 || max_rows_per_seg <= 0) return 0;
+  dim3 grid(max_rows_per_seg, n_segs);
+  segment_copy_kernel<<<grid, 128, 0, s>>>(src, dst, segs, H);
+  return 1;
+}
 
 int launch_combine(const CombineParams& p, cudaStream_t s) {
   if (p.T > 0) combine_kernel<<<p.T, 256, 0, s>>>(p);

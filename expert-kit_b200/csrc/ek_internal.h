@@ -166,13 +166,21 @@ struct CombineParams {
   const float* weights;        // [T,k]
   __nv_bfloat16* y;            // [T,H]
   int32_t T, k, H;
-  int32_t n_shared, Tk;        // shared rows at Tk + j*T + t
+  int32_t n_shared, Tk;        // shared rows at shared[(j*T + t)]
   int32_t bf16_products;
+  const __nv_bfloat16* shared; // [n_shared*T, H]; null: obuf + Tk*H
 };
 int launch_combine(const CombineParams& p, cudaStream_t s);
 // out[t,s,:] = obuf[inv[t*k+s]]
 int launch_unpermute(const __nv_bfloat16* obuf, const int32_t* inv, __nv_bfloat16* out, int32_t T,
                      int32_t k, int32_t H, cudaStream_t s);
+
+// Row-segment copies for the expert-parallel regroup: dst[seg.dst + i] = src[seg.src + i], i < seg.n
+struct RowSegment {
+  int32_t src, dst, n, pad;
+};
+int launch_segment_copy(const __nv_bfloat16* src, __nv_bfloat16* dst, const RowSegment* segs, int32_t n_segs,
+                        int32_t max_rows_per_seg, int32_t H, cudaStream_t s);
 
 // Registration-time layout kernels.
 struct RetileParams {

@@ -76,6 +76,9 @@ SIGNATURES = {
     "ek_set_stream": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "ek_moe_forward_fused_async": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "ek_sync": (C.c_int32, [C.c_void_p]),
+    "ek_ep_route": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "ek_ep_ffn": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "ek_ep_combine": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "ek_bucket_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_char_p, C.c_size_t]),
 }

@@ -219,7 +219,26 @@ class Backend:
         self._check(self._lib.ek_sync(self._h))
 
     def set_stream(self, cuda_stream: Optional[int]):
-        self._check(self._lib.ek_set_stream(self._h, C.c_void_p(cuda_stream or 0)))
+        """Run on the given CUDA stream handle (0 = the default stream); None = the backend's own."""
+        h = C.c_void_p(-1) if cuda_stream is None else C.c_void_p(int(cuda_stream))
+        self._check(self._lib.ek_set_stream(self._h, h))
+
+    # ---- expert-parallel stages (device tensors, asynchronous on the backend stream) -------------
+    def ep_route(self, layer: int, x: torch.Tensor, send_rows: torch.Tensor, counts: torch.Tensor):
+        assert x.is_cuda and send_rows.is_cuda and counts.is_cuda and counts.dtype == torch.int32
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and send_rows.is_contiguous()
+        self._check(self._lib.ek_ep_route(self._h, layer, _ptr(x), x.shape[0], _ptr(send_rows), _ptr(counts)))
+
+    def ep_ffn(self, layer: int, rows: torch.Tensor, counts_src: torch.Tensor, x: torch.Tensor,
+               out_rows: torch.Tensor):
+        counts_src = counts_src.to(torch.int32).contiguous().cpu()
+        assert rows.is_contiguous() and out_rows.is_contiguous() and x.is_contiguous()
+        self._check(self._lib.ek_ep_ffn(self._h, layer, _ptr(rows) if rows.numel() else None, _ptr(counts_src), _ptr(x),
+                                        x.shape[0], _ptr(out_rows) if out_rows.numel() else None))
+
+    def ep_combine(self, layer: int, returned: torch.Tensor, T: int, y: torch.Tensor):
+        assert returned.is_contiguous() and y.is_contiguous()
+        self._check(self._lib.ek_ep_combine(self._h, layer, _ptr(returned), T, _ptr(y)))
 
     def route_from_logits(self, logits: torch.Tensor, bias: Optional[torch.Tensor] = None):
         logits = logits.to(torch.float32).contiguous()

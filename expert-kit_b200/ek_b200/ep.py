@@ -1,0 +1,99 @@
+"""Expert-parallel MoE layer over the GPUs of one box.
+
+The reference shards experts over worker processes and moves rows with one gRPC per distinct
+expert (ek-computation/src/controller/executor.rs:141-226).  Here expert e lives on rank
+e // (n_experts // world) and rows move with two all-to-all exchanges over NVLink
+(`torch.distributed`, NCCL): dispatch of the routed rows to the expert owners and return of the
+expert outputs.  Routing, bucketing, the grouped expert FFN and the weighted combine are the
+library's kernels (`ek_ep_route`, `ek_ep_ffn`, `ek_ep_combine`).
+
+One process per GPU.  The exchange plan is computed on the host from the all-gathered per-expert
+row counts; that is the one host synchronisation per layer.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def plan_exchange(counts_all: torch.Tensor, rank: int, world: int):
+    """counts_all[r, e] = rows rank r routes to global expert e (host tensor).
+
+    Returns (send_splits, recv_splits, counts_src): rows this rank sends to / receives from each
+    rank, and counts_src[s, le] = rows arriving from rank s for local expert le -- arrival order is
+    source-major, expert-minor, because every source sends its rows sorted by expert."""
+    E = counts_all.shape[1]
+    if E % world:
+        raise ValueError("the expert count must be divisible by the number of ranks")
+    el = E // world
+    per_dest = counts_all.view(world, world, el).sum(dim=2)          # [src, dst]
+    send_splits = per_dest[rank].tolist()
+    recv_splits = per_dest[:, rank].tolist()
+    counts_src = counts_all[:, rank * el:(rank + 1) * el].contiguous().to(torch.int32)
+    return send_splits, recv_splits, counts_src
+
+
+class BackendStages:
+    """The three device stages of one rank, served by the CUDA backend."""
+
+    def __init__(self, backend):
+        self.be = backend
+        cfg = backend.cfg
+        self.n_experts, self.top_k, self.hidden = cfg.n_experts, cfg.top_k, cfg.hidden
+
+    def route(self, layer: int, x: torch.Tensor, send_rows: torch.Tensor, counts: torch.Tensor):
+        self.be.ep_route(layer, x, send_rows, counts)
+
+    def ffn(self, layer: int, rows: torch.Tensor, counts_src: torch.Tensor, x: torch.Tensor, out_rows: torch.Tensor):
+        self.be.ep_ffn(layer, rows, counts_src, x, out_rows)
+
+    def combine(self, layer: int, returned: torch.Tensor, T: int, y: torch.Tensor):
+        self.be.ep_combine(layer, returned, T, y)
+
+
+class ExpertParallelMoE:
+    """y = shared(x) + sum_k w_k expert_k(x) with the experts sharded over `group`."""
+
+    def __init__(self, stages, group: Optional[dist.ProcessGroup] = None, max_recv_rows: Optional[int] = None):
+        self.stages = stages
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.max_recv_rows = max_recv_rows
+        self._bufs = {}
+        self.last_counts_all = None
+
+    def _buf(self, name: str, rows: int, like: torch.Tensor) -> torch.Tensor:
+        b = self._bufs.get(name)
+        if b is None or b.shape[0] < rows or b.device != like.device:
+            b = torch.empty(max(rows, 1), like.shape[1], dtype=like.dtype, device=like.device)
+            self._bufs[name] = b
+        return b
+
+    def forward(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        st = self.stages
+        T, H = x.shape
+        Tk = T * st.top_k
+        send = self._buf("send", Tk, x)
+        counts = torch.empty(st.n_experts, dtype=torch.int32, device=x.device)
+        st.route(layer, x, send, counts)
+        # every rank learns every rank's per-expert row counts (one small collective + one D2H)
+        gathered = torch.empty(self.world * st.n_experts, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(gathered, counts, group=self.group)
+        counts_all = gathered.view(self.world, st.n_experts).cpu()
+        self.last_counts_all = counts_all
+        send_splits, recv_splits, counts_src = plan_exchange(counts_all, self.rank, self.world)
+        n_recv = int(sum(recv_splits))
+        if self.max_recv_rows is not None and n_recv > self.max_recv_rows:
+            raise RuntimeError(f"{n_recv} rows arrive at rank {self.rank}, more than the {self.max_recv_rows} planned for")
+        recv = self._buf("recv", n_recv, x)
+        dist.all_to_all_single(recv[:n_recv], send[:Tk], recv_splits, send_splits, group=self.group)
+        out_rows = self._buf("out", n_recv, x)
+        st.ffn(layer, recv[:n_recv], counts_src, x, out_rows[:n_recv])
+        returned = self._buf("ret", Tk, x)
+        dist.all_to_all_single(returned[:Tk], out_rows[:n_recv], send_splits, recv_splits, group=self.group)
+        y = torch.empty_like(x)
+        st.combine(layer, returned[:Tk], T, y)
+        return y

@@ -233,11 +233,35 @@ int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl);
 
 /* ---- device-resident fast path (no host staging, used by the Python integration, the
  *      benchmark and expert-parallel drivers; stream is a cudaStream_t or NULL) ----------- */
+/* All later work of this backend runs on `cuda_stream` (NULL = CUDA's default stream);
+ * (void*)-1 returns to the backend's own non-blocking stream. */
 int32_t ek_set_stream(ek_backend_t* be, void* cuda_stream);
 /* Same as ek_moe_forward_fused with device pointers, asynchronous on the backend stream. */
 int32_t ek_moe_forward_fused_async(ek_backend_t* be, int32_t layer, const void* x_dev, int32_t T,
                                    void* y_dev);
 int32_t ek_sync(ek_backend_t* be);
+
+/* ---- expert-parallel stages ------------------------------------------------------------------
+ * The reference shards experts over worker processes and moves rows by one gRPC per expert
+ * (ek-computation/src/controller/executor.rs:141-226).  Here expert e of a layer lives on rank
+ * e / (n_experts / ep_size) of one multi-GPU box and rows move by all-to-all over NVLink, which
+ * the caller performs between these three stages (see ek_b200/ep.py).  All pointers are device
+ * pointers; all work is asynchronous on the backend stream (ek_set_stream / ek_sync).
+ *
+ * 1. ek_ep_route: route this rank's tokens over ALL experts and gather their rows in global expert
+ *    order into send_rows_dev[T*k, H] (rows of one destination rank are contiguous).
+ *    counts_dev[n_experts] receives the rows per expert.
+ * 2. ek_ep_ffn: rows_dev holds what arrived, ordered by (source rank, local expert);
+ *    counts_src_host[ep_size][n_experts/ep_size] (HOST) gives the row count of each such segment.
+ *    Runs this rank's experts on them, and the shared expert on the local tokens x_dev[T,H];
+ *    out_rows_dev receives the expert outputs in the same arrival order.
+ * 3. ek_ep_combine: returned_rows_dev[T*k, H] are the outputs sent back by the owners, in the
+ *    order of stage 1's send rows; y_dev[T,H] = sum_k w*out + shared(x). */
+int32_t ek_ep_route(ek_backend_t* be, int32_t layer, const void* x_dev, int32_t T, void* send_rows_dev,
+                    int32_t* counts_dev);
+int32_t ek_ep_ffn(ek_backend_t* be, int32_t layer, const void* rows_dev, const int32_t* counts_src_host,
+                  const void* x_dev, int32_t T, void* out_rows_dev);
+int32_t ek_ep_combine(ek_backend_t* be, int32_t layer, const void* returned_rows_dev, int32_t T, void* y_dev);
 
 /* ---- allocation-free bucketing ------------------------------------------------------------
  * No counterpart in the reference.  Some callers are not allowed to allocate device memory (a

@@ -1,0 +1,130 @@
+"""One rank of the expert-parallel tests (launched by torch.distributed.run).
+
+  python -m torch.distributed.run --nproc-per-node N tests/ep_worker.py {cpu|gpu}
+
+cpu: gloo, CPU tensors, the three stages served by the CPU oracle (checks the exchange plan, the
+     arrival-order bookkeeping and the collectives' split sizes without a GPU);
+gpu: nccl, one GPU per rank, the stages served by the CUDA backend.
+Each rank owns a slice of a global batch; the result must match the single-process oracle."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "expert-kit_b200"), os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+from oracle import configs as OC          # noqa: E402
+from oracle import ek_oracle as O         # noqa: E402
+from ek_b200.ep import ExpertParallelMoE, plan_exchange  # noqa: E402
+
+
+class OracleStages:
+    """CPU stand-in with the interface of ek_b200.ep.BackendStages; holds only this rank's experts."""
+
+    def __init__(self, cfg, layer, rank, world):
+        self.cfg, self.layer = cfg, layer
+        self.n_experts, self.top_k, self.hidden = cfg.n_experts, cfg.top_k, cfg.hidden
+        self.el = cfg.n_experts // world
+        self.lo = rank * self.el
+        self.local = {self.lo + i: layer["experts"][self.lo + i] for i in range(self.el)}
+
+    def route(self, layer_idx, x, send_rows, counts):
+        _, ids, w = O.route(self.cfg, x, self.layer["wg"], self.layer["bias"])
+        c, off, perm = O.bucket(ids, self.n_experts)
+        self.w, self.perm = w, perm
+        send_rows[:perm.numel()] = x[(perm // self.top_k).long()]
+        counts.copy_(c)
+
+    def ffn(self, layer_idx, rows, counts_src, x, out_rows):
+        pos = 0
+        for s in range(counts_src.shape[0]):
+            for le in range(self.el):
+                n = int(counts_src[s, le])
+                if n:
+                    up, gate, down = self.local[self.lo + le].bf16()
+                    out_rows[pos:pos + n] = O.expert_ffn(rows[pos:pos + n], up, gate, down)
+                    pos += n
+        self.shared_out = None
+        if self.layer["shared"] is not None:
+            self.shared_out = O.expert_ffn(x, *self.layer["shared"].bf16())
+
+    def combine(self, layer_idx, returned, T, y):
+        k = self.top_k
+        outs = torch.empty(T, k, self.hidden, dtype=torch.bfloat16)
+        outs.view(T * k, self.hidden)[self.perm.long()] = returned
+        r = O.combine(outs, self.w, self.cfg.bf16_combine)
+        if self.shared_out is not None:
+            r = r + self.shared_out
+        y.copy_(r)
+
+
+def main():
+    mode = sys.argv[1]
+    import datetime
+    dist.init_process_group("gloo" if mode == "cpu" else "nccl", timeout=datetime.timedelta(seconds=90))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    if mode == "cpu":
+        cfg = O.MoEConfig(hidden=64, intermediate=32, n_experts=8, top_k=3, scoring=O.SCORE_SIGMOID, n_group=4,
+                          topk_group=3, routed_scaling=2.5, n_shared=1)
+        T_global = 20 + world
+    else:
+        cfg = OC.config(1)
+        cfg.quant = "fp8"
+        T_global = 48 * world + 3
+    layer = OC.make_layer(cfg, 777)
+    x = OC.make_inputs(cfg, T_global, 778)
+    ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
+    # ragged split of the global batch
+    bounds = [T_global * r // world + (1 if 0 < r < world else 0) for r in range(world + 1)]
+    lo, hi = bounds[rank], bounds[rank + 1]
+    if mode == "cpu":
+        stages = OracleStages(cfg, layer, rank, world)
+        xl = x[lo:hi].contiguous()
+        be = None
+    else:
+        import ek_b200
+        import helpers as Hh
+        from ek_b200.backend import expert_tensors
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=T_global, device=torch.cuda.current_device(),
+                                               ep_rank=rank, ep_size=world))
+        be.register_router(0, layer["wg"], layer["bias"])
+        el = cfg.n_experts // world
+        for e in range(rank * el, (rank + 1) * el):
+            w = layer["experts"][e]
+            be.register_expert(be.expert_id(0, e), expert_tensors(0, e, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
+        w = layer["shared"]
+        be.register_expert(be.shared_id(0), expert_tensors(0, None, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s,
+                                                           shared=True))
+        be.set_stream(torch.cuda.current_stream().cuda_stream)
+        stages = ek_b200.BackendStages(be)
+        xl = x[lo:hi].contiguous().cuda()
+    moe = ExpertParallelMoE(stages)
+    for _ in range(2):                      # twice: buffers and staging areas are reused
+        y = moe.forward(0, xl)
+    if be is not None:
+        be.sync()
+    y = y.cpu()
+    # plan consistency: what I send to d equals what d expects from me
+    sp, rp, cs = plan_exchange(moe.last_counts_all, rank, world)
+    assert sum(sp) == (hi - lo) * cfg.top_k
+    assert int(cs.sum()) == sum(rp)
+    want = ref["y"][lo:hi]
+    d = (y.float() - want.float()).abs()
+    max_rel = (d.max() / want.float().abs().max()).item()
+    ok = max_rel <= 2e-2 and d.mean().item() <= 1e-3
+    print(f"rank {rank}/{world} tokens {hi - lo} max-rel {max_rel:.3e} mean-abs {d.mean().item():.3e} {'OK' if ok else 'FAIL'}",
+          flush=True)
+    if be is not None:
+        be.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

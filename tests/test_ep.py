@@ -1,0 +1,50 @@
+"""Expert-parallel path: exchange plan (pure host logic) and a two-rank run over gloo on CPU with
+the stages served by the oracle; the same worker runs on GPUs with NCCL (marked gpu, needs >= 2)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _launch(n, mode, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "ep_worker.py"), mode]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+
+
+def test_plan_exchange_is_consistent():
+    from ek_b200.ep import plan_exchange
+    g = torch.Generator().manual_seed(1)
+    world, E = 4, 16
+    counts_all = torch.randint(0, 5, (world, E), generator=g, dtype=torch.int32)
+    plans = [plan_exchange(counts_all, r, world) for r in range(world)]
+    for r in range(world):
+        send, recv, cs = plans[r]
+        assert sum(send) == int(counts_all[r].sum())
+        for d in range(world):
+            assert send[d] == plans[d][1][r]                # what r sends to d is what d expects from r
+        assert cs.shape == (world, E // world)
+        assert [int(x) for x in cs.sum(1)] == recv
+    with pytest.raises(ValueError):
+        plan_exchange(counts_all[:, :15], 0, world)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_over_gloo_matches_single_process_oracle(world):
+    r = _launch(world, "cpu", 29600 + world)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == world
+
+
+@pytest.mark.gpu
+def test_expert_parallel_over_nccl_matches_oracle():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    r = _launch(2, "gpu", 29650)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == 2
