@@ -279,7 +279,8 @@ def workload_config(T: int, n_gpus: int, n_exp: int = E):
             "tokens_per_gpu": T // n_gpus,
             "parallelism": "single GPU" if n_gpus == 1 else
             f"ep{n_gpus}: {n_exp // n_gpus} routed experts per GPU, shared expert and router replicated, "
-            "NCCL all-to-all dispatch/combine over NVLink, global batch fixed (strong scaling)",
+            "NCCL over NVLink (all-gather + reduce-scatter of fp32 partial sums for decode-sized batches, "
+            "all-to-all dispatch/combine above 2048 tokens), global batch fixed (strong scaling)",
             "l2": "weights streamed per step (11.3 GB) exceed the 126 MB L2; no flush needed"}
 
 
@@ -302,7 +303,7 @@ def main_ep(args, rank: int, world: int, local: int):
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
-    moe = ek_b200.ExpertParallelMoE(ek_b200.BackendStages(be))
+    moe = ek_b200.ExpertParallelMoE(ek_b200.BackendStages(be), mode=args.ep_mode)
     g = torch.Generator(device=dev).manual_seed(17 + rank)
     xs = [torch.randn(Tl, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(4)]
     for i in range(args.warmup):
@@ -337,9 +338,11 @@ def main_ep(args, rank: int, world: int, local: int):
             samples.setdefault(k_, []).append(v)
     be.stage_timing(False)
     stage = {k_: statistics.median(v) for k_, v in samples.items()}
-    counts_all = moe.last_counts_all
     el = n_exp // world
-    mine = counts_all[:, rank * el:(rank + 1) * el].sum(0)
+    if moe.last_counts_all is not None and args.ep_mode == "a2a":
+        mine = moe.last_counts_all[:, rank * el:(rank + 1) * el].sum(0)
+    else:   # gather scheme: this rank routed the whole global batch itself
+        mine = be.expert_counts(0)[rank * el:(rank + 1) * el]
     active = int((mine > 0).sum())
     rows = int(mine.sum()) + NSHARED * Tl
     # keep every GPU under the same load for about half a second so that the clock sampler sees it;
@@ -417,6 +420,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--sweep", default="", help="comma-separated extra token counts reported under 'sweep'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-mode", default="auto", choices=["auto", "gather", "a2a"],
+                    help="exchange scheme at N > 1 (auto: all-gather/reduce-scatter up to 2048 global tokens)")
     ap.add_argument("--experts", type=int, default=E,
                     help="routed experts (default: the full 256; smaller values give profiler-sized cases)")
     args = ap.parse_args()

@@ -366,12 +366,21 @@ int check_status(ek_backend* be) {
 // Stage timers, routing, bucketing, gather, FFN, combine on device buffers.  `x` is a device
 // pointer to [T,H]; result in `y` (device [T,H]) or, for the controller-level call
 // (given_ids != nullptr), in `out_tk` (device [T,k,H]).
+// Expert-parallel variant of the fused call: the shared expert runs on the token slice
+// [sh_t0, sh_t0 + sh_T) only and the routed (local) contributions are left as fp32 partial sums.
+struct LayerOpts {
+  int sh_t0 = 0;
+  int sh_T = -1;            // -1: all T tokens
+  float* partial = nullptr; // [T,H] fp32 instead of y
+};
+
 int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, const int32_t* given_ids_dev,
-              __nv_bfloat16* y, __nv_bfloat16* out_tk) {
+              __nv_bfloat16* y, __nv_bfloat16* out_tk, const LayerOpts& opt = LayerOpts()) {
   const ek_config_t& c = be->cfg;
   const int Tk = T * k;
   const bool fused = given_ids_dev == nullptr;
   const int n_shared = fused ? c.n_shared_experts : 0;
+  const int sh_T = n_shared > 0 ? (opt.sh_T < 0 ? T : opt.sh_T) : 0;
   cudaStream_t s = be->stream;
   mark(be, 0);
   const int32_t* ids = given_ids_dev;
@@ -422,17 +431,18 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   pp.ids = ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
   pp.T = T; pp.k = k; pp.E = c.n_experts; pp.e_lo = be->e_lo; pp.e_hi = be->e_hi;
   be->launches += launch_permute(pp, s);
-  const int nmax = pick_nmax(Tk, be->n_local);
+  // expected rows per local expert: Tk / n_experts whatever the sharding
+  const int nmax = pick_nmax((int)((int64_t)Tk * be->n_local / c.n_experts), be->n_local);
   WorklistParams wp;
   wp.counts = be->counts; wp.offsets = be->offsets; wp.registered = L.registered;
   wp.chunks = be->chunks; wp.n_chunks = be->n_chunks;
   wp.E = c.n_experts; wp.e_lo = be->e_lo; wp.e_hi = be->e_hi;
   wp.chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
-  wp.n_shared = n_shared; wp.T = T; wp.Tk = Tk;
+  wp.n_shared = sh_T > 0 ? n_shared : 0; wp.T = sh_T; wp.Tk = Tk;
   wp.max_chunks = be->max_chunks;
   wp.status = be->status;
   be->launches += launch_worklist(wp, s);
-  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, n_shared > 0, s);
+  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T, s);
   cudaMemcpyAsync(L.last_counts, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s);
   L.have_counts = true;
   mark(be, 2);
@@ -440,7 +450,14 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   mark(be, 3);
   run_ffn(be, L, nmax, 1);
   mark(be, 4);
-  if (fused) {
+  if (fused && opt.partial) {
+    CombineParams cp;
+    cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = nullptr;
+    cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = 0; cp.Tk = Tk;
+    cp.bf16_products = c.bf16_combine;
+    cp.shared = nullptr;
+    be->launches += launch_combine_partial(cp, opt.partial, s);
+  } else if (fused) {
     CombineParams cp;
     cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = y;
     cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = n_shared; cp.Tk = Tk;
@@ -1277,7 +1294,7 @@ int32_t ek_ep_route(ek_backend_t* be, int32_t layer, const void* x_dev, int32_t 
   pp.T = T; pp.k = c.top_k; pp.E = c.n_experts; pp.e_lo = 0; pp.e_hi = c.n_experts;
   be->launches += launch_permute(pp, s);
   be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, reinterpret_cast<__nv_bfloat16*>(send_rows_dev),
-                                T, c.top_k, c.hidden, 0, s);
+                                T, c.top_k, c.hidden, 0, 0, s);
   CK(cudaMemcpyAsync(counts_dev, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s));
   CK(cudaMemcpyAsync(L.last_counts, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s));
   L.have_counts = true;
@@ -1398,6 +1415,46 @@ int32_t ek_ep_combine(ek_backend_t* be, int32_t layer, const void* returned_rows
   cp.bf16_products = c.bf16_combine;
   cp.shared = be->obuf + (size_t)be->ep_rows * c.hidden;   // shared expert rows of the last ek_ep_ffn
   be->launches += launch_combine(cp, be->stream);
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+// Expert parallelism without data-dependent exchange sizes (decode-sized batches): every rank
+// holds all T_all tokens (all-gathered by the caller), routes them, runs ITS experts on the rows
+// routed to them and leaves fp32 partial sums for all tokens; the caller sums the partials across
+// ranks (reduce-scatter) and calls ek_ep_finish on its own token slice.
+int32_t ek_ep_partial(ek_backend_t* be, int32_t layer, const void* x_all_dev, int32_t T_all, int32_t t0,
+                      int32_t T_local, float* partial_dev) {
+  if (!be || !x_all_dev || !partial_dev) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (T_all < 1 || T_all > c.max_tokens) return fail(be, EK_INVALID_INPUT, "T_all=%d outside [1,%d]", T_all, c.max_tokens);
+  if (t0 < 0 || T_local < 0 || t0 + T_local > T_all) return fail(be, EK_INVALID_INPUT, "token slice outside the batch");
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end() || !li->second.router_w)
+    return fail(be, EK_NOT_FOUND, "layer %d has no router weight registered", layer);
+  LayerOpts opt;
+  opt.sh_t0 = t0;
+  opt.sh_T = T_local;
+  opt.partial = partial_dev;
+  be->ep_rows = T_all * c.top_k;   // shared rows start behind the routed rows
+  be->ep_T = T_local;
+  return run_layer(be, li->second, reinterpret_cast<const __nv_bfloat16*>(x_all_dev), T_all, c.top_k, nullptr,
+                   nullptr, nullptr, opt);
+}
+
+int32_t ek_ep_finish(ek_backend_t* be, int32_t layer, const float* reduced_dev, int32_t T_local, void* y_dev) {
+  (void)layer;
+  if (!be || !reduced_dev || !y_dev) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (T_local < 1 || T_local > c.max_tokens) return fail(be, EK_INVALID_INPUT, "T_local out of range");
+  if (c.n_shared_experts > 0 && be->ep_T != T_local) return fail(be, EK_INVALID_INPUT, "ek_ep_partial must run on the same slice first");
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  be->launches += launch_combine_finish(reduced_dev, be->obuf + (size_t)be->ep_rows * c.hidden, c.n_shared_experts,
+                                        T_local, c.hidden, reinterpret_cast<__nv_bfloat16*>(y_dev), be->stream);
   CK(cudaGetLastError());
   return EK_OK;
 }

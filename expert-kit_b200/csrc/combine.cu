@@ -101,6 +101,67 @@ __global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __r
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
 }
 
+__global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, float* __restrict__ partial) {
+  __shared__ int s_row[kMaxK];
+  __shared__ float s_w[kMaxK];
+  const int t = blockIdx.x;
+  if (threadIdx.x < p.k) {
+    s_row[threadIdx.x] = p.inv[(size_t)t * p.k + threadIdx.x];
+    s_w[threadIdx.x] = p.weights[(size_t)t * p.k + threadIdx.x];
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < p.H / 8; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.k; ++s) {
+      const int row = s_row[s];
+      if (row < 0) continue;
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.obuf + (size_t)row * p.H + v * 8), f);
+      const float w = s_w[s];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        acc[j] = __fadd_rn(acc[j], p.bf16_products ? round_bf16(__fmul_rn(w, f[j])) : __fmul_rn(w, f[j]));
+    }
+    float4* d = reinterpret_cast<float4*>(partial + (size_t)t * p.H + v * 8);
+    d[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    d[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
+__global__ void __launch_bounds__(256) combine_finish_kernel(const float* __restrict__ reduced,
+                                                             const __nv_bfloat16* __restrict__ shared,
+                                                             int32_t n_shared, int32_t T, int32_t H,
+                                                             __nv_bfloat16* __restrict__ y) {
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+    const float4* r = reinterpret_cast<const float4*>(reduced + (size_t)t * H + v * 8);
+    const float4 a = r[0], b = r[1];
+    float acc[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    if (n_shared > 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = round_bf16(acc[j]);
+      float sh[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sh[j] = 0.f;
+      for (int q = 0; q < n_shared; ++q) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(shared + ((size_t)q * T + t) * H + v * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sh[j] += f[j];
+      }
+      if (n_shared > 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sh[j] = round_bf16(sh[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += sh[j];
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)t * H + v * 8) = pack8(acc);
+  }
+}
+
 // One CTA per (segment, row-in-segment): rows move between arrival order and expert order.
 __global__ void __launch_bounds__(128) segment_copy_kernel(const __nv_bfloat16* __restrict__ src,
                                                            __nv_bfloat16* __restrict__ dst,
@@ -121,6 +182,16 @@ int launch_segment_copy(const __nv_bfloat16* src, __nv_bfloat16* dst, const RowS
   dim3 grid(max_rows_per_seg, n_segs);
   segment_copy_kernel<<<grid, 128, 0, s>>>(src, dst, segs, H);
   return 1;
+}
+
+int launch_combine_partial(const CombineParams& p, float* partial, cudaStream_t s) {
+  if (p.T > 0) combine_partial_kernel<<<p.T, 256, 0, s>>>(p, partial);
+  return p.T > 0 ? 1 : 0;
+}
+int launch_combine_finish(const float* reduced, const __nv_bfloat16* shared, int32_t n_shared, int32_t T,
+                          int32_t H, __nv_bfloat16* y, cudaStream_t s) {
+  if (T > 0) combine_finish_kernel<<<T, 256, 0, s>>>(reduced, shared, n_shared, T, H, y);
+  return T > 0 ? 1 : 0;
 }
 
 int launch_combine(const CombineParams& p, cudaStream_t s) {

@@ -130,8 +130,9 @@ int launch_worklist(const WorklistParams& p, cudaStream_t s);
 
 // rows [0,Tk): xp[r] = x[perm[r]/k]; rows [Tk, Tk+T) = x (only when with_shared)
 // `n_routed` (device) = number of permuted rows that exist on this rank (offsets[E]).
+// The shared expert's rows are tokens [shared_t0, shared_t0 + shared_T) of x (shared_T = 0: none).
 int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_routed,
-                  __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t with_shared,
+                  __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t shared_t0, int32_t shared_T,
                   cudaStream_t s);
 
 struct FfnParams {
@@ -171,6 +172,12 @@ struct CombineParams {
   const __nv_bfloat16* shared; // [n_shared*T, H]; null: obuf + Tk*H
 };
 int launch_combine(const CombineParams& p, cudaStream_t s);
+// Expert-parallel partial sums: partial[t,:] = sum over the slots whose expert is local of
+// w[t,k] * out[t,k,:] in fp32 (no shared expert, no rounding); and the finish after the
+// cross-rank sum: y[i,:] = bf16(reduced[i,:]) + shared rows.
+int launch_combine_partial(const CombineParams& p, float* partial, cudaStream_t s);
+int launch_combine_finish(const float* reduced, const __nv_bfloat16* shared, int32_t n_shared, int32_t T,
+                          int32_t H, __nv_bfloat16* y, cudaStream_t s);
 // out[t,s,:] = obuf[inv[t*k+s]]
 int launch_unpermute(const __nv_bfloat16* obuf, const int32_t* inv, __nv_bfloat16* out, int32_t T,
                      int32_t k, int32_t H, cudaStream_t s);

@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __rest
                                                      const int32_t* __restrict__ perm,
                                                      const int32_t* __restrict__ n_routed,
                                                      __nv_bfloat16* __restrict__ xp, int32_t T,
-                                                     int32_t k, int32_t H) {
+                                                     int32_t k, int32_t H, int32_t shared_t0) {
   const int r = blockIdx.x;
   const int Tk = T * k;
   int src;
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __rest
     if (r >= *n_routed) return;   // rows of non-local experts are not materialised
     src = perm[r] / k;
   } else {
-    src = r - Tk;
+    src = shared_t0 + r - Tk;     // the shared expert's tokens: a slice of x starting at shared_t0
   }
   const uint4* s = reinterpret_cast<const uint4*>(x + (size_t)src * H);
   uint4* d = reinterpret_cast<uint4*>(xp + (size_t)r * H);
@@ -201,10 +201,10 @@ int launch_worklist(const WorklistParams& p, cudaStream_t s) {
 }
 
 int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_routed,
-                  __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t with_shared,
+                  __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t shared_t0, int32_t shared_T,
                   cudaStream_t s) {
-  const int rows = T * k + (with_shared ? T : 0);
-  if (rows > 0) gather_kernel<<<rows, 128, 0, s>>>(x, perm, n_routed, xp, T, k, H);
+  const int rows = T * k + shared_T;
+  if (rows > 0) gather_kernel<<<rows, 128, 0, s>>>(x, perm, n_routed, xp, T, k, H, shared_t0);
   return rows > 0 ? 1 : 0;
 }
 

@@ -236,6 +236,15 @@ class Backend:
         self._check(self._lib.ek_ep_ffn(self._h, layer, _ptr(rows) if rows.numel() else None, _ptr(counts_src), _ptr(x),
                                         x.shape[0], _ptr(out_rows) if out_rows.numel() else None))
 
+    def ep_partial(self, layer: int, x_all: torch.Tensor, t0: int, T_local: int, partial: torch.Tensor):
+        assert x_all.is_cuda and partial.is_cuda and partial.dtype == torch.float32
+        assert x_all.dtype == torch.bfloat16 and x_all.is_contiguous() and partial.is_contiguous()
+        self._check(self._lib.ek_ep_partial(self._h, layer, _ptr(x_all), x_all.shape[0], t0, T_local, _ptr(partial)))
+
+    def ep_finish(self, layer: int, reduced: torch.Tensor, y: torch.Tensor):
+        assert reduced.dtype == torch.float32 and reduced.is_contiguous() and y.is_contiguous()
+        self._check(self._lib.ek_ep_finish(self._h, layer, _ptr(reduced), reduced.shape[0], _ptr(y)))
+
     def ep_combine(self, layer: int, returned: torch.Tensor, T: int, y: torch.Tensor):
         assert returned.is_contiguous() and y.is_contiguous()
         self._check(self._lib.ek_ep_combine(self._h, layer, _ptr(returned), T, _ptr(y)))

@@ -7,8 +7,9 @@ e // (n_experts // world) and rows move with two all-to-all exchanges over NVLin
 expert outputs.  Routing, bucketing, the grouped expert FFN and the weighted combine are the
 library's kernels (`ek_ep_route`, `ek_ep_ffn`, `ek_ep_combine`).
 
-One process per GPU.  The exchange plan is computed on the host from the all-gathered per-expert
-row counts; that is the one host synchronisation per layer.
+One process per GPU.  In the all-to-all scheme the exchange plan is computed on the host from the
+all-gathered per-expert row counts (one host synchronisation per layer); the gather scheme for
+decode-sized batches (`ek_ep_partial`, `ek_ep_finish`) needs none.
 """
 from __future__ import annotations
 
@@ -52,11 +53,28 @@ class BackendStages:
     def combine(self, layer: int, returned: torch.Tensor, T: int, y: torch.Tensor):
         self.be.ep_combine(layer, returned, T, y)
 
+    def partial(self, layer: int, x_all: torch.Tensor, t0: int, T_local: int, partial: torch.Tensor):
+        self.be.ep_partial(layer, x_all, t0, T_local, partial)
+
+    def finish(self, layer: int, reduced: torch.Tensor, y: torch.Tensor):
+        self.be.ep_finish(layer, reduced, y)
+
 
 class ExpertParallelMoE:
-    """y = shared(x) + sum_k w_k expert_k(x) with the experts sharded over `group`."""
+    """y = shared(x) + sum_k w_k expert_k(x) with the experts sharded over `group`.
 
-    def __init__(self, stages, group: Optional[dist.ProcessGroup] = None, max_recv_rows: Optional[int] = None):
+    Two exchange schemes:
+
+    "gather"  (default up to `gather_max_tokens` global tokens, equal batch per rank): all-gather
+              the tokens, every rank runs its experts on the rows routed to them, reduce-scatter the
+              fp32 partial sums.  Two collectives of fixed size, no host synchronisation.
+    "a2a"     rows travel only to the ranks that own their experts (two all-to-alls whose split
+              sizes come from the all-gathered per-expert counts: one host synchronisation)."""
+
+    def __init__(self, stages, group: Optional[dist.ProcessGroup] = None, max_recv_rows: Optional[int] = None,
+                 mode: str = "auto", gather_max_tokens: int = 2048):
+        self.mode = mode
+        self.gather_max_tokens = gather_max_tokens
         self.stages = stages
         self.group = group
         self.rank = dist.get_rank(group)
@@ -72,7 +90,43 @@ class ExpertParallelMoE:
             self._bufs[name] = b
         return b
 
-    def forward(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, layer: int, x: torch.Tensor, equal_batches: bool = True) -> torch.Tensor:
+        """x: this rank's tokens [T,H].  `equal_batches`: every rank passes the same T (required by
+        the "gather" scheme; with "auto" unequal batches use the all-to-all scheme)."""
+        mode = self.mode
+        if mode == "auto":
+            mode = "gather" if equal_batches and x.shape[0] * self.world <= self.gather_max_tokens else "a2a"
+        if mode == "gather":
+            return self._forward_gather(layer, x)
+        return self._forward_a2a(layer, x)
+
+    def _forward_gather(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        st = self.stages
+        T, H = x.shape
+        Ta = T * self.world
+        x_all = self._buf("x_all", Ta, x)[:Ta]
+        dist.all_gather_into_tensor(x_all.view(-1), x.reshape(-1), group=self.group)
+        part = self._bufs.get("partial")
+        if part is None or part.shape[0] < Ta or part.device != x.device:
+            part = torch.empty(Ta, H, dtype=torch.float32, device=x.device)
+            self._bufs["partial"] = part
+        part = part[:Ta]
+        st.partial(layer, x_all, self.rank * T, T, part)
+        red = self._bufs.get("reduced")
+        if red is None or red.shape[0] < T or red.device != x.device:
+            red = torch.empty(T, H, dtype=torch.float32, device=x.device)
+            self._bufs["reduced"] = red
+        red = red[:T]
+        if dist.get_backend(self.group) == "gloo":      # no reduce-scatter there
+            dist.all_reduce(part, group=self.group)
+            red.copy_(part[self.rank * T:(self.rank + 1) * T])
+        else:
+            dist.reduce_scatter_tensor(red, part, group=self.group)
+        y = torch.empty_like(x)
+        st.finish(layer, red, y)
+        return y
+
+    def _forward_a2a(self, layer: int, x: torch.Tensor) -> torch.Tensor:
         st = self.stages
         T, H = x.shape
         Tk = T * st.top_k

@@ -263,6 +263,17 @@ int32_t ek_ep_ffn(ek_backend_t* be, int32_t layer, const void* rows_dev, const i
                   const void* x_dev, int32_t T, void* out_rows_dev);
 int32_t ek_ep_combine(ek_backend_t* be, int32_t layer, const void* returned_rows_dev, int32_t T, void* y_dev);
 
+/* Expert parallelism for decode-sized batches, without data-dependent exchange sizes or host
+ * synchronisation: the caller all-gathers the tokens of all ranks into x_all_dev[T_all,H];
+ * ek_ep_partial routes all of them, runs THIS rank's experts on the rows routed to them (and the
+ * shared expert on the rank's own slice [t0, t0+T_local)) and writes fp32 partial sums
+ * partial_dev[T_all,H]; the caller sums the partials over the ranks (reduce-scatter) and
+ * ek_ep_finish turns its slice into y_dev[T_local,H] = bf16(sum) + shared(x).  Same exchange the
+ * reference performs with gRPC fan-out/fan-in (executor.rs:141-226), as two collectives. */
+int32_t ek_ep_partial(ek_backend_t* be, int32_t layer, const void* x_all_dev, int32_t T_all, int32_t t0,
+                      int32_t T_local, float* partial_dev);
+int32_t ek_ep_finish(ek_backend_t* be, int32_t layer, const float* reduced_dev, int32_t T_local, void* y_dev);
+
 /* ---- allocation-free bucketing ------------------------------------------------------------
  * No counterpart in the reference.  Some callers are not allowed to allocate device memory (a
  * worker whose memory is one pre-carved pool, a plugin running inside another runtime's step);

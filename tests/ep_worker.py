@@ -52,6 +52,25 @@ class OracleStages:
         if self.layer["shared"] is not None:
             self.shared_out = O.expert_ffn(x, *self.layer["shared"].bf16())
 
+    def partial(self, layer_idx, x_all, t0, T_local, partial):
+        cfg = self.cfg
+        _, ids, w = O.route(cfg, x_all, self.layer["wg"], self.layer["bias"])
+        partial.zero_()
+        for e in range(self.lo, self.lo + self.el):
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if tok.numel():
+                out = O.expert_ffn(x_all[tok], *self.local[e].bf16()).float()
+                partial.index_add_(0, tok, out * w[tok, slot].float().unsqueeze(-1))
+        self.shared_out = None
+        if self.layer["shared"] is not None:
+            self.shared_out = O.expert_ffn(x_all[t0:t0 + T_local], *self.layer["shared"].bf16())
+
+    def finish(self, layer_idx, reduced, y):
+        r = reduced.to(torch.bfloat16)
+        if self.shared_out is not None:
+            r = r + self.shared_out
+        y.copy_(r)
+
     def combine(self, layer_idx, returned, T, y):
         k = self.top_k
         outs = torch.empty(T, k, self.hidden, dtype=torch.bfloat16)
@@ -64,6 +83,7 @@ class OracleStages:
 
 def main():
     mode = sys.argv[1]
+    scheme = sys.argv[2] if len(sys.argv) > 2 else "a2a"
     import datetime
     dist.init_process_group("gloo" if mode == "cpu" else "nccl", timeout=datetime.timedelta(seconds=90))
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -78,8 +98,13 @@ def main():
     layer = OC.make_layer(cfg, 777)
     x = OC.make_inputs(cfg, T_global, 778)
     ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
-    # ragged split of the global batch
-    bounds = [T_global * r // world + (1 if 0 < r < world else 0) for r in range(world + 1)]
+    if scheme == "gather":        # equal batches
+        T_global -= T_global % world
+        x = x[:T_global]
+        ref = {"y": ref["y"][:T_global]}
+        bounds = [T_global * r // world for r in range(world + 1)]
+    else:                         # ragged split of the global batch
+        bounds = [T_global * r // world + (1 if 0 < r < world else 0) for r in range(world + 1)]
     lo, hi = bounds[rank], bounds[rank + 1]
     if mode == "cpu":
         stages = OracleStages(cfg, layer, rank, world)
@@ -103,16 +128,17 @@ def main():
         be.set_stream(torch.cuda.current_stream().cuda_stream)
         stages = ek_b200.BackendStages(be)
         xl = x[lo:hi].contiguous().cuda()
-    moe = ExpertParallelMoE(stages)
+    moe = ExpertParallelMoE(stages, mode=scheme)
     for _ in range(2):                      # twice: buffers and staging areas are reused
         y = moe.forward(0, xl)
     if be is not None:
         be.sync()
     y = y.cpu()
-    # plan consistency: what I send to d equals what d expects from me
-    sp, rp, cs = plan_exchange(moe.last_counts_all, rank, world)
-    assert sum(sp) == (hi - lo) * cfg.top_k
-    assert int(cs.sum()) == sum(rp)
+    if scheme == "a2a":
+        # plan consistency: what I send to d equals what d expects from me
+        sp, rp, cs = plan_exchange(moe.last_counts_all, rank, world)
+        assert sum(sp) == (hi - lo) * cfg.top_k
+        assert int(cs.sum()) == sum(rp)
     want = ref["y"][lo:hi]
     d = (y.float() - want.float()).abs()
     max_rel = (d.max() / want.float().abs().max()).item()

@@ -10,9 +10,10 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _launch(n, mode, port):
+def _launch(n, mode, port, scheme="a2a"):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "ep_worker.py"), mode]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "ep_worker.py"), mode,
+           scheme]
     return subprocess.run(cmd, capture_output=True, text=True, timeout=600)
 
 
@@ -33,18 +34,19 @@ def test_plan_exchange_is_consistent():
         plan_exchange(counts_all[:, :15], 0, world)
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_over_gloo_matches_single_process_oracle(world):
-    r = _launch(world, "cpu", 29600 + world)
+@pytest.mark.parametrize("world,scheme", [(2, "a2a"), (4, "a2a"), (2, "gather"), (4, "gather")])
+def test_expert_parallel_over_gloo_matches_single_process_oracle(world, scheme):
+    r = _launch(world, "cpu", 29600 + world + (10 if scheme == "gather" else 0), scheme)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == world
 
 
 @pytest.mark.gpu
-def test_expert_parallel_over_nccl_matches_oracle():
+@pytest.mark.parametrize("scheme", ["a2a", "gather"])
+def test_expert_parallel_over_nccl_matches_oracle(scheme):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
-    r = _launch(2, "gpu", 29650)
+    r = _launch(2, "gpu", 29650 + (1 if scheme == "gather" else 0), scheme)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == 2
