@@ -36,6 +36,7 @@ import torch  # noqa: E402
 METRIC = "MoE expert-layer tokens/s (DSV3 FP8-W/bf16-A)"
 UNIT = "tokens/s"
 H, I, E, K, NSHARED = 7168, 2048, 256, 8, 1
+LAYERS_NOTE = ""
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1590.0
 
@@ -158,7 +159,7 @@ def quantize_fp8_block_dev(w: torch.Tensor):
 
 
 def build_backend(T_max: int, rank: int = 0, seed: int = 3000, n_experts: int = E, ep_rank: int = 0,
-                  ep_size: int = 1):
+                  ep_size: int = 1, n_layers: int = 1):
     """Registers the router, the shared expert and the routed experts this rank owns
     (all of them at ep_size 1).  The router weight is the same on every rank."""
     import ek_b200
@@ -166,24 +167,25 @@ def build_backend(T_max: int, rank: int = 0, seed: int = 3000, n_experts: int = 
     dev = torch.device("cuda", torch.cuda.current_device())
     cfg = ek_b200.BackendConfig(hidden=H, intermediate=I, n_experts=n_experts, top_k=K, scoring=1, n_group=8,
                                 topk_group=4, norm_topk_prob=True, routed_scaling=2.5, n_shared_experts=NSHARED,
-                                bf16_combine=False, quant=1, max_tokens=T_max, max_layers=1,
+                                bf16_combine=False, quant=1, max_tokens=T_max, max_layers=n_layers,
                                 device=dev.index, ep_rank=ep_rank, ep_size=ep_size, model_name="dsv3")
     be = ek_b200.Backend(cfg)
-    g = torch.Generator(device=dev).manual_seed(seed)
-    wg = (torch.randn(n_experts, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-    be.register_router(0, wg, torch.zeros(n_experts, device=dev))
-    g = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
     el = n_experts // ep_size
-    for e in list(range(ep_rank * el, (ep_rank + 1) * el)) + ["shared"]:
-        mats = []
-        for shape in ((I, H), (I, H), (H, I)):
-            w = torch.randn(shape, generator=g, device=dev) * 0.02
-            mats.append(quantize_fp8_block_dev(w))
-        (up, us), (gate, gs), (down, ds) = mats
-        if e == "shared":
-            be.register_expert(be.shared_id(0), expert_tensors(0, None, up, gate, down, us, gs, ds, shared=True))
-        else:
-            be.register_expert(be.expert_id(0, e), expert_tensors(0, e, up, gate, down, us, gs, ds))
+    for layer in range(n_layers):
+        g = torch.Generator(device=dev).manual_seed(seed + 1000 * layer)
+        wg = (torch.randn(n_experts, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        be.register_router(layer, wg, torch.zeros(n_experts, device=dev))
+        g = torch.Generator(device=dev).manual_seed(seed + 1000 * layer + 1 + rank)
+        for e in list(range(ep_rank * el, (ep_rank + 1) * el)) + ["shared"]:
+            mats = []
+            for shape in ((I, H), (I, H), (H, I)):
+                w = torch.randn(shape, generator=g, device=dev) * 0.02
+                mats.append(quantize_fp8_block_dev(w))
+            (up, us), (gate, gs), (down, ds) = mats
+            if e == "shared":
+                be.register_expert(be.shared_id(layer), expert_tensors(layer, None, up, gate, down, us, gs, ds, shared=True))
+            else:
+                be.register_expert(be.expert_id(layer, e), expert_tensors(layer, e, up, gate, down, us, gs, ds))
     return be, dev
 
 
@@ -273,6 +275,7 @@ def run_reference(args):
 
 def workload_config(T: int, n_gpus: int, n_exp: int = E):
     return {"workload": f"cfg3 DeepSeek-V3-shape MoE layer, W8A16 (fp8 e4m3 + 128x128 fp32 block scales), global batch T={T} tokens"
+                        + LAYERS_NOTE
                         + ("" if n_exp == E else f" [REDUCED to {n_exp} routed experts: profiling case, not the benchmark]"),
             "hidden": H, "intermediate": I, "experts": n_exp, "shared_experts": NSHARED, "top_k": K,
             "routing": "sigmoid, 8 groups, top-4 groups, renormalised, x2.5", "global_tokens": T,
@@ -299,11 +302,26 @@ def main_ep(args, rank: int, world: int, local: int):
         raise SystemExit("--tokens must be divisible by the number of GPUs")
     Tl = T // world
     n_exp = args.experts
-    be, dev = build_backend(max(T, 256), rank, n_experts=n_exp, ep_rank=rank, ep_size=world)
+    NL = args.layers
+    be, dev = build_backend(max(T, 256), rank, n_experts=n_exp, ep_rank=rank, ep_size=world, n_layers=NL)
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
-    moe = ek_b200.ExpertParallelMoE(ek_b200.BackendStages(be), mode=args.ep_mode)
+    moe_one = ek_b200.ExpertParallelMoE(ek_b200.BackendStages(be), mode=args.ep_mode)
+
+    class _Stack:
+        """One step = every layer of the stack on its own seeded hidden states (the attention
+        blocks between the MoE layers are not part of this path)."""
+        last_counts_all = None
+
+        def forward(self, _layer, x):
+            y = None
+            for layer in range(NL):
+                y = moe_one.forward(layer, x)
+            self.last_counts_all = moe_one.last_counts_all
+            return y
+
+    moe = _Stack() if NL > 1 else moe_one
     g = torch.Generator(device=dev).manual_seed(17 + rank)
     xs = [torch.randn(Tl, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(4)]
     for i in range(args.warmup):
@@ -366,10 +384,10 @@ def main_ep(args, rank: int, world: int, local: int):
     sc = 12 * (I // 128) * (H // 128)
     bytes_rank = (active + NSHARED) * (3 * H * I + sc) + 2 * H * n_exp + 4 * Tl * H
     flops_rank = 2 * Tl * H * n_exp + 6 * H * I * (rows)
-    roof_s = max(bytes_rank / (P["hbm"] * 1e9), flops_rank / (P["tf_sus"] * 1e12))
+    roof_s = NL * max(bytes_rank / (P["hbm"] * 1e9), flops_rank / (P["tf_sus"] * 1e12))   # per step
     nvlink_bytes = 2 * Tl * K * H * 2 * (1 - 1 / world)
     layer = {"roofline_tokens_per_s": T / roof_s, "frac": roof_s * 1e3 / ms_step, "bound": "hbm",
-             "bytes_per_gpu": bytes_rank, "flops_per_gpu": flops_rank, "active_experts_rank0": active,
+             "layers": NL, "bytes_per_gpu_per_layer": bytes_rank, "flops_per_gpu_per_layer": flops_rank, "active_experts_rank0": active,
              "nvlink_bytes_per_gpu_per_step": int(nvlink_bytes), "stage_ms_rank0": stage}
 
     # end to end: host batch in, host result out, through the public Python API of this package
@@ -420,12 +438,17 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--sweep", default="", help="comma-separated extra token counts reported under 'sweep'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=1,
+                    help="MoE layers per step (58 = the full DeepSeek-V3 expert stack; each layer has its own weights)")
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "gather", "a2a"],
                     help="exchange scheme at N > 1 (auto: all-gather/reduce-scatter up to 2048 global tokens)")
     ap.add_argument("--experts", type=int, default=E,
                     help="routed experts (default: the full 256; smaller values give profiler-sized cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    global LAYERS_NOTE
+    if args.layers > 1:
+        LAYERS_NOTE = f" x {args.layers} layers per step (cfg5-style expert stack)"
     if args.impl == "reference":
         return run_reference(args)
 

@@ -243,10 +243,13 @@ int ensure_layer(ek_backend* be, int layer, Layer** out) {
     CK(cudaMalloc(&L.gu_scale, (size_t)be->n_slots * d.it * d.kt_gu * 2 * sizeof(float)));
     CK(cudaMalloc(&L.dn_scale, (size_t)be->n_slots * d.hp * d.kt_dn * 2 * sizeof(float)));
   }
+  // clear on the load stream and wait: the backend's streams are non-blocking, so a memset on the
+  // default stream could land after a later flag update
   CK(cudaMalloc(&L.registered, sizeof(int32_t) * be->n_slots));
-  CK(cudaMemset(L.registered, 0, sizeof(int32_t) * be->n_slots));
+  CK(cudaMemsetAsync(L.registered, 0, sizeof(int32_t) * be->n_slots, be->load_stream));
   CK(cudaMalloc(&L.last_counts, sizeof(int32_t) * be->cfg.n_experts));
-  CK(cudaMemset(L.last_counts, 0, sizeof(int32_t) * be->cfg.n_experts));
+  CK(cudaMemsetAsync(L.last_counts, 0, sizeof(int32_t) * be->cfg.n_experts, be->load_stream));
+  CK(cudaStreamSynchronize(be->load_stream));
   L.host_registered.assign(be->n_slots, 0);
   auto ins = be->layers.emplace(layer, L);
   *out = &ins.first->second;
@@ -623,6 +626,11 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
 #undef CKC
   int rc = make_maps(be);
   if (rc != EK_OK) return cleanup_fail(rc);
+  // the memsets above ran on the default stream; the backend's own streams do not wait for it
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    fail(be, EK_CUDA, "device synchronisation failed after workspace set-up");
+    return cleanup_fail(EK_CUDA);
+  }
   const char* impl = getenv("EK_B200_FFN_IMPL");
   if (impl && std::string(impl) == "simt") be->ffn_impl = 1;
   const char* prec = getenv("EK_B200_PRECISE_DEQUANT");
@@ -937,6 +945,9 @@ int32_t ek_router_register(ek_backend_t* be, int32_t layer, const void* weight, 
     CK(cudaMalloc(&L->router_bias, sizeof(float) * be->cfg.n_experts));
     CK(cudaMemcpy(L->router_bias, bias, sizeof(float) * be->cfg.n_experts, cudaMemcpyDefault));
   }
+  // device-to-device copies above are asynchronous on the default stream, which the backend's
+  // non-blocking streams do not wait for
+  CK(cudaDeviceSynchronize());
   return EK_OK;
 }
 

@@ -140,6 +140,7 @@ void router_tc_plan(int T, int H, int n_sm, int* n_splits, int* atoms_per_split)
   const int n_atoms = (H + 63) / 64;
   const int m_tiles = (T + kTokTile - 1) / kTokTile;
   int ks = n_sm / m_tiles;
+  if (ks > 16) ks = 16;   // the select kernel adds the partial sums serially: keep that chain short
   if (ks < 1) ks = 1;
   if (ks > n_atoms) ks = n_atoms;
   const int per = (n_atoms + ks - 1) / ks;

@@ -192,3 +192,21 @@ def test_stage_times_and_launch_counter(small):
     assert set(t) == {"route", "permute", "gateup", "down", "combine"}
     assert all(v > 0 for v in t.values())
     assert be.kernel_launches() - before == 8     # logits, select, permute, worklist, gather, gate/up, down, combine
+
+
+def test_many_layers_registered_back_to_back():
+    """Layers created and filled in quick succession (device-resident weights, no host copies to
+    slow the loader down): every layer's first expert must be usable right away."""
+    import ek_b200
+    cfg = O.MoEConfig(hidden=256, intermediate=128, n_experts=4, top_k=2, scoring=O.SCORE_SOFTMAX, quant="bf16")
+    n_layers = 12
+    be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=32, max_layers=n_layers))
+    layers = [OC.make_layer(cfg, 500 + i) for i in range(n_layers)]
+    for i, layer in enumerate(layers):
+        Hh.register_layer(be, i, layer, device="cuda")
+    x = OC.make_inputs(cfg, 24, 77)
+    for i, layer in enumerate(layers):
+        ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], None)
+        y = be.moe_forward_fused(i, x.cuda()).cpu()
+        Hh.assert_outputs_close(y, ref["y"], f"layer {i}")
+    be.close()
