@@ -438,6 +438,10 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--sweep", default="", help="comma-separated extra token counts reported under 'sweep'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--stream", type=int, default=0,
+                    help="also run a continuous-batching stream of this many steps (decode ~Poisson(96) tokens, a "
+                         "512-2048 token prefill chunk every 10th step, Zipf(1.2) expert load rotated every 200 steps, "
+                         "every expert >= 1 row) through the controller-level entry point; reported under 'stream'")
     ap.add_argument("--layers", type=int, default=1,
                     help="MoE layers per step (58 = the full DeepSeek-V3 expert stack; each layer has its own weights)")
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "gather", "a2a"],
@@ -465,7 +469,7 @@ def main():
     T = args.tokens
     sweep = [int(t) for t in args.sweep.split(",") if t]
     n_exp = args.experts
-    be, dev = build_backend(max([T] + sweep), rank, n_experts=n_exp)
+    be, dev = build_backend(max([T] + sweep + ([2400] if args.stream > 0 else [])), rank, n_experts=n_exp)
     # the library launches on this stream, so torch's events bracket exactly its kernels
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
@@ -583,6 +587,55 @@ def main():
                               "layer_roofline_frac": (rs * 1e3) / st,
                               "stage_ms": {k_: round(v, 4) for k_, v in stage_n.items()}}
 
+    stream_out = None
+    if args.stream > 0:
+        gs = torch.Generator().manual_seed(4)
+        gd = torch.Generator(device=dev).manual_seed(5)
+        zipf_p = (torch.arange(1, n_exp + 1, dtype=torch.float32, device=dev) ** -1.2)
+
+        def zipf_ids_dev(Ts, rot):
+            """k distinct experts per token from a Zipf(1.2) law over a rotated ranking; experts left
+            without a row take over the first (hottest) slot of distinct tokens."""
+            ids = torch.multinomial(zipf_p.expand(Ts, n_exp), K, replacement=False, generator=gd)
+            ids = (ids + rot) % n_exp
+            for _ in range(4):
+                present = torch.zeros(n_exp, dtype=torch.bool, device=dev)
+                present[ids.reshape(-1)] = True
+                missing = (~present).nonzero().flatten()
+                if missing.numel() == 0:
+                    break
+                ids[:missing.numel(), 0] = missing
+            return ids.to(torch.int32).contiguous()
+
+        steps = []
+        for i in range(args.stream):
+            Ts = int(torch.poisson(torch.tensor(96.0), generator=gs).item()) + 1
+            if i % 10 == 9:
+                Ts += int(torch.randint(512, 2049, (1,), generator=gs).item())
+            Ts = max(Ts, n_exp // K + 1)
+            steps.append((Ts, zipf_ids_dev(Ts, (i // 200) * 37)))
+        Tmax = max(t for t, _ in steps)
+        xb = torch.randn(Tmax, H, generator=g, device=dev).to(torch.bfloat16)
+        ob = torch.empty(Tmax * K * H, dtype=torch.bfloat16, device=dev)
+        import ctypes as C
+
+        def run_stream():
+            for Ts, ids in steps:
+                be._check(be._lib.ek_moe_forward(be._h, 0, xb.data_ptr(), Ts, ids.data_ptr(), K, ob.data_ptr()))
+
+        if Tmax <= be.cfg.max_tokens:
+            run_stream()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            run_stream()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            tok = sum(t for t, _ in steps)
+            stream_out = {"steps": args.stream, "tokens": tok, "seconds": dt, "tokens_per_s": tok / dt,
+                          "ms_per_step": dt / args.stream * 1e3}
+        else:
+            stream_out = {"skipped": f"largest step has {Tmax} tokens; rerun with --sweep {Tmax} to size the workspace"}
+
     if rank == 0:
         base = None
         if not args.no_cpu_baseline:
@@ -595,6 +648,8 @@ def main():
                 "layer_roofline": layer, "cpu_baseline": base}
         if sweep_out:
             line["sweep"] = sweep_out
+        if stream_out:
+            line["stream"] = stream_out
         print(json.dumps(line))
     be.close()
     if dist is not None:

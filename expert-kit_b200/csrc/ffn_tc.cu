@@ -33,7 +33,14 @@ namespace {
 
 using namespace ekptx;
 
-constexpr int kConvWarps = 8;
+// 8 (default) or 16 converter warps: one or two warps per (tile, lane quarter).  Measured on the
+// DeepSeek-V3 shape: 16 warps are 4-9 % slower at every batch size (more barrier traffic, no gain
+// in issue rate), so 8 it is.
+#ifndef EK_CONV_WARPS
+#define EK_CONV_WARPS 8
+#endif
+constexpr int kConvWarps = EK_CONV_WARPS;
+constexpr int kKSplit = kConvWarps / 8;      // warps sharing a tile row split its 8 chunks along K
 constexpr int kMmaWarps = 2;
 constexpr int kThreads = (kConvWarps + 1 + kMmaWarps) * 32;
 constexpr int kASlots = 4;       // A-operand staging slots in tensor memory
@@ -56,7 +63,7 @@ struct Cfg {
   static constexpr int STAGES_RAW = kSmemLimit / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int MMAS = TKE / 16;                           // MMA instructions per tile
-  static constexpr int NCH = 8;                                   // 16-byte chunks per thread (one tile row)
+  static constexpr int NCH = 8 / kKSplit;                         // 16-byte chunks per thread
   static constexpr int WPC = QUANT == EK_QUANT_BF16 ? 4 : 8;      // 32-bit A words per chunk
   static constexpr int NW = NCH * WPC;
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
@@ -183,7 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       mbar_init(smem_u32(&bar_empty[i]), kConvWarps + kMmaWarps);
     }
     for (int i = 0; i < kASlots; ++i) {
-      mbar_init(smem_u32(&bar_afull[i]), 4);
+      mbar_init(smem_u32(&bar_afull[i]), kConvWarps / 2);
       mbar_init(smem_u32(&bar_aempty[i]), 1);
     }
     mbar_init(smem_u32(&bar_accfull), kMmaWarps);
@@ -318,7 +325,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     }
   } else {
     // =============================== converters + epilogue =================================
-    const int wg = warp >> 2, q = warp & 3;
+    // warp -> (tile of the stage, K part of the tile row, lane quarter of tensor memory)
+    const int wg = warp / (4 * kKSplit), kh = (warp >> 2) % kKSplit, q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
     uint32_t it = 0, items_done = 0;
@@ -358,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         uint4 raw[C::NCH];
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j)
-          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)(j * kTileRows + r) * 16);
+          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)((kh * C::NCH + j) * kTileRows + r) * 16);
         uint32_t aw[C::NW];
         uint32_t s_hi = 0, s_lo = 0;
         if (QUANT == EK_QUANT_FP8_BLOCK128 && !PRECISE) {
@@ -371,10 +379,14 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT, PRECISE>(raw[j], scale, s_hi, s_lo, aw + j * C::WPC);
-        const uint32_t col0 = kABaseCol + a * kASlotCols;
+        const uint32_t col0 = kABaseCol + a * kASlotCols + kh * C::NW;
         tc_fence_after();
+        if (C::NW >= 32) {
 #pragma unroll
-        for (int w0 = 0; w0 < C::NW; w0 += 32) tmem_st32(lane_base + col0 + w0, aw + w0);
+          for (int w0 = 0; w0 < C::NW; w0 += 32) tmem_st32(lane_base + col0 + w0, aw + w0);
+        } else {
+          tmem_st16(lane_base + col0, aw);
+        }
         PROF_LAP(2)
         tc_wait_st();
         tc_fence_before();
@@ -397,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       // gate/up: this thread owns intermediate feature rt*128 + r (gate in accumulator 0, up in 1);
       // down: hidden features (2*rt)*128 + r (accumulator 0) and (2*rt+1)*128 + r (accumulator 1)
       const int feat = (GATEUP ? rt : 2 * rt) * kTileRows + r;
-      for (int cb = wg; cb < N / 8; cb += 2) {
+      for (int cb = warp >> 2; cb < N / 8; cb += kConvWarps / 4) {
         if (cb * 8 >= cd.n_rows) break;
         uint32_t g[8], u[8];
         tmem_ld8(lane_base + cb * 8, g);
@@ -424,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       if (lane == 0) mbar_arrive(smem_u32(&bar_accempty));
       PROF_LAP(5)
     }
-    if (lane == 0 && (warp == 0 || warp == 4)) { PROF_DUMP(2 + wg) }
+    if (lane == 0 && (warp == 0 || warp == 4 * kKSplit)) { PROF_DUMP(2 + wg) }
   }
 
   tc_fence_before();

@@ -367,3 +367,28 @@ def test_fast_and_precise_block_scaling_both_within_tolerance_at_dsv3_shape():
     # rounding the block scale to bf16 must not cost more than a fraction of the bf16 noise floor
     assert errs[False] <= errs[True] * 1.25 + 1e-5, errs
     be.close()
+
+
+def test_continuous_batching_stream_ragged_packing():
+    """A short version of the continuous-batching stream: every step mixes a Poisson number of
+    decode tokens with, every 5th step, one prefill chunk; expert load is Zipf(1.2)-skewed with the
+    hot set rotated every 10 steps and every expert receives at least one row.  Each step's
+    [T,k,H] reply must match the oracle and the per-expert counts must be exact, whatever the mix
+    of chunk sizes the work list ends up with."""
+    cfg = O.MoEConfig(hidden=256, intermediate=128, n_experts=32, top_k=4, scoring=O.SCORE_SOFTMAX, quant="fp8")
+    layer = OC.make_layer(cfg, 4242)
+    be = _backend(cfg, layer, 512)
+    g = torch.Generator().manual_seed(99)
+    for step in range(24):
+        T = int(torch.poisson(torch.tensor(24.0), generator=g).item()) + 8
+        if step % 5 == 4:
+            T += int(torch.randint(64, 200, (1,), generator=g).item())
+        ids = OC.zipf_ids(T, cfg.top_k, cfg.n_experts, 1.2, g, cover_all=True, rot=(step // 10) * 7)
+        x = OC.make_inputs(cfg, T, 5000 + step)
+        out = be.moe_forward(0, x, ids)
+        ref = O.moe_expert_outputs(x, ids, layer["experts"])
+        _close(out, ref, f"stream step {step} (T={T})")
+        counts = be.expert_counts(0)
+        assert torch.equal(counts, torch.bincount(ids.reshape(-1).long(), minlength=cfg.n_experts).to(torch.int32))
+        assert int(counts.min()) >= 1
+    be.close()
