@@ -43,10 +43,12 @@ constexpr int kConvWarps = EK_CONV_WARPS;
 constexpr int kKSplit = kConvWarps / 8;      // warps sharing a tile row split its 8 chunks along K
 constexpr int kMmaWarps = 2;
 constexpr int kThreads = (kConvWarps + 1 + kMmaWarps) * 32;
-constexpr int kASlots = 4;       // A-operand staging slots in tensor memory
-constexpr int kASlotCols = 64;   // columns per slot (128 bf16 along K)
-constexpr int kABaseCol = 256;   // accumulators live in columns [0, 256)
+constexpr int kASlotCols = 64;   // tensor-memory columns per A staging slot (128 bf16 along K)
 constexpr int kTmemCols = 512;
+#ifndef EK_MAX_A_SLOTS
+#define EK_MAX_A_SLOTS 6
+#endif
+constexpr int kMaxASlots = EK_MAX_A_SLOTS;
 constexpr int kSmemLimit = 232448 - 4096;
 
 template <int QUANT, bool GATEUP, int NMAX>
@@ -66,6 +68,12 @@ struct Cfg {
   static constexpr int NCH = 8 / kKSplit;                         // 16-byte chunks per thread
   static constexpr int WPC = QUANT == EK_QUANT_BF16 ? 4 : 8;      // 32-bit A words per chunk
   static constexpr int NW = NCH * WPC;
+  // tensor memory: two accumulators of NMAX columns, the rest is a ring of A staging slots (an
+  // even number, shared by the two chains): 6 slots for the decode variants, 4 at NMAX = 128
+  static constexpr int A_BASE = 2 * NMAX;
+  static constexpr int A_SLOTS_RAW = ((kTmemCols - A_BASE) / kASlotCols) & ~1;
+  static constexpr int A_SLOTS = A_SLOTS_RAW > kMaxASlots ? kMaxASlots : A_SLOTS_RAW;
+  static_assert(A_SLOTS >= 4, "need at least two A slots per chain");
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
 };
@@ -174,7 +182,7 @@ template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
 __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
   using C = Cfg<QUANT, GATEUP, NMAX>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_afull[kASlots], bar_aempty[kASlots];
+  __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_afull[kMaxASlots], bar_aempty[kMaxASlots];
   __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
@@ -189,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       mbar_init(smem_u32(&bar_full[i]), 1);
       mbar_init(smem_u32(&bar_empty[i]), kConvWarps + kMmaWarps);
     }
-    for (int i = 0; i < kASlots; ++i) {
+    for (int i = 0; i < C::A_SLOTS; ++i) {
       mbar_init(smem_u32(&bar_afull[i]), kConvWarps / 2);
       mbar_init(smem_u32(&bar_aempty[i]), 1);
     }
@@ -298,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           for (int j = 0; j < C::MMAS; ++j) bd[j] = b0 + (uint64_t)((j / 4) * atom_step + (j % 4) * 2);
           PROF_LAP(1)
           const uint32_t tcount = it * 2 + chain;
-          const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
+          const uint32_t a = tcount % C::A_SLOTS, aph = (tcount / C::A_SLOTS) & 1u;
           if (!mbar_wait(smem_u32(&bar_afull[a]), aph, abortp)) {
             report(p.status, DEV_TIMEOUT, 202, item, kt);
             ok = false;
@@ -306,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           }
           tc_fence_after();
           PROF_LAP(2)
-          const uint32_t a_tmem = tmem + kABaseCol + a * kASlotCols;
+          const uint32_t a_tmem = tmem + C::A_BASE + a * kASlotCols;
           if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           tc_commit(smem_u32(&bar_aempty[a]));
@@ -355,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
         PROF_LAP(0)
         const uint32_t tcount = it * 2 + wg;
-        const uint32_t a = tcount % kASlots, aph = (tcount / kASlots) & 1u;
+        const uint32_t a = tcount % C::A_SLOTS, aph = (tcount / C::A_SLOTS) & 1u;
         if (!mbar_wait(smem_u32(&bar_aempty[a]), aph ^ 1u, abortp)) {
           report(p.status, DEV_TIMEOUT, 301, item, kt);
           ok = false;
@@ -379,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT, PRECISE>(raw[j], scale, s_hi, s_lo, aw + j * C::WPC);
-        const uint32_t col0 = kABaseCol + a * kASlotCols + kh * C::NW;
+        const uint32_t col0 = C::A_BASE + a * kASlotCols + kh * C::NW;
         tc_fence_after();
         if (C::NW >= 32) {
 #pragma unroll
