@@ -981,7 +981,7 @@ int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x, int32
       cd.slot = it->second.slot + v;
       cd.in_row = cidx * chunk_rows;
       cd.out_row = v * n + cidx * chunk_rows;
-      cd.n_rows = std::min(chunk_rows, n - cidx * chunk_rows);
+      cd.n_rows = std::min(chunk_rows, n - cidx * chunk_rows) | (per > 1 ? kChunkMulti : 0);
       be->h_chunks[v * per + cidx] = cd;
     }
   const int32_t total = per * n_virtual;
@@ -1365,7 +1365,8 @@ int32_t ek_ep_ffn(ek_backend_t* be, int32_t layer, const void* rows_dev, const i
     for (int c0 = 0; c0 < n; c0 += chunk_rows) {
       if (n_chunks >= be->h_chunks_cap || n_chunks >= be->max_chunks) return false;
       ChunkDesc cd;
-      cd.slot = slot; cd.in_row = in_row + c0; cd.out_row = out_row + c0; cd.n_rows = std::min(chunk_rows, n - c0);
+      cd.slot = slot; cd.in_row = in_row + c0; cd.out_row = out_row + c0;
+      cd.n_rows = std::min(chunk_rows, n - c0) | (n > chunk_rows ? kChunkMulti : 0);
       be->h_chunks[n_chunks++] = cd;
     }
     return true;

@@ -30,8 +30,11 @@ struct ChunkDesc {
   int32_t slot;      // expert slot in the layer slab
   int32_t in_row;    // first row in the permuted activation buffer (GEMM B operand)
   int32_t out_row;   // first row in the output buffer
-  int32_t n_rows;    // valid rows (1..chunk size)
+  int32_t n_rows;    // valid rows (1..chunk size) in the low 16 bits; bit 16: the expert's rows span
+                     // several chunks, i.e. its weights are read again by the neighbouring items
 };
+constexpr int32_t kChunkRowsMask = 0xFFFF;
+constexpr int32_t kChunkMulti = 1 << 16;
 
 // Device-side error word: {code, where}.  Kernels only ever write non-zero values.
 struct DevStatus {

@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(128) simt_gateup_kernel(FfnParams p) {
   __shared__ float xs[kRows][128];
   const int c = blockIdx.x;
   if (c >= *p.n_chunks) return;
-  const ChunkDesc cd = p.chunks[c];
+  ChunkDesc cd = p.chunks[c];
+  cd.n_rows &= kChunkRowsMask;
   const int it = blockIdx.y, r = threadIdx.x;
   const int TK = QUANT == EK_QUANT_BF16 ? 64 : 128;
   float ag[kRows], au[kRows];
@@ -109,7 +110,8 @@ __global__ void __launch_bounds__(128) simt_down_kernel(FfnParams p) {
   __shared__ float xs[kRows][128];
   const int c = blockIdx.x;
   if (c >= *p.n_chunks) return;
-  const ChunkDesc cd = p.chunks[c];
+  ChunkDesc cd = p.chunks[c];
+  cd.n_rows &= kChunkRowsMask;
   const int ht = blockIdx.y, r = threadIdx.x;
   const int TK = QUANT == EK_QUANT_BF16 ? 64 : 128;
   float acc[kRows];

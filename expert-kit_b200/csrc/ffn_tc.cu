@@ -229,7 +229,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       bool ok = true;
       PROF_DECL
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        const ChunkDesc cd = p.chunks[item / n_rt];
+        ChunkDesc cd = p.chunks[item / n_rt];
+        // weights that the neighbouring items read again stay in L2; the rest is streamed through
+        const bool reread = (cd.n_rows & kChunkMulti) != 0;
+        cd.n_rows &= kChunkRowsMask;
         const int rt = item % n_rt;
         const int N = pick_n(cd.n_rows, NMAX);
         const CUtensorMap* map = maps + map_index(N);
@@ -248,7 +251,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
           mbar_arrive_expect_tx(full, C::W_BYTES + C::X_ATOMS * N * 128);
-          bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
+          if (reread) bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
+          else bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
 #pragma unroll
           for (int a = 0; a < C::X_ATOMS; ++a)
             tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
@@ -281,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       const uint32_t d_tmem = tmem + chain * NMAX;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
         const ChunkDesc cd = p.chunks[item / n_rt];
-        const int N = pick_n(cd.n_rows, NMAX);
+        const int N = pick_n(cd.n_rows & kChunkRowsMask, NMAX);
         const uint32_t idesc = umma_idesc_bf16(N);
         const uint32_t atom_step = (uint32_t)(N * 128) >> 4;   // descriptor units between 64-element K atoms
         if (!mbar_wait(smem_u32(&bar_accempty), (items_done & 1u) ^ 1u, abortp)) {
@@ -341,7 +345,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     bool ok = true;
     PROF_DECL
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
-      const ChunkDesc cd = p.chunks[item / n_rt];
+      ChunkDesc cd = p.chunks[item / n_rt];
+      cd.n_rows &= kChunkRowsMask;
       const int rt = item % n_rt;
       const int N = pick_n(cd.n_rows, NMAX);
       // block scale of this warpgroup's tile: [K step][warpgroup] in both modes

@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
         d.slot = le;
         d.in_row = off + c * p.chunk_rows;
         d.out_row = d.in_row;
-        d.n_rows = min(p.chunk_rows, cnt - c * p.chunk_rows);
+        d.n_rows = min(p.chunk_rows, cnt - c * p.chunk_rows) | (nch > 1 ? kChunkMulti : 0);
         p.chunks[first + c] = d;
       }
     }
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
     d.slot = n_local + j;
     d.in_row = p.Tk + c * p.chunk_rows;
     d.out_row = p.Tk + j * p.T + c * p.chunk_rows;
-    d.n_rows = min(p.chunk_rows, p.T - c * p.chunk_rows);
+    d.n_rows = min(p.chunk_rows, p.T - c * p.chunk_rows) | (per_shared > 1 ? kChunkMulti : 0);
     p.chunks[running + i] = d;
     if (c == 0 && !p.registered[d.slot]) {
       if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
