@@ -182,7 +182,7 @@ template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
 __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
   using C = Cfg<QUANT, GATEUP, NMAX>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[8], bar_empty[8], bar_afull[kMaxASlots], bar_aempty[kMaxASlots];
+  __shared__ __align__(8) uint64_t bar_full[8], bar_wempty[8], bar_xempty[8], bar_afull[kMaxASlots], bar_aempty[kMaxASlots];
   __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
@@ -194,8 +194,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < C::STAGES; ++i) {
-      mbar_init(smem_u32(&bar_full[i]), 1);
-      mbar_init(smem_u32(&bar_empty[i]), kConvWarps + kMmaWarps);
+      mbar_init(smem_u32(&bar_full[i]), 2);               // weight copy + activation copy
+      mbar_init(smem_u32(&bar_wempty[i]), kConvWarps);     // converters have read the weight tiles
+      mbar_init(smem_u32(&bar_xempty[i]), kMmaWarps);      // both chains' MMAs on the stage are done
     }
     for (int i = 0; i < C::A_SLOTS; ++i) {
       mbar_init(smem_u32(&bar_afull[i]), kConvWarps / 2);
@@ -221,10 +222,16 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   const int total = n_chunks * n_rt;
 
   if (warp == kConvWarps) {
-    // =============================== producer ==============================================
-    if (lane == 0) {
+    // =============================== producers =============================================
+    // Two lanes, two independent rings over the same stages: lane 0 refills the weight tiles of a
+    // stage as soon as the converters have read them, lane 1 the activation tile once both MMA
+    // chains are done with it.  The weights (the long-latency HBM stream) thereby start their next
+    // trip a whole MMA phase earlier than the activations.
+    if (lane < 2) {
+      const bool weights = lane == 0;
       const CUtensorMap* maps = GATEUP ? p.x_maps : p.h_maps;
-      const uint64_t stream_once = policy_evict_first();   // weights are read exactly once per pass
+      const uint64_t stream_once = policy_evict_first();   // weights read exactly once per pass
+      uint64_t* bar_free = weights ? bar_wempty : bar_xempty;
       uint32_t it = 0;
       bool ok = true;
       PROF_DECL
@@ -242,24 +249,28 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         const int brow = GATEUP ? cd.in_row : cd.out_row;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp)) {
-            report(p.status, DEV_TIMEOUT, 100, item, kt);
+          if (!mbar_wait(smem_u32(&bar_free[s]), ph ^ 1u, abortp)) {
+            report(p.status, DEV_TIMEOUT, weights ? 100 : 101, item, kt);
             ok = false;
             break;
           }
           PROF_LAP(0)
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
-          mbar_arrive_expect_tx(full, C::W_BYTES + C::X_ATOMS * N * 128);
-          if (reread) bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
-          else bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
+          if (weights) {
+            mbar_arrive_expect_tx(full, C::W_BYTES);
+            if (reread) bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
+            else bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
+          } else {
+            mbar_arrive_expect_tx(full, C::X_ATOMS * N * 128);
 #pragma unroll
-          for (int a = 0; a < C::X_ATOMS; ++a)
-            tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
+            for (int a = 0; a < C::X_ATOMS; ++a)
+              tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
+          }
           PROF_LAP(1)
         }
       }
-      PROF_DUMP(0)
+      if (weights) { PROF_DUMP(0) }
       // never leave with copies in flight: wait (bounded) for every stage armed in the last lap
       const uint32_t lo = it > (uint32_t)C::STAGES ? it - C::STAGES : 0;
       for (uint32_t i = lo; i < it; ++i) {
@@ -322,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           tc_commit(smem_u32(&bar_aempty[a]));
-          tc_commit(smem_u32(&bar_empty[cs]));
+          tc_commit(smem_u32(&bar_xempty[cs]));
           PROF_LAP(3)
         }
         if (ok) tc_commit(smem_u32(&bar_accfull));
@@ -406,7 +417,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(smem_u32(&bar_afull[a]));
-          mbar_arrive(smem_u32(&bar_empty[s]));
+          mbar_arrive(smem_u32(&bar_wempty[s]));
         }
         PROF_LAP(3)
       }
@@ -422,26 +433,49 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       // gate/up: this thread owns intermediate feature rt*128 + r (gate in accumulator 0, up in 1);
       // down: hidden features (2*rt)*128 + r (accumulator 0) and (2*rt+1)*128 + r (accumulator 1)
       const int feat = (GATEUP ? rt : 2 * rt) * kTileRows + r;
-      for (int cb = warp >> 2; cb < N / 8; cb += kConvWarps / 4) {
-        if (cb * 8 >= cd.n_rows) break;
-        uint32_t g[8], u[8];
-        tmem_ld8(lane_base + cb * 8, g);
-        tmem_ld8(lane_base + NMAX + cb * 8, u);
-        tc_wait_ld();
+      // Row pointers advance by a constant stride; full column blocks take a branch-free path.
+      const size_t ostride = GATEUP ? (size_t)p.d.Ip : (size_t)p.d.H;
+      __nv_bfloat16* obase = (GATEUP ? p.hbuf : p.obuf) + (size_t)cd.out_row * ostride + feat;
+      const bool f0 = GATEUP || feat < p.d.H, f1 = !GATEUP && feat + kTileRows < p.d.H;
+      auto emit = [&](__nv_bfloat16* o, float gv, float uv) {
+        if (GATEUP) {
+          *o = __float2bfloat16_rn(uv * __fdividef(gv, 1.f + __expf(-gv)));
+        } else {
+          if (f0) *o = __float2bfloat16_rn(gv);
+          if (f1) o[kTileRows] = __float2bfloat16_rn(uv);
+        }
+      };
+      if (NMAX >= 64 && N >= 64) {
+        // wide tiles: 32 columns of both accumulators per tensor-memory round trip
+        for (int cb = warp >> 2; cb < N / 32; cb += kConvWarps / 4) {
+          const int c0 = cb * 32;
+          if (c0 >= cd.n_rows) break;
+          uint32_t g[32], u[32];
+          tmem_ld32(lane_base + c0, g);
+          tmem_ld32(lane_base + NMAX + c0, u);
+          tc_wait_ld();
+          __nv_bfloat16* o = obase + (size_t)c0 * ostride;
+          if (c0 + 32 <= cd.n_rows) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int col = cb * 8 + i;
-          if (col < cd.n_rows) {
-            const float gv = __uint_as_float(g[i]), uv = __uint_as_float(u[i]);
-            if (GATEUP) {
-              const float h = uv * (gv / (1.f + __expf(-gv)));
-              p.hbuf[(size_t)(cd.out_row + col) * p.d.Ip + feat] = __float2bfloat16_rn(h);
-            } else {
-              __nv_bfloat16* o = p.obuf + (size_t)(cd.out_row + col) * p.d.H;
-              if (feat < p.d.H) o[feat] = __float2bfloat16_rn(gv);
-              if (feat + kTileRows < p.d.H) o[feat + kTileRows] = __float2bfloat16_rn(uv);
-            }
+            for (int i = 0; i < 32; ++i, o += ostride) emit(o, __uint_as_float(g[i]), __uint_as_float(u[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i, o += ostride)
+              if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(u[i]));
           }
+        }
+      } else {
+        for (int cb = warp >> 2; cb < N / 8; cb += kConvWarps / 4) {
+          const int c0 = cb * 8;
+          if (c0 >= cd.n_rows) break;
+          uint32_t g[8], u[8];
+          tmem_ld8(lane_base + c0, g);
+          tmem_ld8(lane_base + NMAX + c0, u);
+          tc_wait_ld();
+          __nv_bfloat16* o = obase + (size_t)c0 * ostride;
+#pragma unroll
+          for (int i = 0; i < 8; ++i, o += ostride)
+            if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(u[i]));
         }
       }
       tc_fence_before();
