@@ -186,6 +186,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
+#ifdef EK_TC_PROFILE
+  __shared__ long long s_issue[8];   // when the weight copy of each stage was issued
+#endif
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -258,7 +261,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
           if (weights) {
+#ifdef EK_TC_PROFILE
+            s_issue[s] = clock64();
+#endif
             mbar_arrive_expect_tx(full, C::W_BYTES);
+            // one 32 KiB bulk copy per stage (tiled TMA or smaller pieces measured no faster)
             if (reread) bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
             else bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
           } else {
@@ -332,9 +339,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           const uint32_t a_tmem = tmem + C::A_BASE + a * kASlotCols;
           if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
-          tc_commit(smem_u32(&bar_aempty[a]));
-          tc_commit(smem_u32(&bar_xempty[cs]));
           PROF_LAP(3)
+          tc_commit(smem_u32(&bar_aempty[a]));
+          PROF_LAP(4)
+          tc_commit(smem_u32(&bar_xempty[cs]));
+          PROF_LAP(5)
         }
         if (ok) tc_commit(smem_u32(&bar_accfull));
       }
@@ -377,6 +386,15 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           ok = false;
           break;
         }
+#ifdef EK_TC_PROFILE
+        // issue -> landed latency of the weight copy, seen by one thread; only samples where this
+        // thread actually had to wait count as latency (the others are upper bounds)
+        if (warp == 0 && lane == 0 && p.prof) {
+          const long long lat = clock64() - s_issue[s];
+          atomicAdd((unsigned long long*)&p.prof[30], (unsigned long long)lat);
+          atomicAdd((unsigned long long*)&p.prof[31], 1ull);
+        }
+#endif
         PROF_LAP(0)
         const uint32_t tcount = it * 2 + wg;
         const uint32_t a = tcount % C::A_SLOTS, aph = (tcount / C::A_SLOTS) & 1u;
