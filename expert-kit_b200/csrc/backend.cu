@@ -610,8 +610,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMalloc(&be->n_chunks, 4));
   CKC(cudaMalloc(&be->status, sizeof(DevStatus)));
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
-  CKC(cudaMalloc(&be->prof, 32 * sizeof(long long)));
-  CKC(cudaMemset(be->prof, 0, 32 * sizeof(long long)));
+  CKC(cudaMalloc(&be->prof, kProfWords * sizeof(long long)));
+  CKC(cudaMemset(be->prof, 0, kProfWords * sizeof(long long)));
   CKC(cudaMallocHost(&be->h_status, sizeof(DevStatus)));
   be->h_chunks_cap = std::max(1024, be->max_chunks);
   CKC(cudaMallocHost(&be->h_chunks, sizeof(ChunkDesc) * be->h_chunks_cap));
@@ -1515,6 +1515,15 @@ int32_t ek_debug_profile(ek_backend_t* be, long long* out32) {
   cudaStreamSynchronize(be->stream);
   cudaMemcpy(out32, be->prof, 32 * sizeof(long long), cudaMemcpyDeviceToHost);
   cudaMemset(be->prof, 0, 32 * sizeof(long long));
+  return EK_OK;
+}
+// Event trace of one CTA of the gate/up kernel: kTraceSteps K steps x kTraceEvents clock values.
+int32_t ek_debug_trace(ek_backend_t* be, long long* out, int32_t n_words) {
+  if (!be || !out || n_words > kProfWords - 32) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  cudaStreamSynchronize(be->stream);
+  cudaMemcpy(out, be->prof + 32, n_words * sizeof(long long), cudaMemcpyDeviceToHost);
   return EK_OK;
 }
 #endif

@@ -138,6 +138,9 @@ int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_
                   __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t shared_t0, int32_t shared_T,
                   cudaStream_t s);
 
+constexpr int kTraceSteps = 96, kTraceEvents = 24;
+constexpr int kProfWords = 32 + kTraceSteps * kTraceEvents;
+
 struct FfnParams {
   Dims d;
   LayerWeights w;

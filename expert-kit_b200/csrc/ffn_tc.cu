@@ -42,7 +42,14 @@ using namespace ekptx;
 constexpr int kConvWarps = EK_CONV_WARPS;
 constexpr int kKSplit = kConvWarps / 8;      // warps sharing a tile row split its 8 chunks along K
 constexpr int kMmaWarps = 2;
-constexpr int kThreads = (kConvWarps + 1 + kMmaWarps) * 32;
+constexpr int kProdWarps = 2;                 // weight ring, activation ring: one warp each
+constexpr int kFirstMmaWarp = kConvWarps + kProdWarps;
+#ifdef EK_TC_PROFILE
+constexpr int kObserverWarps = 1;   // watches the weight barriers: true issue -> landed time
+#else
+constexpr int kObserverWarps = 0;
+#endif
+constexpr int kThreads = (kConvWarps + kProdWarps + kMmaWarps + kObserverWarps) * 32;
 constexpr int kASlotCols = 64;   // tensor-memory columns per A staging slot (128 bf16 along K)
 constexpr int kTmemCols = 512;
 #ifndef EK_MAX_A_SLOTS
@@ -73,7 +80,11 @@ struct Cfg {
   static constexpr int A_BASE = 2 * NMAX;
   static constexpr int A_SLOTS_RAW = ((kTmemCols - A_BASE) / kASlotCols) & ~1;
   static constexpr int A_SLOTS = A_SLOTS_RAW > kMaxASlots ? kMaxASlots : A_SLOTS_RAW;
+  static constexpr int A_PER = A_SLOTS / 2;                       // slots per chain
   static_assert(A_SLOTS >= 4, "need at least two A slots per chain");
+  // a converter reaches step it + STAGES only after its chain completed step it + STAGES - A_PER >= it,
+  // i.e. after the ready barrier of step it has flipped: arrivals of two laps never mix
+  static_assert(A_PER <= STAGES_RAW, "A slots per chain must not exceed the stage count");
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
 };
@@ -85,11 +96,15 @@ struct Cfg {
 #define PROF_DECL long long pt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pc_ = clock64();
 #define PROF_LAP(i) { long long n_ = clock64(); pt_[i] += n_ - pc_; pc_ = n_; }
 #define PROF_DUMP(role) \
-  if (p.prof) for (int i_ = 0; i_ < 8; ++i_) atomicAdd((unsigned long long*)&p.prof[(role) * 8 + i_], (unsigned long long)pt_[i_]);
+  if (p.prof) for (int i_ = 0; i_ < 6; ++i_) atomicAdd((unsigned long long*)&p.prof[(role) * 8 + i_], (unsigned long long)pt_[i_]);
+#define TRACE(itv, ev) \
+  if (GATEUP && blockIdx.x == 7 && p.prof && (itv) >= 300u && (itv) < 300u + kTraceSteps) \
+    p.prof[32 + ((itv) - 300u) * kTraceEvents + (ev)] = clock64();
 #else
 #define PROF_DECL
 #define PROF_LAP(i)
 #define PROF_DUMP(role)
+#define TRACE(itv, ev)
 #endif
 
 __device__ __forceinline__ void report(DevStatus* st, int code, int where, int a0, int a1) {
@@ -182,7 +197,7 @@ template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
 __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
   using C = Cfg<QUANT, GATEUP, NMAX>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[8], bar_wempty[8], bar_xempty[8], bar_afull[kMaxASlots], bar_aempty[kMaxASlots];
+  __shared__ __align__(8) uint64_t bar_wfull[8], bar_wempty[8], bar_ready[8], bar_done[kMmaWarps][8];
   __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
@@ -197,20 +212,19 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < C::STAGES; ++i) {
-      mbar_init(smem_u32(&bar_full[i]), 2);               // weight copy + activation copy
+      mbar_init(smem_u32(&bar_wfull[i]), 1);               // weight tiles of the stage have landed
       mbar_init(smem_u32(&bar_wempty[i]), kConvWarps);     // converters have read the weight tiles
-      mbar_init(smem_u32(&bar_xempty[i]), kMmaWarps);      // both chains' MMAs on the stage are done
-    }
-    for (int i = 0; i < C::A_SLOTS; ++i) {
-      mbar_init(smem_u32(&bar_afull[i]), kConvWarps / 2);
-      mbar_init(smem_u32(&bar_aempty[i]), 1);
+      // both A tiles of the step are in tensor memory (one arrival per converter warp) and the
+      // activation tile has landed (the producer's expect_tx arrival + the copy's bytes)
+      mbar_init(smem_u32(&bar_ready[i]), kConvWarps + 1);
+      for (int c = 0; c < kMmaWarps; ++c) mbar_init(smem_u32(&bar_done[c][i]), 1);   // chain c's MMAs of the step are complete
     }
     mbar_init(smem_u32(&bar_accfull), kMmaWarps);
     mbar_init(smem_u32(&bar_accempty), kConvWarps);
     for (int i = 0; i < kMmaWarps; ++i) mbar_init(smem_u32(&bar_drain[i]), 1);
     mbar_init_fence();
   }
-  if (warp == kConvWarps + 1) {
+  if (warp == kFirstMmaWarp) {
     tmem_alloc(smem_u32(&s_tmem), kTmemCols);
     tmem_relinquish();
   }
@@ -224,17 +238,18 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;   // K tiles of the GEMM = pipeline stages per work item
   const int total = n_chunks * n_rt;
 
-  if (warp == kConvWarps) {
+  if (warp < kFirstMmaWarp && warp >= kConvWarps) {
     // =============================== producers =============================================
-    // Two lanes, two independent rings over the same stages: lane 0 refills the weight tiles of a
-    // stage as soon as the converters have read them, lane 1 the activation tile once both MMA
-    // chains are done with it.  The weights (the long-latency HBM stream) thereby start their next
-    // trip a whole MMA phase earlier than the activations.
-    if (lane < 2) {
-      const bool weights = lane == 0;
+    // Two threads in two warps, two independent rings over the same stages: one refills the weight
+    // tiles of a stage as soon as the converters have read them, the other the activation tile once
+    // both MMA chains are done with the stage.  The weights (the long-latency HBM stream) thereby
+    // start their next trip a whole MMA phase earlier than the activations.  The activation copy
+    // signals the stage's `ready` barrier, the one the MMA threads wait on.
+    if (lane == 0) {
+      const bool weights = warp == kConvWarps;
       const CUtensorMap* maps = GATEUP ? p.x_maps : p.h_maps;
       const uint64_t stream_once = policy_evict_first();   // weights read exactly once per pass
-      uint64_t* bar_free = weights ? bar_wempty : bar_xempty;
+      uint64_t* bar_full = weights ? bar_wfull : bar_ready;
       uint32_t it = 0;
       bool ok = true;
       PROF_DECL
@@ -252,7 +267,15 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         const int brow = GATEUP ? cd.in_row : cd.out_row;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bar_free[s]), ph ^ 1u, abortp)) {
+          // a fresh barrier passes a wait on parity 1: the first lap over the ring does not block
+          bool free_ok;
+          if (weights) {
+            free_ok = mbar_wait(smem_u32(&bar_wempty[s]), ph ^ 1u, abortp);
+          } else {
+            free_ok = mbar_wait(smem_u32(&bar_done[0][s]), ph ^ 1u, abortp) &&
+                      mbar_wait(smem_u32(&bar_done[1][s]), ph ^ 1u, abortp);
+          }
+          if (!free_ok) {
             report(p.status, DEV_TIMEOUT, weights ? 100 : 101, item, kt);
             ok = false;
             break;
@@ -264,11 +287,14 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
 #ifdef EK_TC_PROFILE
             s_issue[s] = clock64();
 #endif
+            TRACE(it, 0)
             mbar_arrive_expect_tx(full, C::W_BYTES);
             // one 32 KiB bulk copy per stage (tiled TMA or smaller pieces measured no faster)
             if (reread) bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
             else bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
+            TRACE(it, 1)
           } else {
+            TRACE(it, 19)
             mbar_arrive_expect_tx(full, C::X_ATOMS * N * 128);
 #pragma unroll
             for (int a = 0; a < C::X_ATOMS; ++a)
@@ -288,19 +314,43 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
       }
     }
-  } else if (warp > kConvWarps) {
+#ifdef EK_TC_PROFILE
+  } else if (warp >= kFirstMmaWarp + kMmaWarps) {
+    if (lane == 0 && p.prof) {
+      uint32_t it = 0;
+      unsigned long long sum = 0, n = 0, mx = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, abortp)) { ok = false; break; }
+          const unsigned long long lat = (unsigned long long)(clock64() - s_issue[s]);
+          TRACE(it, 2)
+          sum += lat; ++n;
+          if (lat > mx) mx = lat;
+        }
+      }
+      atomicAdd((unsigned long long*)&p.prof[30], sum);
+      atomicAdd((unsigned long long*)&p.prof[31], n);
+      atomicMax((unsigned long long*)&p.prof[29], mx);
+    }
+#endif
+  } else if (warp >= kFirstMmaWarp) {
     // =============================== MMA issuers ===========================================
-    // Two issuing threads in two warps ("chains"), each with its own accumulator: one thread's
-    // instruction stream between MMAs (barrier polls, commits) costs about as much as the MMAs
-    // themselves take, so a single issuer leaves the tensor pipe idle half of the time.
+    // Two issuing threads in two warps ("chains"), each with its own accumulator: the instruction
+    // stream of one thread between MMAs (barrier waits, descriptors, commits) costs about as much
+    // time as the MMAs take, so a single issuer leaves the tensor pipe idle half of the time.  For
+    // the same reason each chain does one wait and one commit per K step and nothing else.
     //   gate/up : chain 0 issues the gate tile, chain 1 the up tile of every K step
     //   down    : chain c issues hidden-row tile 2*rp + c
     if (lane == 0) {
-      const uint32_t chain = warp - (kConvWarps + 1);
-      uint32_t it = 0, items_done = 0, s = 0, ph = 0;
+      const uint32_t chain = warp - kFirstMmaWarp;
+      uint32_t it = 0, items_done = 0, s = 0, ph = 0, ai = 0;
       bool ok = true;
       PROF_DECL
       const uint32_t d_tmem = tmem + chain * NMAX;
+      // descriptor of stage 0's activation tile; stages are a constant number of 16-byte units apart
+      const uint64_t b_base = umma_desc_sw128(stage0 + C::W_BYTES);
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
         const ChunkDesc cd = p.chunks[item / n_rt];
         const int N = pick_n(cd.n_rows & kChunkRowsMask, NMAX);
@@ -316,34 +366,31 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const uint32_t cs = s, cph = ph;
           if (++s == (uint32_t)C::STAGES) { s = 0; ph ^= 1u; }
-          if (!mbar_wait(smem_u32(&bar_full[cs]), cph, abortp)) {
-            report(p.status, DEV_TIMEOUT, 201, item, kt);
-            ok = false;
-            break;
-          }
+          const uint32_t a_tmem = tmem + C::A_BASE + (ai * 2 + chain) * kASlotCols;
+          if (++ai == (uint32_t)C::A_PER) ai = 0;
           // B descriptors of the stage's activation tile: one per 16-element K step
-          const uint64_t b0 = umma_desc_sw128(stage0 + cs * C::STAGE_BYTES + C::W_BYTES);
+          const uint64_t b0 = b_base + (uint64_t)(cs * (uint32_t)(C::STAGE_BYTES >> 4));
           uint64_t bd[C::MMAS];
 #pragma unroll
           for (int j = 0; j < C::MMAS; ++j) bd[j] = b0 + (uint64_t)((j / 4) * atom_step + (j % 4) * 2);
           PROF_LAP(1)
-          const uint32_t tcount = it * 2 + chain;
-          const uint32_t a = tcount % C::A_SLOTS, aph = (tcount / C::A_SLOTS) & 1u;
-          if (!mbar_wait(smem_u32(&bar_afull[a]), aph, abortp)) {
-            report(p.status, DEV_TIMEOUT, 202, item, kt);
+          if (chain == 0) { TRACE(it, 21) }
+          // both A tiles stored and the activation tile landed
+          if (!mbar_wait(smem_u32(&bar_ready[cs]), cph, abortp)) {
+            report(p.status, DEV_TIMEOUT, 201, item, kt);
             ok = false;
             break;
           }
           tc_fence_after();
           PROF_LAP(2)
-          const uint32_t a_tmem = tmem + C::A_BASE + a * kASlotCols;
+          TRACE(it, 12 + 4 * chain)
           if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
           PROF_LAP(3)
-          tc_commit(smem_u32(&bar_aempty[a]));
+          TRACE(it, 13 + 4 * chain)
+          tc_commit(smem_u32(&bar_done[chain][cs]));
           PROF_LAP(4)
-          tc_commit(smem_u32(&bar_xempty[cs]));
-          PROF_LAP(5)
+          TRACE(it, 14 + 4 * chain)
         }
         if (ok) tc_commit(smem_u32(&bar_accfull));
       }
@@ -381,29 +428,25 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         const float scale = scale_next;
         if (QUANT != EK_QUANT_BF16 && kt + 1 < KT) scale_next = __ldg(sc + (size_t)(kt + 1) * 2);
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp)) {
+        if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, abortp)) {
           report(p.status, DEV_TIMEOUT, 300, item, kt);
           ok = false;
           break;
         }
-#ifdef EK_TC_PROFILE
-        // issue -> landed latency of the weight copy, seen by one thread; only samples where this
-        // thread actually had to wait count as latency (the others are upper bounds)
-        if (warp == 0 && lane == 0 && p.prof) {
-          const long long lat = clock64() - s_issue[s];
-          atomicAdd((unsigned long long*)&p.prof[30], (unsigned long long)lat);
-          atomicAdd((unsigned long long*)&p.prof[31], 1ull);
-        }
-#endif
         PROF_LAP(0)
-        const uint32_t tcount = it * 2 + wg;
-        const uint32_t a = tcount % C::A_SLOTS, aph = (tcount / C::A_SLOTS) & 1u;
-        if (!mbar_wait(smem_u32(&bar_aempty[a]), aph ^ 1u, abortp)) {
-          report(p.status, DEV_TIMEOUT, 301, item, kt);
-          ok = false;
-          break;
+        if (q == 0 && lane == 0) { TRACE(it, 3 + 4 * wg) }
+        // A slot of this step: free once this warpgroup's chain has completed step it - A_PER
+        const uint32_t a = (it % C::A_PER) * 2 + wg;
+        if (it >= (uint32_t)C::A_PER) {
+          const uint32_t j = it - C::A_PER;
+          if (!mbar_wait(smem_u32(&bar_done[wg][j % C::STAGES]), (j / C::STAGES) & 1u, abortp)) {
+            report(p.status, DEV_TIMEOUT, 301, item, kt);
+            ok = false;
+            break;
+          }
         }
         PROF_LAP(1)
+        if (q == 0 && lane == 0) { TRACE(it, 4 + 4 * wg) }
         const uint8_t* tile = smem_raw + (stage0 - smem_u32(smem_raw)) + s * C::STAGE_BYTES + wg * kTileBytes;
         uint4 raw[C::NCH];
 #pragma unroll
@@ -430,14 +473,16 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           tmem_st16(lane_base + col0, aw);
         }
         PROF_LAP(2)
+        if (q == 0 && lane == 0) { TRACE(it, 5 + 4 * wg) }
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(smem_u32(&bar_afull[a]));
+          mbar_arrive(smem_u32(&bar_ready[s]));
           mbar_arrive(smem_u32(&bar_wempty[s]));
         }
         PROF_LAP(3)
+        if (q == 0 && lane == 0) { TRACE(it, 6 + 4 * wg) }
       }
       if (!ok) break;
       // ---- epilogue ----
@@ -506,7 +551,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == kConvWarps + 1) {
+  if (warp == kFirstMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
