@@ -33,14 +33,20 @@ namespace {
 
 using namespace ekptx;
 
-// 8 (default) or 16 converter warps: one or two warps per (tile, lane quarter).  Measured on the
-// DeepSeek-V3 shape: 16 warps are 4-9 % slower at every batch size (more barrier traffic, no gain
-// in issue rate), so 8 it is.
+// Converter warps come in groups of 8 (two warpgroups: one per tile of the stage, one warp per
+// tensor-memory lane quarter).  Group g converts the K steps kt = g, g + kGroups, ...: with two
+// groups, two steps are in conversion at any time and each scheduler holds four converter warps
+// instead of two, whose conversion phases (bound by the half-rate integer pipe and by dependent
+// issue) overlap instead of taking turns.  Splitting a tile row between two warps instead doubled
+// the per-warp barrier work and measured 4-9 % slower.
 #ifndef EK_CONV_WARPS
-#define EK_CONV_WARPS 8
+#define EK_CONV_WARPS 16
 #endif
 constexpr int kConvWarps = EK_CONV_WARPS;
-constexpr int kKSplit = kConvWarps / 8;      // warps sharing a tile row split its 8 chunks along K
+constexpr int kGroupWarps = 8;
+constexpr int kGroups = kConvWarps / kGroupWarps;
+static_assert(kConvWarps % kGroupWarps == 0 && kGroups >= 1 && kGroups <= 2,
+              "converter warps come in one or two groups of 8 (three groups faulted at launch and are not supported)");
 constexpr int kMmaWarps = 2;
 constexpr int kProdWarps = 2;                 // weight ring, activation ring: one warp each
 constexpr int kFirstMmaWarp = kConvWarps + kProdWarps;
@@ -72,7 +78,7 @@ struct Cfg {
   static constexpr int STAGES_RAW = kSmemLimit / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int MMAS = TKE / 16;                           // MMA instructions per tile
-  static constexpr int NCH = 8 / kKSplit;                         // 16-byte chunks per thread
+  static constexpr int NCH = 8;                                   // 16-byte chunks per thread (its tile row)
   static constexpr int WPC = QUANT == EK_QUANT_BF16 ? 4 : 8;      // 32-bit A words per chunk
   static constexpr int NW = NCH * WPC;
   // tensor memory: two accumulators of NMAX columns, the rest is a ring of A staging slots (an
@@ -213,10 +219,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     s_abort = 0;
     for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(smem_u32(&bar_wfull[i]), 1);               // weight tiles of the stage have landed
-      mbar_init(smem_u32(&bar_wempty[i]), kConvWarps);     // converters have read the weight tiles
+      mbar_init(smem_u32(&bar_wempty[i]), kGroupWarps);    // the step's converter group has read the weight tiles
       // both A tiles of the step are in tensor memory (one arrival per converter warp) and the
       // activation tile has landed (the producer's expect_tx arrival + the copy's bytes)
-      mbar_init(smem_u32(&bar_ready[i]), kConvWarps + 1);
+      mbar_init(smem_u32(&bar_ready[i]), kGroupWarps + 1);
       for (int c = 0; c < kMmaWarps; ++c) mbar_init(smem_u32(&bar_done[c][i]), 1);   // chain c's MMAs of the step are complete
     }
     mbar_init(smem_u32(&bar_accfull), kMmaWarps);
@@ -405,10 +411,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   } else {
     // =============================== converters + epilogue =================================
     // warp -> (tile of the stage, K part of the tile row, lane quarter of tensor memory)
-    const int wg = warp / (4 * kKSplit), kh = (warp >> 2) % kKSplit, q = warp & 3;
+    const int grp = warp / kGroupWarps, wg = (warp % kGroupWarps) >> 2, q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
-    uint32_t it = 0, items_done = 0;
+    uint32_t it_base = 0, items_done = 0;
     bool ok = true;
     PROF_DECL
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
@@ -423,10 +429,12 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
                     : p.w.dn_scale + ((size_t)cd.slot * p.d.hp + rt) * (size_t)p.d.kt_dn * 2 + wg;
       }
       float scale_next = 1.f;
-      if (QUANT != EK_QUANT_BF16) scale_next = __ldg(sc);
-      for (int kt = 0; kt < KT; ++kt, ++it) {
+      if (QUANT != EK_QUANT_BF16 && grp < KT) scale_next = __ldg(sc + (size_t)grp * 2);
+      const uint32_t it0 = it_base;   // global index of the item's first K step (the same in every role)
+      for (int kt = grp; kt < KT; kt += kGroups) {
+        const uint32_t it = it0 + kt;
         const float scale = scale_next;
-        if (QUANT != EK_QUANT_BF16 && kt + 1 < KT) scale_next = __ldg(sc + (size_t)(kt + 1) * 2);
+        if (QUANT != EK_QUANT_BF16 && kt + kGroups < KT) scale_next = __ldg(sc + (size_t)(kt + kGroups) * 2);
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
         if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, abortp)) {
           report(p.status, DEV_TIMEOUT, 300, item, kt);
@@ -451,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         uint4 raw[C::NCH];
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j)
-          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)((kh * C::NCH + j) * kTileRows + r) * 16);
+          raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)(j * kTileRows + r) * 16);
         uint32_t aw[C::NW];
         uint32_t s_hi = 0, s_lo = 0;
         if (QUANT == EK_QUANT_FP8_BLOCK128 && !PRECISE) {
@@ -464,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT, PRECISE>(raw[j], scale, s_hi, s_lo, aw + j * C::WPC);
-        const uint32_t col0 = C::A_BASE + a * kASlotCols + kh * C::NW;
+        const uint32_t col0 = C::A_BASE + a * kASlotCols;
         tc_fence_after();
         if (C::NW >= 32) {
 #pragma unroll
@@ -484,6 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         PROF_LAP(3)
         if (q == 0 && lane == 0) { TRACE(it, 6 + 4 * wg) }
       }
+      it_base += (uint32_t)KT;
       if (!ok) break;
       // ---- epilogue ----
       if (!mbar_wait(smem_u32(&bar_accfull), items_done & 1u, abortp)) {
@@ -546,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       if (lane == 0) mbar_arrive(smem_u32(&bar_accempty));
       PROF_LAP(5)
     }
-    if (lane == 0 && (warp == 0 || warp == 4 * kKSplit)) { PROF_DUMP(2 + wg) }
+    if (lane == 0 && (warp == 0 || warp == 4)) { PROF_DUMP(2 + wg) }
   }
 
   tc_fence_before();
