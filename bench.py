@@ -414,10 +414,9 @@ def main_ep(args, rank: int, world: int, local: int):
     e2e = {"value": T * e2e_steps / float(tt.item()), "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
            "d2h_bytes_per_step": T * H * 2, "steps": e2e_steps}
     if rank == 0:
+        # the CPU baseline is timed at N = 1 only: here the other ranks' host threads (NCCL proxies,
+        # the ranks waiting in destroy_process_group) share the cores and would distort it
         base = None
-        if not args.no_cpu_baseline:
-            b = cpu_baseline(T)
-            base = {k_: b[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(T, world, n_exp),
@@ -442,6 +441,9 @@ def main():
                     help="also run a continuous-batching stream of this many steps (decode ~Poisson(96) tokens, a "
                          "512-2048 token prefill chunk every 10th step, Zipf(1.2) expert load rotated every 200 steps, "
                          "every expert >= 1 row) through the controller-level entry point; reported under 'stream'")
+    ap.add_argument("--worker-threads", type=int, default=0,
+                    help="also drive the worker-level seam: one single-expert call per distinct expert of the batch "
+                         "from this many host threads; reported under 'worker_path'")
     ap.add_argument("--layers", type=int, default=1,
                     help="MoE layers per step (58 = the full DeepSeek-V3 expert stack; each layer has its own weights)")
     ap.add_argument("--ep-mode", default="auto", choices=["auto", "gather", "a2a"],
@@ -587,6 +589,55 @@ def main():
                               "layer_roofline_frac": (rs * 1e3) / st,
                               "stage_ms": {k_: round(v, 4) for k_, v in stage_n.items()}}
 
+    worker_out = None
+    if args.worker_threads > 0:
+        # The reference's own seam: one single-expert call per distinct expert of the batch, issued
+        # from N host threads as its worker does per RPC (host buffers in and out); the library
+        # serves whatever is queued as one grouped launch.
+        import threading
+        xw = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+        _, art = be.moe_forward_fused(0, xw, debug=True)
+        ids = art["ids"].cpu()
+        xh = xw.cpu()
+        per_expert = {}
+        for e in torch.unique(ids).tolist():
+            rows = (ids == e).any(dim=1).nonzero().flatten()
+            xe = xh[rows].contiguous().pin_memory()
+            # (id, x pointer, rows, y pointer) prepared once: the timed loop is the C call alone, so
+            # the interpreter lock is free while a call waits and the threads really overlap
+            per_expert[e] = (be.expert_id(0, e).encode(), xe, xe.shape[0], torch.empty_like(xe).pin_memory())
+        experts = sorted(per_expert)
+        fwd, handle = be._lib.ek_expert_forward, be._h
+        nthr = args.worker_threads
+        c0, b0 = be.worker_batch_stats()
+        reps = max(3, args.steps // 4)
+        go = threading.Barrier(nthr + 1)
+
+        def run(tid):
+            mine = experts[tid::nthr]
+            for _ in range(reps + 1):
+                go.wait()
+                for e in mine:
+                    eid, xe, n_e, ye = per_expert[e]
+                    if fwd(handle, eid, xe.data_ptr(), n_e, ye.data_ptr()) != 0:
+                        raise RuntimeError(be._lib.ek_last_error(handle).decode())
+                go.wait()
+
+        ths = [threading.Thread(target=run, args=(i,)) for i in range(nthr)]
+        for t_ in ths:
+            t_.start()
+        go.wait(); go.wait()                      # warm-up round
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            go.wait(); go.wait()
+        dt = (time.perf_counter() - t0) / reps
+        for t_ in ths:
+            t_.join()
+        c1, b1 = be.worker_batch_stats()
+        worker_out = {"threads": nthr, "calls_per_step": len(experts), "ms_per_step": dt * 1e3,
+                      "tokens_per_s": T / dt, "calls": c1 - c0, "grouped_passes": b1 - b0,
+                      "note": "single-expert calls with host buffers from N threads (wall clock, expert FFN only)"}
+
     stream_out = None
     if args.stream > 0:
         gs = torch.Generator().manual_seed(4)
@@ -650,6 +701,8 @@ def main():
             line["sweep"] = sweep_out
         if stream_out:
             line["stream"] = stream_out
+        if worker_out:
+            line["worker_path"] = worker_out
         print(json.dumps(line))
     be.close()
     if dist is not None:

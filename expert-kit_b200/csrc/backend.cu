@@ -45,6 +45,17 @@ struct ExpertRef {
 
 }  // namespace
 
+// One worker-level call waiting to be served (lives on its caller's stack).
+struct ExpertReq {
+  const char* id = nullptr;
+  const void* x = nullptr;
+  void* y = nullptr;
+  int n = 0;
+  int row0 = 0;
+  int rc = EK_OK;
+  bool done = false;   // written and read under the forward lock
+};
+
 struct ek_backend {
   ek_config_t cfg;
   Dims d;
@@ -102,6 +113,9 @@ struct ek_backend {
   std::set<std::string> loading;
   mutable std::shared_mutex reg_mu;           // the worker's RwLock around ExpertDB
   std::mutex fwd_mu;                          // forwards share one workspace
+  std::mutex pend_mu;                         // queue of worker-level requests waiting for a grouped launch
+  std::vector<ExpertReq*> pending;
+  int64_t batched_calls = 0, batched_launches = 0;   // worker-level calls served / grouped launches used (under fwd_mu)
   std::mutex load_mu;                         // loads share the staging buffers
   mutable std::mutex err_mu;
   mutable std::string err;
@@ -953,32 +967,33 @@ int32_t ek_router_register(ek_backend_t* be, int32_t layer, const void* weight, 
 
 // ---- forward ---------------------------------------------------------------------------------
 
-int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x, int32_t n, void* y) {
-  if (!be || !id || !x || !y) return EK_INVALID_INPUT;
-  if (n < 1) return fail(be, EK_INVALID_INPUT, "empty batch");   // core.rs:55 asserts non-empty
-  cudaSetDevice(be->cfg.device);
-  std::lock_guard<std::mutex> fg(be->fwd_mu);
-  std::shared_lock<std::shared_mutex> g(be->reg_mu);
-  auto it = be->experts.find(id);
-  if (it == be->experts.end()) return fail(be, EK_EXPERT_NOT_FOUND, "%s", id);
+// ---- worker-level forward: concurrent single-expert calls are served as one grouped launch ----
+//
+// The reference worker runs one `forward` per RPC on up to 48 runtime threads
+// (ek-computation/src/worker/core.rs:47-74, bin/worker.rs:5), each on its own expert.  A single
+// expert occupies 16 of the 148 CTAs of the grouped GEMM, so here every caller queues its request
+// and whoever gets the forward lock next serves everything queued so far in one launch per layer
+// ("combining lock"); callers whose request was served by someone else just pick up the result.
+namespace {
+
+// One virtual-expert request served alone (shared experts with several virtual slots): the partial
+// outputs are summed with the combine kernel.
+int serve_shared(ek_backend* be, ExpertReq& r, const ExpertRef& ent) {
   const ek_config_t& c = be->cfg;
-  std::string model; int layer, expert; bool shared;
-  parse_id(id, model, layer, expert, shared);
-  const int n_virtual = shared ? c.n_shared_experts : 1;
+  const int n = r.n, n_virtual = c.n_shared_experts;
   if ((int64_t)n * n_virtual > be->rows_cap - 128) return fail(be, EK_INVALID_INPUT, "batch of %d rows exceeds the workspace", n);
-  Layer& L = be->layers[it->second.layer];
+  Layer& L = be->layers[ent.layer];
   const size_t H = c.hidden;
   cudaStream_t s = be->stream;
-  // rows [0,n) of the permuted buffer are the request
-  CK(cudaMemcpyAsync(be->xp, x, (size_t)n * H * 2, cudaMemcpyDefault, s));
+  CK(cudaMemcpyAsync(be->xp, r.x, (size_t)n * H * 2, cudaMemcpyDefault, s));
   const int nmax = n <= 32 ? 32 : n <= 64 ? 64 : 128;
   const int chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
   const int per = (n + chunk_rows - 1) / chunk_rows;
-  if (per * n_virtual > 1024) return fail(be, EK_INVALID_INPUT, "batch too large for a single-expert call");
+  if (per * n_virtual > std::min(be->h_chunks_cap, be->max_chunks)) return fail(be, EK_INVALID_INPUT, "batch too large for a single-expert call");
   for (int v = 0; v < n_virtual; ++v)
     for (int cidx = 0; cidx < per; ++cidx) {
       ChunkDesc cd;
-      cd.slot = it->second.slot + v;
+      cd.slot = ent.slot + v;
       cd.in_row = cidx * chunk_rows;
       cd.out_row = v * n + cidx * chunk_rows;
       cd.n_rows = std::min(chunk_rows, n - cidx * chunk_rows) | (per > 1 ? kChunkMulti : 0);
@@ -986,25 +1001,139 @@ int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x, int32
     }
   const int32_t total = per * n_virtual;
   CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * total, cudaMemcpyHostToDevice, s));
-  be->h_status->aux1 = total;   // reuse pinned word as the source of the count
+  be->h_status->aux1 = total;   // pinned word as the source of the count
   CK(cudaMemcpyAsync(be->n_chunks, &be->h_status->aux1, 4, cudaMemcpyHostToDevice, s));
   run_ffn(be, L, nmax, 0);
   run_ffn(be, L, nmax, 1);
-  __nv_bfloat16* res = be->obuf;
-  if (n_virtual > 1) {
-    // sum the virtual shared experts' partial outputs with the combine kernel (weights unused)
-    CombineParams cp;
-    cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
-    cp.T = n; cp.k = 0; cp.H = c.hidden; cp.n_shared = n_virtual; cp.Tk = 0; cp.bf16_products = 0;
-    cp.shared = nullptr;
-    be->launches += launch_combine(cp, s);
-    res = be->y_dev;
-  }
-  CK(cudaMemcpyAsync(y, res, (size_t)n * H * 2, cudaMemcpyDefault, s));
+  CombineParams cp;
+  cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
+  cp.T = n; cp.k = 0; cp.H = c.hidden; cp.n_shared = n_virtual; cp.Tk = 0; cp.bf16_products = 0;
+  cp.shared = nullptr;
+  be->launches += launch_combine(cp, s);
+  CK(cudaMemcpyAsync(r.y, be->y_dev, (size_t)n * H * 2, cudaMemcpyDefault, s));
   int rc = check_status(be);
   if (rc != EK_OK) return rc;
   CK(cudaGetLastError());
   return EK_OK;
+}
+
+// Requests of one layer, each on one expert slot: rows packed back to back, one grouped launch.
+int serve_group(ek_backend* be, int layer, std::vector<std::pair<ExpertReq*, int>>& group) {
+  const ek_config_t& c = be->cfg;
+  Layer& L = be->layers[layer];
+  const size_t H = c.hidden;
+  cudaStream_t s = be->stream;
+  int n_max = 0;
+  for (auto& g : group) n_max = std::max(n_max, g.first->n);
+  const int nmax = n_max <= 32 ? 32 : n_max <= 64 ? 64 : 128;
+  const int chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
+  int row = 0, n_chunks = 0;
+  for (auto& g : group) {
+    ExpertReq& r = *g.first;
+    const int per = (r.n + chunk_rows - 1) / chunk_rows;
+    CK(cudaMemcpyAsync(be->xp + (size_t)row * H, r.x, (size_t)r.n * H * 2, cudaMemcpyDefault, s));
+    for (int cidx = 0; cidx < per; ++cidx) {
+      ChunkDesc cd;
+      cd.slot = g.second;
+      cd.in_row = row + cidx * chunk_rows;
+      cd.out_row = row + cidx * chunk_rows;
+      cd.n_rows = std::min(chunk_rows, r.n - cidx * chunk_rows) | (per > 1 ? kChunkMulti : 0);
+      be->h_chunks[n_chunks++] = cd;
+    }
+    r.row0 = row;
+    row += r.n;
+  }
+  CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * n_chunks, cudaMemcpyHostToDevice, s));
+  be->h_status->aux1 = n_chunks;
+  CK(cudaMemcpyAsync(be->n_chunks, &be->h_status->aux1, 4, cudaMemcpyHostToDevice, s));
+  run_ffn(be, L, nmax, 0);
+  run_ffn(be, L, nmax, 1);
+  for (auto& g : group) {
+    ExpertReq& r = *g.first;
+    CK(cudaMemcpyAsync(r.y, be->obuf + (size_t)r.row0 * H, (size_t)r.n * H * 2, cudaMemcpyDefault, s));
+  }
+  int rc = check_status(be);
+  if (rc != EK_OK) return rc;
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+// Serves every queued request; called with the forward lock held.
+void serve_pending(ek_backend* be) {
+  std::vector<ExpertReq*> batch;
+  {
+    std::lock_guard<std::mutex> pg(be->pend_mu);
+    batch.swap(be->pending);
+  }
+  if (batch.empty()) return;
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  const ek_config_t& c = be->cfg;
+  // group by layer, in arrival order; a group is cut when the workspace or the chunk list is full
+  std::map<int, std::vector<std::pair<ExpertReq*, int>>> by_layer;
+  for (ExpertReq* r : batch) {
+    auto it = be->experts.find(r->id);
+    if (it == be->experts.end()) {
+      r->rc = fail(be, EK_EXPERT_NOT_FOUND, "%s", r->id);
+      r->done = true;
+      continue;
+    }
+    std::string model; int layer, expert; bool shared;
+    parse_id(r->id, model, layer, expert, shared);
+    if (shared && c.n_shared_experts > 1) {
+      r->rc = serve_shared(be, *r, it->second);
+      r->done = true;
+      continue;
+    }
+    if (r->n > be->rows_cap - 128) {
+      r->rc = fail(be, EK_INVALID_INPUT, "batch of %d rows exceeds the workspace", r->n);
+      r->done = true;
+      continue;
+    }
+    by_layer[it->second.layer].push_back({r, it->second.slot});
+  }
+  for (auto& kv : by_layer) {
+    auto& all = kv.second;
+    size_t i = 0;
+    while (i < all.size()) {
+      std::vector<std::pair<ExpertReq*, int>> group;
+      int rows = 0, chunks = 0;
+      while (i < all.size()) {
+        const int n = all[i].first->n;
+        const int ch = (n + 15) / 16;   // upper bound on its chunks
+        if (!group.empty() && (rows + n > be->rows_cap - 128 || chunks + ch > std::min(be->h_chunks_cap, be->max_chunks))) break;
+        group.push_back(all[i]);
+        rows += n;
+        chunks += ch;
+        ++i;
+      }
+      const int rc = serve_group(be, kv.first, group);
+      for (auto& g2 : group) {
+        g2.first->rc = rc;
+        g2.first->done = true;
+      }
+    }
+  }
+  be->batched_calls += (int64_t)batch.size();
+  be->batched_launches += 1;
+}
+
+}  // namespace
+
+int32_t ek_expert_forward(ek_backend_t* be, const char* id, const void* x, int32_t n, void* y) {
+  if (!be || !id || !x || !y) return EK_INVALID_INPUT;
+  if (n < 1) return fail(be, EK_INVALID_INPUT, "empty batch");   // core.rs:55 asserts non-empty
+  ExpertReq r;
+  r.id = id; r.x = x; r.n = n; r.y = y;
+  {
+    std::lock_guard<std::mutex> pg(be->pend_mu);
+    be->pending.push_back(&r);
+  }
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  if (!r.done) {
+    cudaSetDevice(be->cfg.device);
+    serve_pending(be);
+  }
+  return r.rc;
 }
 
 static int stage_in(ek_backend* be, const void* x, size_t bytes, const __nv_bfloat16** dev) {
@@ -1498,6 +1627,14 @@ int32_t ek_stage_times(ek_backend_t* be, float* ms) {
   return EK_OK;
 }
 int64_t ek_kernel_launches(const ek_backend_t* be) { return be ? be->launches.load() : 0; }
+
+int32_t ek_worker_batch_stats(ek_backend_t* be, int64_t* calls, int64_t* batches) {
+  if (!be || !calls || !batches) return EK_INVALID_INPUT;
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  *calls = be->batched_calls;
+  *batches = be->batched_launches;
+  return EK_OK;
+}
 
 int32_t ek_set_precise_dequant(ek_backend_t* be, int32_t on) {
   if (!be) return EK_INVALID_INPUT;

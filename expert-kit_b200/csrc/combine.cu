@@ -33,26 +33,27 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-// One CTA per token, 128-bit loads of the k expert rows, fp32 accumulation in slot order.
-__global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
-  __shared__ int s_row[kMaxK];
-  __shared__ float s_w[kMaxK];
-  const int t = blockIdx.x;
-  if (threadIdx.x < p.k) {
-    s_row[threadIdx.x] = p.inv[(size_t)t * p.k + threadIdx.x];
-    s_w[threadIdx.x] = p.weights[(size_t)t * p.k + threadIdx.x];
-  }
-  __syncthreads();
-  for (int v = threadIdx.x; v < p.H / 8; v += blockDim.x) {
-    float acc[8];
+// Rows of the k slots of one 8-element vector, loaded BATCH at a time before the ordered sum: the
+// loads are independent, the additions are not.  Small batches of tokens want all eight loads in
+// flight per thread (few CTAs, latency-bound); large ones want the occupancy of the short form.
+template <int BATCH>
+__device__ __forceinline__ void weighted_rows(const CombineParams& p, const int* s_row, const float* s_w, int v,
+                                              float* acc) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int s = 0; s < p.k; ++s) {
-      const int row = s_row[s];
-      if (row < 0) continue;
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int s0 = 0; s0 < p.k; s0 += BATCH) {
+    uint4 raw[BATCH];
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int row = s0 + i < p.k ? s_row[s0 + i] : -1;
+      raw[i] = row >= 0 ? *reinterpret_cast<const uint4*>(p.obuf + (size_t)row * p.H + v * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      if (s0 + i >= p.k || s_row[s0 + i] < 0) continue;
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.obuf + (size_t)row * p.H + v * 8), f);
-      const float w = s_w[s];
+      unpack8(raw[i], f);
+      const float w = s_w[s0 + i];
       if (p.bf16_products) {
         // routing weights were rounded to bf16 upstream; products are bf16 tensors
 #pragma unroll
@@ -62,6 +63,26 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
         for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(w, f[j]));
       }
     }
+  }
+}
+
+// One CTA per (token, slice of H): 128-bit loads of the k expert rows, fp32 accumulation in slot
+// order.  gridDim.y slices keep small batches from running on a handful of SMs.
+template <int BATCH>
+__global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
+  __shared__ int s_row[kMaxK];
+  __shared__ float s_w[kMaxK];
+  const int t = blockIdx.x;
+  if (threadIdx.x < p.k) {
+    s_row[threadIdx.x] = p.inv[(size_t)t * p.k + threadIdx.x];
+    s_w[threadIdx.x] = p.weights[(size_t)t * p.k + threadIdx.x];
+  }
+  __syncthreads();
+  const int nv = p.H / 8, per = (nv + gridDim.y - 1) / gridDim.y;
+  const int v_lo = blockIdx.y * per, v_hi = min(nv, v_lo + per);
+  for (int v = v_lo + threadIdx.x; v < v_hi; v += blockDim.x) {
+    float acc[8];
+    weighted_rows<BATCH>(p, s_row, s_w, v, acc);
     if (p.n_shared > 0) {
       // the routed sum is a bf16 tensor before the shared expert's bf16 output is added
 #pragma unroll
@@ -101,6 +122,7 @@ __global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __r
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
 }
 
+template <int BATCH>
 __global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, float* __restrict__ partial) {
   __shared__ int s_row[kMaxK];
   __shared__ float s_w[kMaxK];
@@ -110,20 +132,11 @@ __global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, f
     s_w[threadIdx.x] = p.weights[(size_t)t * p.k + threadIdx.x];
   }
   __syncthreads();
-  for (int v = threadIdx.x; v < p.H / 8; v += blockDim.x) {
+  const int nv = p.H / 8, per = (nv + gridDim.y - 1) / gridDim.y;
+  const int v_lo = blockIdx.y * per, v_hi = min(nv, v_lo + per);
+  for (int v = v_lo + threadIdx.x; v < v_hi; v += blockDim.x) {
     float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int s = 0; s < p.k; ++s) {
-      const int row = s_row[s];
-      if (row < 0) continue;
-      float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.obuf + (size_t)row * p.H + v * 8), f);
-      const float w = s_w[s];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        acc[j] = __fadd_rn(acc[j], p.bf16_products ? round_bf16(__fmul_rn(w, f[j])) : __fmul_rn(w, f[j]));
-    }
+    weighted_rows<BATCH>(p, s_row, s_w, v, acc);
     float4* d = reinterpret_cast<float4*>(partial + (size_t)t * p.H + v * 8);
     d[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     d[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -135,7 +148,9 @@ __global__ void __launch_bounds__(256) combine_finish_kernel(const float* __rest
                                                              int32_t n_shared, int32_t T, int32_t H,
                                                              __nv_bfloat16* __restrict__ y) {
   const int t = blockIdx.x;
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+  const int nv = H / 8, per = (nv + gridDim.y - 1) / gridDim.y;
+  const int v_lo = blockIdx.y * per, v_hi = min(nv, v_lo + per);
+  for (int v = v_lo + threadIdx.x; v < v_hi; v += blockDim.x) {
     const float4* r = reinterpret_cast<const float4*>(reduced + (size_t)t * H + v * 8);
     const float4 a = r[0], b = r[1];
     float acc[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -184,18 +199,32 @@ int launch_segment_copy(const __nv_bfloat16* src, __nv_bfloat16* dst, const RowS
   return 1;
 }
 
+// H slices per token: enough CTAs for two per SM, at least 256 threads' worth of vectors each
+static int h_slices(int T, int H) {
+  int parts = (296 + T - 1) / T;
+  const int most = (H / 8 + 255) / 256;
+  if (parts > most) parts = most;
+  return parts < 1 ? 1 : parts;
+}
+
 int launch_combine_partial(const CombineParams& p, float* partial, cudaStream_t s) {
-  if (p.T > 0) combine_partial_kernel<<<p.T, 256, 0, s>>>(p, partial);
+  if (p.T > 0) {
+    if (p.T < 1024) combine_partial_kernel<8><<<dim3(p.T, h_slices(p.T, p.H)), 256, 0, s>>>(p, partial);
+    else combine_partial_kernel<2><<<dim3(p.T, 1), 256, 0, s>>>(p, partial);
+  }
   return p.T > 0 ? 1 : 0;
 }
 int launch_combine_finish(const float* reduced, const __nv_bfloat16* shared, int32_t n_shared, int32_t T,
                           int32_t H, __nv_bfloat16* y, cudaStream_t s) {
-  if (T > 0) combine_finish_kernel<<<T, 256, 0, s>>>(reduced, shared, n_shared, T, H, y);
+  if (T > 0) combine_finish_kernel<<<dim3(T, h_slices(T, H)), 256, 0, s>>>(reduced, shared, n_shared, T, H, y);
   return T > 0 ? 1 : 0;
 }
 
 int launch_combine(const CombineParams& p, cudaStream_t s) {
-  if (p.T > 0) combine_kernel<<<p.T, 256, 0, s>>>(p);
+  if (p.T > 0) {
+    if (p.T < 1024) combine_kernel<8><<<dim3(p.T, h_slices(p.T, p.H)), 256, 0, s>>>(p);
+    else combine_kernel<2><<<dim3(p.T, 1), 256, 0, s>>>(p);
+  }
   return p.T > 0 ? 1 : 0;
 }
 

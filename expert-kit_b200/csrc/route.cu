@@ -123,12 +123,31 @@ __global__ void __launch_bounds__(kSelWarps * 32) route_select_kernel(RouteParam
   const int E = p.E;
   if (p.partial) {
     // add the split-K partial sums in split order; the softmax path works on bf16 logits like the
-    // reference's bf16 linear layer
-    for (int e = lane; e < E; e += 32) {
-      float v = 0.f;
-      for (int ks = 0; ks < p.n_partials; ++ks) v += p.partial[((size_t)ks * p.T + t) * E + e];
-      if (p.scoring == EK_SCORE_SOFTMAX) v = __bfloat162float(__float2bfloat16_rn(v));
-      lg[e] = v;
+    // reference's bf16 linear layer.  Four experts per lane and four splits per round: 16
+    // independent loads in flight instead of one dependent chain per expert.
+    for (int e0 = lane; e0 < E; e0 += 128) {
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int k0 = 0; k0 < p.n_partials; k0 += 4) {
+        float tmp[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = e0 + 32 * j;
+            tmp[a][j] = (k0 + a < p.n_partials && e < E) ? p.partial[((size_t)(k0 + a) * p.T + t) * E + e] : 0.f;
+          }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+          if (k0 + a < p.n_partials) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] += tmp[a][j];
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + 32 * j;
+        if (e < E) lg[e] = p.scoring == EK_SCORE_SOFTMAX ? __bfloat162float(__float2bfloat16_rn(v[j])) : v[j];
+      }
     }
     __syncwarp();
   }

@@ -71,6 +71,7 @@ SIGNATURES = {
     "ek_stage_timing_enable": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ek_stage_times": (C.c_int32, [C.c_void_p, C.POINTER(C.c_float)]),
     "ek_kernel_launches": (C.c_int64, [C.c_void_p]),
+    "ek_worker_batch_stats": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "ek_debug_set_ffn_impl": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ek_set_precise_dequant": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ek_set_stream": (C.c_int32, [C.c_void_p, C.c_void_p]),

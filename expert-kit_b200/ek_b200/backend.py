@@ -311,6 +311,12 @@ class Backend:
     def kernel_launches(self) -> int:
         return int(self._lib.ek_kernel_launches(self._h))
 
+    def worker_batch_stats(self):
+        """(worker-level calls served, grouped passes that served them)."""
+        calls, batches = C.c_int64(0), C.c_int64(0)
+        self._check(self._lib.ek_worker_batch_stats(self._h, C.byref(calls), C.byref(batches)))
+        return int(calls.value), int(batches.value)
+
     def set_precise_dequant(self, on: bool):
         """fp8: apply block scales in fp32 inside the GEMM (bit-exact reference dequantisation)."""
         self._check(self._lib.ek_set_precise_dequant(self._h, int(on)))

@@ -220,6 +220,13 @@ int32_t ek_stage_times(ek_backend_t* be, float* ms /* [EK_STAGE_COUNT] */);
 /* Number of kernels this library launched on the backend since creation. */
 int64_t ek_kernel_launches(const ek_backend_t* be);
 
+/* Worker-level calls (`ek_expert_forward`, `ek_worker_forward_wire`) issued from several threads at
+ * once are served together: whoever holds the forward lock runs every request queued so far as one
+ * grouped launch per layer, the way the reference's 48 runtime threads each enter
+ * EKInstanceGate::forward (ek-computation/src/worker/core.rs:47-74) but share one GPU here.
+ * `calls` = requests served so far, `batches` = grouped passes that served them. */
+int32_t ek_worker_batch_stats(ek_backend_t* be, int64_t* calls, int64_t* batches);
+
 /* FP8 block scales inside the grouped GEMM.  0 (default): the scale is split into two bf16
  * terms and applied with packed bf16 arithmetic (16 significant bits of the scale, one final
  * rounding; equals the reference formula except within 2^-17 of a rounding boundary).  1: applied

@@ -181,6 +181,45 @@ def test_concurrent_forwards_and_loads(small):
     assert be.loaded() == 8
 
 
+def test_concurrent_worker_calls_share_grouped_launches(small):
+    """Single-expert calls from many threads (one RPC per expert in the reference worker) are
+    served in groups: same bits as the calls made one by one, fewer passes than calls."""
+    cfg, layer, be = small
+    Hh.register_layer(be, 0, layer)
+    xs = {e: OC.make_inputs(cfg, 3 + 5 * e, 100 + e) for e in range(8)}   # ragged batch sizes 3..38
+    alone = {e: be.expert_forward(be.expert_id(0, e), xs[e]) for e in range(8)}
+    for e in range(8):
+        Hh.assert_outputs_close(alone[e], O.expert_ffn(xs[e], *layer["experts"][e].bf16()), "single call")
+    calls0, batches0 = be.worker_batch_stats()
+    assert calls0 == batches0 == 8
+    rounds, errors = 25, []
+    start = threading.Barrier(8)
+
+    def worker(e):
+        try:
+            for _ in range(rounds):
+                start.wait()
+                y = be.expert_forward(be.expert_id(0, e), xs[e])
+                assert torch.equal(y, alone[e]), f"expert {e}: grouped result differs from the single call"
+        except Exception as ex:   # noqa: BLE001
+            errors.append(ex)
+            start.abort()
+
+    ths = [threading.Thread(target=worker, args=(e,)) for e in range(8)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    assert not errors, errors
+    calls, batches = be.worker_batch_stats()
+    assert calls - calls0 == 8 * rounds
+    assert batches - batches0 < 8 * rounds, "no two concurrent calls were ever served together"
+    # an unknown expert in a group fails alone
+    with pytest.raises(Exception):
+        be.expert_forward("nope/l0-e0", xs[0])
+    assert torch.equal(be.expert_forward(be.expert_id(0, 1), xs[1]), alone[1])
+
+
 def test_stage_times_and_launch_counter(small):
     cfg, layer, be = small
     Hh.register_layer(be, 0, layer)
