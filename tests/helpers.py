@@ -80,3 +80,18 @@ def golden_experts(t, layer: int, n: int):
 def golden_shared(t, layer: int):
     pre = f"model.layers.{layer}.mlp.shared_experts."
     return O.ExpertWeights(t[pre + "up_proj.weight"], t[pre + "gate_proj.weight"], t[pre + "down_proj.weight"])
+
+
+def build_host_shim(tmpdir) -> str:
+    """Compiles tests/host_shim/worker_threads.cpp (the C++ mirror of the worker driving the C ABI)
+    against the in-tree library; returns the binary's path."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib_dir = os.path.join(root, "expert-kit_b200", "lib")
+    out = os.path.join(str(tmpdir), "worker_threads")
+    cmd = ["g++", "-std=c++17", "-O2", "-Wall", "-Werror", "-I", os.path.join(root, "include"),
+           os.path.join(root, "tests", "host_shim", "worker_threads.cpp"), "-o", out,
+           "-L", lib_dir, "-lek_b200", "-Wl,-rpath," + lib_dir, "-pthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return out

@@ -66,3 +66,17 @@ def test_expert_id_parsing_matches_expert_key():
     for bad in ("qwen3-l0-e6", "qwen3/l0", "qwen3/lx-e1"):
         with pytest.raises(ek_b200.EKError):
             parse_expert_id(bad)
+
+
+def test_cpp_host_mirror_compiles_and_refuses_without_a_gpu(lib, tmp_path):
+    """include/ek_b200.hpp (ExpertDB / ExpertBackend / EKInstanceGate over the C ABI) compiles
+    warning-free and links; with no CUDA device the create error surfaces as EKError, exit code 3."""
+    import subprocess
+    import torch
+    import helpers as Hh
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the GPU test runs the driver")
+    exe = Hh.build_host_shim(tmp_path)
+    r = subprocess.run([exe, "256", "128", "4", "4", "2", "1"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 3, (r.returncode, r.stderr)
+    assert "no CUDA device" in r.stderr and "EK_CUDA" in r.stderr

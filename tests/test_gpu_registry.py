@@ -220,6 +220,23 @@ def test_concurrent_worker_calls_share_grouped_launches(small):
     assert torch.equal(be.expert_forward(be.expert_id(0, 1), xs[1]), alone[1])
 
 
+def test_cpp_worker_mirror_with_48_threads(tmp_path):
+    """The C++ mirror of the worker (include/ek_b200.hpp) with the reference's 48 runtime threads:
+    one EKInstanceGate::forward per expert; replies identical to the single-threaded ones,
+    malformed requests rejected as errors, and concurrent requests share grouped launches."""
+    import json
+    import subprocess
+    exe = Hh.build_host_shim(tmp_path)
+    r = subprocess.run([exe, "1024", "512", "48", "4", "48", "5"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    rep = json.loads(r.stdout.strip().splitlines()[-1])
+    assert rep["mismatches"] == 0 and rep["errors"] == 0 and rep["rejected"] == 4
+    assert rep["one_thread_passes"] == rep["one_thread_calls"] == 48 * 5
+    assert rep["threads_calls"] == 48 * 5
+    assert rep["threads_passes"] < rep["threads_calls"], rep
+    print(rep)
+
+
 def test_stage_times_and_launch_counter(small):
     cfg, layer, be = small
     Hh.register_layer(be, 0, layer)
