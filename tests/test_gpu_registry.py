@@ -231,7 +231,7 @@ def test_cpp_worker_mirror_with_48_threads(tmp_path):
     assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
     rep = json.loads(r.stdout.strip().splitlines()[-1])
     assert rep["mismatches"] == 0 and rep["errors"] == 0 and rep["rejected"] == 4
-    assert rep["one_thread_passes"] == rep["one_thread_calls"] == 48 * 5
+    assert rep["one_thread_passes"] == rep["one_thread_calls"] == 48 * 6   # warm-up round + 5 timed
     assert rep["threads_calls"] == 48 * 5
     assert rep["threads_passes"] < rep["threads_calls"], rep
     print(rep)
