@@ -428,6 +428,7 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
       if (encode_2d(be, &tp.x_map, x, (uint64_t)c.hidden, (uint64_t)T, 128)) {
         tp.w_map = L.router_map;
         tp.partial = be->partial;
+        tp.zero_counts = be->counts;
         tp.status = be->status;
         tp.T = T; tp.H = c.hidden; tp.E = c.n_experts;
         tp.n_atoms = (c.hidden + 63) / 64;
@@ -441,7 +442,7 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
       }
     }
     if (!tc_done) be->launches += launch_router_logits(rp, s);
-    be->launches += launch_route_select(rp, s);
+    be->launches += launch_route_select(rp, s, tc_done);
     ids = be->ids;
   } else {
     // caller-supplied ids may be invalid: rows that no expert claims must read as "absent"
@@ -463,9 +464,9 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   wp.n_shared = sh_T > 0 ? n_shared : 0; wp.T = sh_T; wp.Tk = Tk;
   wp.max_chunks = be->max_chunks;
   wp.status = be->status;
+  wp.counts_copy = L.last_counts;   // the layer's activation metric, read back by ek_expert_counts
   be->launches += launch_worklist(wp, s);
   be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T, s);
-  cudaMemcpyAsync(L.last_counts, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s);
   L.have_counts = true;
   mark(be, 2);
   run_ffn(be, L, nmax, 0);

@@ -70,6 +70,8 @@ __device__ __forceinline__ void weighted_rows(const CombineParams& p, const int*
 // order.  gridDim.y slices keep small batches from running on a handful of SMs.
 template <int BATCH>
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_row[kMaxK];
   __shared__ float s_w[kMaxK];
   const int t = blockIdx.x;
@@ -111,6 +113,8 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
 __global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __restrict__ obuf,
                                                         const int32_t* __restrict__ inv,
                                                         __nv_bfloat16* __restrict__ out, int32_t H) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x;  // token*k + slot
   const int row = inv[i];
   uint4* d = reinterpret_cast<uint4*>(out + (size_t)i * H);
@@ -124,6 +128,8 @@ __global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __r
 
 template <int BATCH>
 __global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, float* __restrict__ partial) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_row[kMaxK];
   __shared__ float s_w[kMaxK];
   const int t = blockIdx.x;
@@ -147,6 +153,8 @@ __global__ void __launch_bounds__(256) combine_finish_kernel(const float* __rest
                                                              const __nv_bfloat16* __restrict__ shared,
                                                              int32_t n_shared, int32_t T, int32_t H,
                                                              __nv_bfloat16* __restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int nv = H / 8, per = (nv + gridDim.y - 1) / gridDim.y;
   const int v_lo = blockIdx.y * per, v_hi = min(nv, v_lo + per);
@@ -209,28 +217,28 @@ static int h_slices(int T, int H) {
 
 int launch_combine_partial(const CombineParams& p, float* partial, cudaStream_t s) {
   if (p.T > 0) {
-    if (p.T < 1024) combine_partial_kernel<8><<<dim3(p.T, h_slices(p.T, p.H)), 256, 0, s>>>(p, partial);
-    else combine_partial_kernel<2><<<dim3(p.T, 1), 256, 0, s>>>(p, partial);
+    if (p.T < 1024) launch_pdl(combine_partial_kernel<8>, dim3(p.T, h_slices(p.T, p.H)), dim3(256), 0, s, p, partial);
+    else launch_pdl(combine_partial_kernel<2>, dim3(p.T, 1), dim3(256), 0, s, p, partial);
   }
   return p.T > 0 ? 1 : 0;
 }
 int launch_combine_finish(const float* reduced, const __nv_bfloat16* shared, int32_t n_shared, int32_t T,
                           int32_t H, __nv_bfloat16* y, cudaStream_t s) {
-  if (T > 0) combine_finish_kernel<<<dim3(T, h_slices(T, H)), 256, 0, s>>>(reduced, shared, n_shared, T, H, y);
+  if (T > 0) launch_pdl(combine_finish_kernel, dim3(T, h_slices(T, H)), dim3(256), 0, s, reduced, shared, n_shared, T, H, y);
   return T > 0 ? 1 : 0;
 }
 
 int launch_combine(const CombineParams& p, cudaStream_t s) {
   if (p.T > 0) {
-    if (p.T < 1024) combine_kernel<8><<<dim3(p.T, h_slices(p.T, p.H)), 256, 0, s>>>(p);
-    else combine_kernel<2><<<dim3(p.T, 1), 256, 0, s>>>(p);
+    if (p.T < 1024) launch_pdl(combine_kernel<8>, dim3(p.T, h_slices(p.T, p.H)), dim3(256), 0, s, p);
+    else launch_pdl(combine_kernel<2>, dim3(p.T, 1), dim3(256), 0, s, p);
   }
   return p.T > 0 ? 1 : 0;
 }
 
 int launch_unpermute(const __nv_bfloat16* obuf, const int32_t* inv, __nv_bfloat16* out, int32_t T,
                      int32_t k, int32_t H, cudaStream_t s) {
-  if (T * k > 0) unpermute_kernel<<<T * k, 128, 0, s>>>(obuf, inv, out, H);
+  if (T * k > 0) launch_pdl(unpermute_kernel, dim3(T * k), dim3(128), 0, s, obuf, inv, out, H);
   return T * k > 0 ? 1 : 0;
 }
 

@@ -7,6 +7,33 @@
 
 #include "../../include/ek_b200.h"
 
+#ifdef __CUDACC__
+#include <utility>
+// Programmatic dependent launch: the kernels of one layer pass are launched back to back with this
+// attribute, each begins with pdl_wait() (returns when every earlier kernel of the stream has
+// completed and its writes are visible) and then lets its successor start launching, so that the
+// launch latency and the prologue of kernel n+1 overlap the tail of kernel n.  Nothing produced by
+// an earlier kernel may be touched before pdl_wait().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+#endif
+
 namespace ek {
 
 // ---- weight tile geometry ----------------------------------------------------------------
@@ -90,6 +117,7 @@ struct RouterTcParams {
   CUtensorMap x_map;        // activations [T,H] bf16, box {64, 128}, 128-byte swizzle
   CUtensorMap w_map;        // router weight [E,H] bf16, box {64, E}
   float* partial;           // [n_splits][T][E]
+  int32_t* zero_counts = nullptr;   // [E] histogram cleared here for the select kernel that follows (may be null)
   DevStatus* status;
   int32_t T, H, E;
   int32_t n_atoms;          // ceil(H / 64)
@@ -100,7 +128,8 @@ bool router_tc_supported(int E, int H);
 void router_tc_plan(int T, int H, int n_sm, int* n_splits, int* atoms_per_split);
 int launch_router_tc(const RouterTcParams& p, cudaStream_t s);
 int launch_f32_to_bf16_check(const float* src, __nv_bfloat16* dst, int64_t n, int32_t* inexact, cudaStream_t s);
-int launch_route_select(const RouteParams& p, cudaStream_t s);
+// `counts_cleared`: the router kernel launched just before already zeroed p.counts
+int launch_route_select(const RouteParams& p, cudaStream_t s, bool counts_cleared = false);
 int launch_histogram(const int32_t* ids, int32_t n, int32_t E, int32_t* counts, DevStatus* st,
                      cudaStream_t s);
 
@@ -122,6 +151,7 @@ struct WorklistParams {
   const int32_t* registered; // [slots]
   ChunkDesc* chunks;         // out
   int32_t* n_chunks;         // out (single int)
+  int32_t* counts_copy = nullptr;   // out [E]: copy of counts kept per layer for the activation metric (may be null)
   int32_t E, e_lo, e_hi;     // local expert window; slot = e - e_lo
   int32_t chunk_rows;        // rows per chunk
   int32_t n_shared, T;       // shared virtual experts: slot = (e_hi-e_lo)+j, in_row = Tk, out_row = Tk+j*T

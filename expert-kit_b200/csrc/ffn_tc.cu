@@ -239,6 +239,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
+  // barriers and tensor memory are this CTA's own; everything below reads what earlier kernels wrote
+  pdl_wait();
+  pdl_trigger();
   const int n_chunks = *p.n_chunks;
   const int n_rt = GATEUP ? p.d.it : p.d.hp;   // work items per chunk
   const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;   // K tiles of the GEMM = pipeline stages per work item
@@ -571,7 +574,7 @@ int launch_one(const FfnParams& p, cudaStream_t s) {
   using C = Cfg<QUANT, GATEUP, NMAX>;
   const int smem = C::STAGES * C::STAGE_BYTES + 1024;
   cudaFuncSetAttribute(ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE><<<p.n_sm, kThreads, smem, s>>>(p);
+  launch_pdl(ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE>, dim3(p.n_sm), dim3(kThreads), (size_t)smem, s, p);
   return 1;
 }
 

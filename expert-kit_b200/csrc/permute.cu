@@ -17,6 +17,8 @@ namespace {
 // One CTA per expert: offsets[e] = sum of counts of local experts below e, then one ordered
 // pass over all assignments, ranking the matches with warp scans.
 __global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_red[8];
   __shared__ int s_base;
   const int e = blockIdx.x;
@@ -88,10 +90,14 @@ __global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
 // Chunk descriptors: every local expert's row range cut into pieces of `chunk_rows`, followed
 // by the virtual shared experts (all T tokens each).
 __global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_scan[1024];
   __shared__ int s_total;
   const int tid = threadIdx.x;
   const int n_local = p.e_hi - p.e_lo;
+  if (p.counts_copy)
+    for (int e = tid; e < p.E; e += 1024) p.counts_copy[e] = p.counts[e];
   int running = 0;
   for (int e0 = 0; e0 < n_local; e0 += 1024) {
     const int le = e0 + tid;
@@ -174,6 +180,8 @@ __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __rest
                                                      const int32_t* __restrict__ n_routed,
                                                      __nv_bfloat16* __restrict__ xp, int32_t T,
                                                      int32_t k, int32_t H, int32_t shared_t0) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int Tk = T * k;
   int src;
@@ -191,12 +199,12 @@ __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __rest
 }  // namespace
 
 int launch_permute(const PermuteParams& p, cudaStream_t s) {
-  if (p.E > 0) permute_kernel<<<p.E, 256, 0, s>>>(p);
+  if (p.E > 0) launch_pdl(permute_kernel, dim3(p.E), dim3(256), 0, s, p);
   return 1;
 }
 
 int launch_worklist(const WorklistParams& p, cudaStream_t s) {
-  worklist_kernel<<<1, 1024, 0, s>>>(p);
+  launch_pdl(worklist_kernel, dim3(1), dim3(1024), 0, s, p);
   return 1;
 }
 
@@ -204,7 +212,7 @@ int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_
                   __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t shared_t0, int32_t shared_T,
                   cudaStream_t s) {
   const int rows = T * k + shared_T;
-  if (rows > 0) gather_kernel<<<rows, 128, 0, s>>>(x, perm, n_routed, xp, T, k, H, shared_t0);
+  if (rows > 0) launch_pdl(gather_kernel, dim3(rows), dim3(128), 0, s, x, perm, n_routed, xp, T, k, H, shared_t0);
   return rows > 0 ? 1 : 0;
 }
 

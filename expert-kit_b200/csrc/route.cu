@@ -28,6 +28,8 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
 // the result is rounded to bf16 (and stored widened).
 template <bool WG_F32>
 __global__ void __launch_bounds__(256) router_logits_kernel(RouteParams p) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ __align__(16) __nv_bfloat16 xs[kTokTile][kHChunk];
   const int t0 = blockIdx.x * kTokTile;
   const int e0 = blockIdx.y * kExpTile;
@@ -111,6 +113,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 
 // One warp per token.
 __global__ void __launch_bounds__(kSelWarps * 32) route_select_kernel(RouteParams p) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float s_score[kSelWarps][kMaxExperts];   // unbiased scores (weights come from these)
   __shared__ float s_choice[kSelWarps][kMaxExperts];  // biased / masked scores used for selection
   __shared__ float s_group[kSelWarps][64];
@@ -244,6 +248,8 @@ __global__ void __launch_bounds__(kSelWarps * 32) route_select_kernel(RouteParam
 
 __global__ void histogram_kernel(const int32_t* ids, int32_t n, int32_t E, int32_t* counts,
                                  DevStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int e = ids[i];
@@ -263,22 +269,22 @@ __global__ void histogram_kernel(const int32_t* ids, int32_t n, int32_t E, int32
 int launch_router_logits(const RouteParams& p, cudaStream_t s) {
   dim3 grid((p.T + kTokTile - 1) / kTokTile, (p.E + kExpTile - 1) / kExpTile);
   if (p.wg_f32)
-    router_logits_kernel<true><<<grid, 256, 0, s>>>(p);
+    launch_pdl(router_logits_kernel<true>, grid, dim3(256), 0, s, p);
   else
-    router_logits_kernel<false><<<grid, 256, 0, s>>>(p);
+    launch_pdl(router_logits_kernel<false>, grid, dim3(256), 0, s, p);
   return 1;
 }
 
-int launch_route_select(const RouteParams& p, cudaStream_t s) {
-  cudaMemsetAsync(p.counts, 0, sizeof(int32_t) * p.E, s);
-  route_select_kernel<<<(p.T + kSelWarps - 1) / kSelWarps, kSelWarps * 32, 0, s>>>(p);
+int launch_route_select(const RouteParams& p, cudaStream_t s, bool counts_cleared) {
+  if (!counts_cleared) cudaMemsetAsync(p.counts, 0, sizeof(int32_t) * p.E, s);
+  launch_pdl(route_select_kernel, dim3((p.T + kSelWarps - 1) / kSelWarps), dim3(kSelWarps * 32), 0, s, p);
   return 1;
 }
 
 int launch_histogram(const int32_t* ids, int32_t n, int32_t E, int32_t* counts, DevStatus* st,
                      cudaStream_t s) {
   cudaMemsetAsync(counts, 0, sizeof(int32_t) * E, s);
-  if (n > 0) histogram_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, n, E, counts, st);
+  if (n > 0) launch_pdl(histogram_kernel, dim3((n + 255) / 256), dim3(256), 0, s, ids, n, E, counts, st);
   return n > 0 ? 1 : 0;
 }
 

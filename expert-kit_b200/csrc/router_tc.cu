@@ -47,6 +47,10 @@ __global__ void __launch_bounds__(192, 1) router_tc_kernel(const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem;
+  pdl_wait();
+  pdl_trigger();
+  if (p.zero_counts && blockIdx.x == 0 && blockIdx.y == 0)
+    for (int i = tid; i < p.E; i += blockDim.x) p.zero_counts[i] = 0;
   const int m0 = blockIdx.x * kTokTile;
   const int a_lo = blockIdx.y * p.atoms_per_split;
   const int a_hi = min(a_lo + p.atoms_per_split, p.n_atoms);
@@ -152,7 +156,7 @@ int launch_router_tc(const RouterTcParams& p, cudaStream_t s) {
   const int smem = kStages * (kAtomBytesA + p.E * 128) + 1024;
   cudaFuncSetAttribute(router_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   dim3 grid((p.T + kTokTile - 1) / kTokTile, p.n_splits);
-  router_tc_kernel<<<grid, 192, smem, s>>>(p);
+  launch_pdl(router_tc_kernel, grid, dim3(192), (size_t)smem, s, p);
   return 1;
 }
 
