@@ -901,6 +901,155 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
   return EK_OK;
 }
 
+// ---- device-ready form of an expert: export and direct registration -------------------------
+// The weight server keeps fetched bundles in a file cache so a restarted worker does not hit the
+// store again (ek-db/src/safetensor/mod.rs:144-171).  The same idea one step later: the tiles and
+// scales exactly as this library keeps them in HBM, so that a restart (or a second GPU that owns
+// the same expert) skips decoding, re-tiling and the fp8 byte re-encoding.
+namespace {
+
+struct TileBlobHeader {
+  char magic[8];            // "EKTILES\0"
+  uint32_t version;         // EK_TILE_LAYOUT_VERSION
+  int32_t quant, hidden, intermediate, n_virtual;
+  uint32_t reserved;
+  uint64_t gu_bytes, dn_bytes, gu_scale_bytes, dn_scale_bytes;   // per virtual slot
+};
+static_assert(sizeof(TileBlobHeader) == 64, "blob header is 64 bytes");
+
+void tile_sizes(const ek_backend* be, TileBlobHeader* h) {
+  const Dims& d = be->d;
+  h->gu_bytes = (uint64_t)d.it * d.kt_gu * 2 * kTileBytes;
+  h->dn_bytes = (uint64_t)d.hp * d.kt_dn * 2 * kTileBytes;
+  const bool q = be->cfg.quant != EK_QUANT_BF16;
+  h->gu_scale_bytes = q ? (uint64_t)d.it * d.kt_gu * 2 * 4 : 0;
+  h->dn_scale_bytes = q ? (uint64_t)d.hp * d.kt_dn * 2 * 4 : 0;
+}
+
+int check_expert_id(ek_backend* be, const char* id, int* layer, int* expert, bool* shared) {
+  const ek_config_t& c = be->cfg;
+  std::string model;
+  if (!parse_id(id, model, *layer, *expert, *shared)) return fail(be, EK_INVALID_INPUT, "invalid expert id: %s", id);
+  if (c.model_name[0] && model != c.model_name)
+    return fail(be, EK_INVALID_INPUT, "expert id %s does not belong to model %s", id, c.model_name);
+  if (*shared && c.n_shared_experts == 0) return fail(be, EK_INVALID_INPUT, "layer has no shared expert: %s", id);
+  if (!*shared && (*expert < be->e_lo || *expert >= be->e_hi))
+    return fail(be, EK_INVALID_INPUT, "expert %d is not in this rank's range [%d,%d)", *expert, be->e_lo, be->e_hi);
+  return EK_OK;
+}
+
+}  // namespace
+
+int32_t ek_expert_export_tiles(ek_backend_t* be, const char* id, void* blob, size_t cap, size_t* needed) {
+  if (!be || !id || !needed) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  int layer, expert;
+  bool shared;
+  int rc = check_expert_id(be, id, &layer, &expert, &shared);
+  if (rc != EK_OK) return rc;
+  TileBlobHeader h;
+  memset(&h, 0, sizeof h);
+  memcpy(h.magic, "EKTILES", 8);
+  h.version = EK_TILE_LAYOUT_VERSION;
+  h.quant = be->cfg.quant; h.hidden = be->cfg.hidden; h.intermediate = be->cfg.intermediate;
+  h.n_virtual = shared ? be->cfg.n_shared_experts : 1;
+  tile_sizes(be, &h);
+  const size_t per = h.gu_bytes + h.dn_bytes + h.gu_scale_bytes + h.dn_scale_bytes;
+  *needed = sizeof h + per * h.n_virtual;
+  if (!blob || cap < *needed) return fail(be, EK_INVALID_INPUT, "tile blob needs %zu bytes", *needed);
+  std::lock_guard<std::mutex> lg(be->load_mu);
+  int slot0;
+  Layer* L;
+  {
+    std::shared_lock<std::shared_mutex> g(be->reg_mu);
+    auto it = be->experts.find(id);
+    if (it == be->experts.end()) return fail(be, EK_EXPERT_NOT_FOUND, "%s", id);
+    L = &be->layers[it->second.layer];
+    slot0 = it->second.slot;
+  }
+  cudaStream_t ls = be->load_stream;
+  uint8_t* o = reinterpret_cast<uint8_t*>(blob);
+  memcpy(o, &h, sizeof h);
+  o += sizeof h;
+  for (int v = 0; v < h.n_virtual; ++v) {
+    const int slot = slot0 + v;
+    CK(cudaMemcpyAsync(o, L->gu + (size_t)slot * h.gu_bytes, h.gu_bytes, cudaMemcpyDeviceToHost, ls));
+    o += h.gu_bytes;
+    CK(cudaMemcpyAsync(o, L->dn + (size_t)slot * h.dn_bytes, h.dn_bytes, cudaMemcpyDeviceToHost, ls));
+    o += h.dn_bytes;
+    if (h.gu_scale_bytes) {
+      CK(cudaMemcpyAsync(o, reinterpret_cast<const uint8_t*>(L->gu_scale) + (size_t)slot * h.gu_scale_bytes, h.gu_scale_bytes, cudaMemcpyDeviceToHost, ls));
+      o += h.gu_scale_bytes;
+      CK(cudaMemcpyAsync(o, reinterpret_cast<const uint8_t*>(L->dn_scale) + (size_t)slot * h.dn_scale_bytes, h.dn_scale_bytes, cudaMemcpyDeviceToHost, ls));
+      o += h.dn_scale_bytes;
+    }
+  }
+  CK(cudaStreamSynchronize(ls));
+  return EK_OK;
+}
+
+int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* blob, size_t len) {
+  if (!be || !id || !blob) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  int layer, expert;
+  bool shared;
+  int rc = check_expert_id(be, id, &layer, &expert, &shared);
+  if (rc != EK_OK) return rc;
+  TileBlobHeader h, want;
+  if (len < sizeof h) return fail(be, EK_SAFETENSOR, "tile blob shorter than its header");
+  memcpy(&h, blob, sizeof h);
+  if (memcmp(h.magic, "EKTILES", 8) != 0) return fail(be, EK_SAFETENSOR, "not a tile blob");
+  if (h.version != EK_TILE_LAYOUT_VERSION)
+    return fail(be, EK_UNSUPPORTED, "tile blob has layout version %u, this library writes %d: register the bundle instead", h.version, EK_TILE_LAYOUT_VERSION);
+  memset(&want, 0, sizeof want);
+  tile_sizes(be, &want);
+  const int n_virtual = shared ? be->cfg.n_shared_experts : 1;
+  if (h.quant != be->cfg.quant || h.hidden != be->cfg.hidden || h.intermediate != be->cfg.intermediate ||
+      h.n_virtual != n_virtual || h.gu_bytes != want.gu_bytes || h.dn_bytes != want.dn_bytes ||
+      h.gu_scale_bytes != want.gu_scale_bytes || h.dn_scale_bytes != want.dn_scale_bytes)
+    return fail(be, EK_INVALID_INPUT, "tile blob was written for another configuration (quant %d, H %d, I %d, %d slots)",
+                h.quant, h.hidden, h.intermediate, h.n_virtual);
+  const size_t per = h.gu_bytes + h.dn_bytes + h.gu_scale_bytes + h.dn_scale_bytes;
+  if (len != sizeof h + per * n_virtual) return fail(be, EK_SAFETENSOR, "tile blob has %zu bytes, expected %zu", len, sizeof h + per * n_virtual);
+
+  std::lock_guard<std::mutex> lg(be->load_mu);
+  Layer* L = nullptr;
+  {
+    std::unique_lock<std::shared_mutex> g(be->reg_mu);
+    rc = ensure_layer(be, layer, &L);
+    if (rc != EK_OK) return rc;
+  }
+  cudaStream_t ls = be->load_stream;
+  // the slot may still be read by forwards queued before an eviction
+  CK(cudaEventRecord(be->fwd_done, be->stream));
+  CK(cudaStreamWaitEvent(ls, be->fwd_done, 0));
+  const uint8_t* in = reinterpret_cast<const uint8_t*>(blob) + sizeof h;
+  for (int v = 0; v < n_virtual; ++v) {
+    const int slot = shared ? be->n_local + v : expert - be->e_lo;
+    CK(cudaMemcpyAsync(L->gu + (size_t)slot * h.gu_bytes, in, h.gu_bytes, cudaMemcpyHostToDevice, ls));
+    in += h.gu_bytes;
+    CK(cudaMemcpyAsync(L->dn + (size_t)slot * h.dn_bytes, in, h.dn_bytes, cudaMemcpyHostToDevice, ls));
+    in += h.dn_bytes;
+    if (h.gu_scale_bytes) {
+      CK(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(L->gu_scale) + (size_t)slot * h.gu_scale_bytes, in, h.gu_scale_bytes, cudaMemcpyHostToDevice, ls));
+      in += h.gu_scale_bytes;
+      CK(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(L->dn_scale) + (size_t)slot * h.dn_scale_bytes, in, h.dn_scale_bytes, cudaMemcpyHostToDevice, ls));
+      in += h.dn_scale_bytes;
+    }
+    const int32_t one = 1;
+    CK(cudaMemcpyAsync(L->registered + slot, &one, sizeof one, cudaMemcpyHostToDevice, ls));
+  }
+  CK(cudaStreamSynchronize(ls));
+  {
+    std::unique_lock<std::shared_mutex> g(be->reg_mu);
+    for (int v = 0; v < n_virtual; ++v) L->host_registered[shared ? be->n_local + v : expert - be->e_lo] = 1;
+    be->loading.erase(id);
+    ExpertRef ref{layer, shared ? be->n_local : expert - be->e_lo};
+    be->experts[id] = ref;
+  }
+  return EK_OK;
+}
+
 int32_t ek_expert_register_safetensors(ek_backend_t* be, const char* id, const void* blob, size_t len) {
   if (!be || !id || !blob) return EK_INVALID_INPUT;
   std::vector<ekst::Entry> ent;

@@ -1,5 +1,5 @@
 """B200-native expert-worker compute backend for Expert Kit (Python side of the C ABI)."""
-from .backend import Backend, BackendConfig, EKError  # noqa: F401
+from .backend import Backend, BackendConfig, EKError, TileCache  # noqa: F401
 from .client import LocalExpertKitClient  # noqa: F401
 from . import _lib  # noqa: F401
 from .ep import ExpertParallelMoE, BackendStages, plan_exchange  # noqa: F401,E402

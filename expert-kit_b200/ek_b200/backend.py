@@ -7,6 +7,8 @@ is `expert_forward`; `EKInstanceGate::forward` (ek-computation/src/worker/core.r
 `moe_forward`.  torch is used only to own buffers and hand out pointers."""
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Tuple
@@ -135,6 +137,21 @@ class Backend:
         """From the serialised per-expert bundle of the weight server."""
         buf = (C.c_char * len(blob)).from_buffer_copy(blob)
         self._check(self._lib.ek_expert_register_safetensors(self._h, expert_id.encode(), buf, len(blob)))
+
+    def export_tiles(self, expert_id: str) -> bytes:
+        """The registered expert in its device-ready form (tiles + scales as kept in HBM)."""
+        need = C.c_size_t(0)
+        self._lib.ek_expert_export_tiles(self._h, expert_id.encode(), None, 0, C.byref(need))
+        if need.value == 0:
+            raise EKError(3, self._lib.ek_last_error(self._h).decode())
+        buf = (C.c_char * need.value)()
+        self._check(self._lib.ek_expert_export_tiles(self._h, expert_id.encode(), buf, need.value, C.byref(need)))
+        return bytes(buf)
+
+    def register_tiles(self, expert_id: str, blob: bytes):
+        """Registers a blob written by `export_tiles` with plain copies (no decoding, no re-tiling)."""
+        buf = (C.c_char * len(blob)).from_buffer_copy(blob)
+        self._check(self._lib.ek_expert_register_tiles(self._h, expert_id.encode(), buf, len(blob)))
 
     def mark_loading(self, expert_id: str) -> bool:
         fresh = C.c_int32(0)
@@ -337,3 +354,39 @@ def expert_tensors(layer: int, expert, up, gate, down, up_s=None, gate_s=None, d
         t[f"{base}.down_proj.weight_scale_inv"] = down_s
         t[f"{base}.gate_proj.weight_scale_inv"] = gate_s
     return t
+
+
+class TileCache:
+    """File cache of device-ready experts, beside the raw bundles the weight server caches
+    (ek-db/src/safetensor/mod.rs:144-171: `fs` cache keyed by ExpertKey::as_object_key).  A hit
+    registers the expert with plain copies; a miss (or a blob written by another layout version or
+    configuration) loads the bundle through `fetch_bundle`, registers it and writes the blob."""
+
+    def __init__(self, backend: "Backend", root: str):
+        self.be, self.root = backend, root
+        os.makedirs(root, exist_ok=True)
+        self.hits = self.misses = 0
+
+    def path(self, expert_id: str) -> str:
+        c = self.be.cfg
+        name = f"{expert_id.replace('/', '__')}.v{L.EK_TILE_LAYOUT_VERSION}.q{c.quant}.h{c.hidden}.i{c.intermediate}.ektiles"
+        return os.path.join(self.root, name)
+
+    def load(self, expert_id: str, fetch_bundle) -> bool:
+        """Registers `expert_id`; returns True when the cache served it."""
+        p = self.path(expert_id)
+        if os.path.exists(p):
+            try:
+                with open(p, "rb") as f:
+                    self.be.register_tiles(expert_id, f.read())
+                self.hits += 1
+                return True
+            except EKError:
+                os.remove(p)          # stale or foreign blob: fall back to the bundle
+        self.be.register_bundle(expert_id, fetch_bundle(expert_id))
+        tmp = p + ".tmp"
+        with open(tmp, "wb") as f:
+            f.write(self.be.export_tiles(expert_id))
+        os.replace(tmp, p)
+        self.misses += 1
+        return False

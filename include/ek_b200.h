@@ -129,6 +129,17 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id,
 int32_t ek_expert_register_safetensors(ek_backend_t* be, const char* id,
                                        const void* blob, size_t blob_len);
 
+/* The expert as this library keeps it in HBM (16 KiB tiles, re-encoded FP8 bytes, re-ordered
+ * scales), for a cache next to the raw bundle in the weight server's file cache
+ * (ek-db/src/safetensor/mod.rs:144-171): a restart registers the blob with plain copies and skips
+ * decoding and re-tiling.  The blob is only valid for the same quant/hidden/intermediate and for
+ * EK_TILE_LAYOUT_VERSION; anything else is refused (EK_UNSUPPORTED / EK_INVALID_INPUT) and the
+ * caller falls back to the bundle.  *needed receives the blob size; EK_INVALID_INPUT when `cap`
+ * is too small. */
+#define EK_TILE_LAYOUT_VERSION 3
+int32_t ek_expert_export_tiles(ek_backend_t* be, const char* id, void* blob, size_t cap, size_t* needed);
+int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* blob, size_t blob_len);
+
 /* ExpertDB::mark_loading (manager.rs:60-70): *fresh = 1 when this call claimed the id. */
 int32_t ek_expert_mark_loading(ek_backend_t* be, const char* id, int32_t* fresh);
 /* ExpertDB::remove (manager.rs:71-74; caller: worker/state.rs:157-165).  Removing an unknown id

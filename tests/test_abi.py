@@ -33,6 +33,12 @@ def test_every_declared_symbol_is_exported(lib):
         assert hasattr(lib, n), f"{n} declared in ek_b200.h but not exported"
 
 
+def test_layout_version_matches_the_header():
+    import ek_b200._lib as L
+    src = open(os.path.join(ROOT, "include", "ek_b200.h")).read()
+    assert int(re.search(r"#define EK_TILE_LAYOUT_VERSION (\d+)", src).group(1)) == L.EK_TILE_LAYOUT_VERSION
+
+
 def test_binding_covers_the_header():
     import ek_b200._lib as L
     assert sorted(L.SIGNATURES) == declared_functions()

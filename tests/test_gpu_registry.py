@@ -237,6 +237,74 @@ def test_cpp_worker_mirror_with_48_threads(tmp_path):
     print(rep)
 
 
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_tile_blob_round_trip_and_file_cache(tmp_path, quant):
+    """Device-ready blobs: export -> evict -> register the blob -> identical outputs; blobs of
+    another layout version or configuration are refused; the file cache serves the second load."""
+    import ek_b200
+    cfg = O.MoEConfig(hidden=256, intermediate=128, n_experts=4, top_k=2, scoring=O.SCORE_SIGMOID, n_shared=1,
+                      quant=quant)
+    layer = OC.make_layer(cfg, 77)
+    be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=32))
+    try:
+        Hh.register_layer(be, 0, layer)
+        x = OC.make_inputs(cfg, 9, 5)
+        ids = [be.expert_id(0, 1), be.shared_id(0)]
+        before = {i: be.expert_forward(i, x) for i in ids}
+        y_fused = be.moe_forward_fused(0, x)
+        blobs = {i: be.export_tiles(i) for i in ids}
+        for i in ids:
+            be.evict(i)
+            assert not be.has(i)
+            be.register_tiles(i, blobs[i])
+            assert be.has(i)
+            assert torch.equal(be.expert_forward(i, x), before[i])
+        assert torch.equal(be.moe_forward_fused(0, x), y_fused)
+        # refused: other layout version, other configuration, truncated, not a blob
+        bad = bytearray(blobs[ids[0]])
+        bad[8] ^= 0xFF
+        with pytest.raises(ek_b200.EKError) as e:
+            be.register_tiles(ids[0], bytes(bad))
+        assert e.value.status == 20
+        with pytest.raises(ek_b200.EKError):
+            be.register_tiles(ids[0], blobs[ids[0]][:-16])
+        with pytest.raises(ek_b200.EKError):
+            be.register_tiles(ids[0], b"x" * 4096)
+        other = ek_b200.Backend(Hh.backend_config(O.MoEConfig(hidden=256, intermediate=256, n_experts=4, top_k=2,
+                                                              quant=quant), max_tokens=32))
+        try:
+            with pytest.raises(ek_b200.EKError):
+                other.register_tiles(ids[0], blobs[ids[0]])
+        finally:
+            other.close()
+        assert torch.equal(be.expert_forward(ids[0], x), before[ids[0]])   # the failed loads left the slot alone
+        # file cache: miss writes the blob, hit needs no bundle
+        from safetensors.torch import save as st_save
+        w = layer["experts"][2]
+        tensors = {"w1.weight": w.up, "w2.weight": w.down, "w3.weight": w.gate}
+        if quant != "bf16":
+            tensors.update({"w1.weight_scale_inv": w.up_s, "w2.weight_scale_inv": w.down_s, "w3.weight_scale_inv": w.gate_s})
+        bundle = st_save({k: v.contiguous() for k, v in tensors.items()})
+        fetched = []
+
+        def fetch(eid):
+            fetched.append(eid)
+            return bundle
+
+        eid = be.expert_id(0, 2)
+        want = be.expert_forward(eid, x)
+        cache = ek_b200.TileCache(be, str(tmp_path / "tiles"))
+        be.evict(eid)
+        assert cache.load(eid, fetch) is False and fetched == [eid]
+        assert torch.equal(be.expert_forward(eid, x), want)
+        be.evict(eid)
+        assert cache.load(eid, fetch) is True and fetched == [eid]
+        assert torch.equal(be.expert_forward(eid, x), want)
+        assert (cache.hits, cache.misses) == (1, 1)
+    finally:
+        be.close()
+
+
 def test_stage_times_and_launch_counter(small):
     cfg, layer, be = small
     Hh.register_layer(be, 0, layer)
