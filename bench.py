@@ -655,7 +655,8 @@ def main():
                 missing = (~present).nonzero().flatten()
                 if missing.numel() == 0:
                     break
-                ids[:missing.numel(), 0] = missing
+                pos = torch.arange(missing.numel(), device=dev)
+                ids[pos % Ts, pos // Ts] = missing          # slot 0 of every token first, then slot 1, ...
             return ids.to(torch.int32).contiguous()
 
         steps = []
