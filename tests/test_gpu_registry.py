@@ -305,6 +305,38 @@ def test_tile_blob_round_trip_and_file_cache(tmp_path, quant):
         be.close()
 
 
+def test_layer_pass_can_be_captured_in_a_cuda_graph():
+    """A decode loop may capture the device-resident call once and replay it: the pass issues no
+    synchronisation, allocation or host read-back, and its programmatic launch edges survive capture."""
+    import ek_b200
+    cfg = O.MoEConfig(hidden=512, intermediate=256, n_experts=16, top_k=4, scoring=O.SCORE_SIGMOID, n_group=4,
+                      topk_group=2, n_shared=1, routed_scaling=2.5, quant="fp8")
+    layer = OC.make_layer(cfg, 5)
+    be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=32))
+    try:
+        Hh.register_layer(be, 0, layer, device="cuda")
+        s = torch.cuda.Stream()
+        be.set_stream(s.cuda_stream)
+        x = OC.make_inputs(cfg, 8, 1).cuda()
+        y_eager, y_graph = torch.empty_like(x), torch.empty_like(x)
+        with torch.cuda.stream(s):
+            be.moe_forward_fused_async(0, x, y_eager)      # first call outside capture (one-time attribute set-up)
+        be.sync()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            be.moe_forward_fused_async(0, x, y_graph)
+        for seed in (2, 3):
+            x.copy_(OC.make_inputs(cfg, 8, seed).cuda())
+            graph.replay()
+            with torch.cuda.stream(s):
+                be.moe_forward_fused_async(0, x, y_eager)
+            be.sync()
+            torch.cuda.synchronize()
+            assert torch.equal(y_graph, y_eager)
+    finally:
+        be.close()
+
+
 def test_stage_times_and_launch_counter(small):
     cfg, layer, be = small
     Hh.register_layer(be, 0, layer)
