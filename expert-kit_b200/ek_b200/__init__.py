@@ -3,3 +3,4 @@ from .backend import Backend, BackendConfig, EKError, TileCache  # noqa: F401
 from .client import LocalExpertKitClient  # noqa: F401
 from . import _lib  # noqa: F401
 from .ep import ExpertParallelMoE, BackendStages, plan_exchange  # noqa: F401,E402
+from .modules import B200MoEBlock  # noqa: F401,E402

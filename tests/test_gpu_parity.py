@@ -392,3 +392,28 @@ def test_continuous_batching_stream_ragged_packing():
         assert torch.equal(counts, torch.bincount(ids.reshape(-1).long(), minlength=cfg.n_experts).to(torch.int32))
         assert int(counts.min()) >= 1
     be.close()
+
+
+def test_moe_block_module_matches_the_golden_blocks():
+    """`B200MoEBlock` in the place of the reference's intercepted blocks: 3-D hidden states in, block
+    output out, on torch's current stream with no synchronisation in between."""
+    import ek_b200
+    for name, want_logits in (("qwen3_tiny", True), ("dsv3_tiny", False)):
+        t, cfg, layer = _golden_case(name)
+        be = _backend(cfg, layer, 32)
+        try:
+            block = ek_b200.B200MoEBlock(be, 0, return_router_logits=want_logits)
+            x3 = t["x"].cuda().view(1, t["x"].shape[0], -1)          # [batch, seq, H] as the decoder passes it
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                out = block(x3)
+                y = out[0] if want_logits else out
+                doubled = y.float() * 2                               # a dependent op on the same stream, no sync
+            side.synchronize()
+            assert y.shape == x3.shape
+            _close(y.view(-1, y.shape[-1]).cpu(), t["y_remote"], name + " block output")
+            assert torch.equal(doubled.cpu(), y.float().cpu() * 2)
+            if want_logits:
+                assert out[1].shape == (t["x"].shape[0], cfg.n_experts)
+        finally:
+            be.close()
