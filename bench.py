@@ -423,6 +423,7 @@ def main_ep(args, rank: int, world: int, local: int):
                 "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
                 "layer_roofline": layer, "cpu_baseline": base}
         print(json.dumps(line))
+    moe_one.close()
     be.close()
     dist.barrier()
     dist.destroy_process_group()
@@ -446,8 +447,9 @@ def main():
                          "from this many host threads; reported under 'worker_path'")
     ap.add_argument("--layers", type=int, default=1,
                     help="MoE layers per step (58 = the full DeepSeek-V3 expert stack; each layer has its own weights)")
-    ap.add_argument("--ep-mode", default="auto", choices=["auto", "gather", "a2a"],
-                    help="exchange scheme at N > 1 (auto: all-gather/reduce-scatter up to 2048 global tokens)")
+    ap.add_argument("--ep-mode", default="auto", choices=["auto", "gather", "a2a", "peer"],
+                    help="exchange scheme at N > 1 (auto: all-gather/reduce-scatter up to 2048 global tokens; peer: the same "
+                         "scheme with the library's own kernels over peer memory instead of NCCL collectives)")
     ap.add_argument("--experts", type=int, default=E,
                     help="routed experts (default: the full 256; smaller values give profiler-sized cases)")
     args = ap.parse_args()

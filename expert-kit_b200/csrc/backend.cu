@@ -48,6 +48,17 @@ struct ExpertRef {
 
 }  // namespace
 
+// Buffers of the peer-memory expert-parallel scheme: this rank's own allocations and every other
+// rank's, mapped through CUDA IPC.
+struct PeerTable {
+  int T_cap = 0;
+  void* own[3] = {nullptr, nullptr, nullptr};
+  void* xall[EK_EP_MAX_RANKS] = {};
+  void* partial[EK_EP_MAX_RANKS] = {};
+  void* flags[EK_EP_MAX_RANKS] = {};
+  bool opened[EK_EP_MAX_RANKS] = {};
+};
+
 // One worker-level call waiting to be served (lives on its caller's stack).
 struct ExpertReq {
   const char* id = nullptr;
@@ -115,6 +126,8 @@ struct ek_backend {
   std::map<std::string, ExpertRef> experts;   // BTreeMap<String, Arc<ExpertBackend>>
   std::set<std::string> loading;
   mutable std::shared_mutex reg_mu;           // the worker's RwLock around ExpertDB
+  uint32_t* ep_counters = nullptr;            // per-destination CTA counters of the peer push kernel
+  PeerTable peers;                            // expert parallel over peer memory
   std::mutex fwd_mu;                          // forwards share one workspace
   std::mutex pend_mu;                         // queue of worker-level requests waiting for a grouped launch
   std::vector<ExpertReq*> pending;
@@ -630,6 +643,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMalloc(&be->n_chunks, 4));
   CKC(cudaMalloc(&be->status, sizeof(DevStatus)));
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
+  CKC(cudaMalloc(&be->ep_counters, EK_EP_MAX_RANKS * sizeof(uint32_t)));
+  CKC(cudaMemset(be->ep_counters, 0, EK_EP_MAX_RANKS * sizeof(uint32_t)));
   CKC(cudaMalloc(&be->prof, kProfWords * sizeof(long long)));
   CKC(cudaMemset(be->prof, 0, kProfWords * sizeof(long long)));
   CKC(cudaMallocHost(&be->h_status, sizeof(DevStatus)));
@@ -664,12 +679,19 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaSetDevice(be->cfg.device);
   if (be->own_stream) cudaStreamSynchronize(be->own_stream);
   if (be->load_stream) cudaStreamSynchronize(be->load_stream);
+  for (int r = 0; r < EK_EP_MAX_RANKS; ++r)
+    if (be->peers.opened[r]) {
+      cudaIpcCloseMemHandle(be->peers.xall[r]);
+      cudaIpcCloseMemHandle(be->peers.partial[r]);
+      cudaIpcCloseMemHandle(be->peers.flags[r]);
+    }
+  for (int i = 0; i < 3; ++i) cudaFree(be->peers.own[i]);
   for (auto& kv : be->layers) free_layer(kv.second);
   cudaFree(be->x_dev); cudaFree(be->y_dev); cudaFree(be->xp); cudaFree(be->hbuf); cudaFree(be->obuf);
   cudaFree(be->tk_dev);
   cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->partial); cudaFree(be->flag_dev); cudaFree(be->ids); cudaFree(be->counts);
   cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
-  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->prof); cudaFree(be->maps);
+  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->prof); cudaFree(be->ep_counters); cudaFree(be->maps);
   cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_segs); cudaFree(be->segs); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
@@ -1785,6 +1807,165 @@ int32_t ek_ep_finish(ek_backend_t* be, int32_t layer, const float* reduced_dev, 
   std::lock_guard<std::mutex> fg(be->fwd_mu);
   be->launches += launch_combine_finish(reduced_dev, be->obuf + (size_t)be->ep_rows * c.hidden, c.n_shared_experts,
                                         T_local, c.hidden, reinterpret_cast<__nv_bfloat16*>(y_dev), be->stream);
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+// ---- expert parallel over peer memory ------------------------------------------------------------
+namespace {
+int check_peer_step(ek_backend* be, int T) {
+  const ek_config_t& c = be->cfg;
+  PeerTable& pt = be->peers;
+  if (!pt.own[0]) return fail(be, EK_INVALID_INPUT, "ek_ep_peer_alloc has not been called");
+  for (int r = 0; r < c.ep_size; ++r)
+    if (!pt.xall[r]) return fail(be, EK_INVALID_INPUT, "rank %d's buffers have not been opened", r);
+  if (T < 1 || T > pt.T_cap) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d] (the size given to ek_ep_peer_alloc)", T, pt.T_cap);
+  return EK_OK;
+}
+void free_peers(ek_backend* be) {
+  PeerTable& pt = be->peers;
+  for (int r = 0; r < EK_EP_MAX_RANKS; ++r) {
+    if (pt.opened[r]) {
+      cudaIpcCloseMemHandle(pt.xall[r]);
+      cudaIpcCloseMemHandle(pt.partial[r]);
+      cudaIpcCloseMemHandle(pt.flags[r]);
+    }
+    pt.opened[r] = false;
+    pt.xall[r] = pt.partial[r] = pt.flags[r] = nullptr;
+  }
+}
+}  // namespace
+
+int32_t ek_ep_peer_alloc(ek_backend_t* be, int32_t tokens_per_rank, uint8_t* handles) {
+  if (!be || !handles) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  static_assert(sizeof(cudaIpcMemHandle_t) == EK_IPC_HANDLE_BYTES, "IPC handle size");
+  if (c.ep_size > EK_EP_MAX_RANKS) return fail(be, EK_UNSUPPORTED, "at most %d ranks", EK_EP_MAX_RANKS);
+  if (tokens_per_rank < 1 || (int64_t)tokens_per_rank * c.ep_size > c.max_tokens)
+    return fail(be, EK_INVALID_INPUT, "%d tokens per rank x %d ranks exceed max_tokens %d", tokens_per_rank, c.ep_size, c.max_tokens);
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  PeerTable& pt = be->peers;
+  if (pt.own[0]) return fail(be, EK_INVALID_INPUT, "peer buffers exist already: destroy the backend to resize them");
+  const size_t Ta = (size_t)tokens_per_rank * c.ep_size;
+  const size_t bytes[3] = {2 * Ta * c.hidden * 2, 2 * Ta * c.hidden * 4, 2 * EK_EP_MAX_RANKS * 4};
+  for (int i = 0; i < 3; ++i) {
+    CK(cudaMalloc(&pt.own[i], bytes[i]));
+    CK(cudaMemset(pt.own[i], 0, bytes[i]));
+    cudaIpcMemHandle_t h;
+    CK(cudaIpcGetMemHandle(&h, pt.own[i]));
+    memcpy(handles + (size_t)i * EK_IPC_HANDLE_BYTES, &h, sizeof h);
+  }
+  CK(cudaDeviceSynchronize());
+  pt.T_cap = tokens_per_rank;
+  pt.xall[c.ep_rank] = pt.own[0];
+  pt.partial[c.ep_rank] = pt.own[1];
+  pt.flags[c.ep_rank] = pt.own[2];
+  return EK_OK;
+}
+
+int32_t ek_ep_peer_open(ek_backend_t* be, int32_t rank, const uint8_t* handles) {
+  if (!be || !handles) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (rank < 0 || rank >= c.ep_size || rank >= EK_EP_MAX_RANKS) return fail(be, EK_INVALID_INPUT, "rank %d outside the group", rank);
+  if (rank == c.ep_rank) return EK_OK;   // the own buffers need no mapping
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  PeerTable& pt = be->peers;
+  if (pt.opened[rank]) return fail(be, EK_INVALID_INPUT, "rank %d's buffers are open already", rank);
+  void* ptrs[3] = {nullptr, nullptr, nullptr};
+  for (int i = 0; i < 3; ++i) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + (size_t)i * EK_IPC_HANDLE_BYTES, sizeof h);
+    // opened with THIS device current: the runtime enables peer access to the owner's device
+    const cudaError_t e = cudaIpcOpenMemHandle(&ptrs[i], h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      for (int j = 0; j < i; ++j) cudaIpcCloseMemHandle(ptrs[j]);
+      return fail(be, EK_CUDA, "cudaIpcOpenMemHandle for rank %d: %s", rank, cudaGetErrorString(e));
+    }
+  }
+  pt.xall[rank] = ptrs[0];
+  pt.partial[rank] = ptrs[1];
+  pt.flags[rank] = ptrs[2];
+  pt.opened[rank] = true;
+  return EK_OK;
+}
+
+int32_t ek_ep_peer_close(ek_backend_t* be) {
+  if (!be) return EK_INVALID_INPUT;
+  cudaSetDevice(be->cfg.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  cudaStreamSynchronize(be->stream);
+  free_peers(be);
+  return EK_OK;
+}
+
+int32_t ek_ep_peer_push(ek_backend_t* be, const void* x_dev, int32_t T, uint32_t step) {
+  if (!be || !x_dev) return EK_INVALID_INPUT;
+  int rc = check_peer_step(be, T);
+  if (rc != EK_OK) return rc;
+  const ek_config_t& c = be->cfg;
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  PeerTable& pt = be->peers;
+  const int H = c.hidden;
+  const size_t Ta = (size_t)T * c.ep_size;
+  const size_t off = (size_t)(step & 1u) * Ta * H + (size_t)c.ep_rank * T * H;   // elements into a rank's xall
+  be->launches += launch_ep_push(reinterpret_cast<const __nv_bfloat16*>(x_dev), T, H, pt.xall, pt.flags, c.ep_size, c.ep_rank,
+                                 step + 1, off, be->ep_counters, be->stream);
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_ep_peer_partial(ek_backend_t* be, int32_t layer, int32_t T, uint32_t step) {
+  if (!be) return EK_INVALID_INPUT;
+  int rc = check_peer_step(be, T);
+  if (rc != EK_OK) return rc;
+  const ek_config_t& c = be->cfg;
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end() || !li->second.router_w)
+    return fail(be, EK_NOT_FOUND, "layer %d has no router weight registered", layer);
+  PeerTable& pt = be->peers;
+  const int H = c.hidden;
+  const size_t Ta = (size_t)T * c.ep_size;
+  const size_t par = (size_t)(step & 1u) * Ta * H;
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(pt.flags[c.ep_rank]);
+  be->launches += launch_ep_wait(my_flags, c.ep_size, step + 1, be->status, 500, be->stream);
+  LayerOpts opt;
+  opt.sh_t0 = c.ep_rank * T;
+  opt.sh_T = T;
+  opt.partial = reinterpret_cast<float*>(pt.partial[c.ep_rank]) + par;
+  be->ep_rows = (int)Ta * c.top_k;
+  be->ep_T = T;
+  rc = run_layer(be, li->second, reinterpret_cast<const __nv_bfloat16*>(pt.xall[c.ep_rank]) + par, (int)Ta, c.top_k, nullptr,
+                 nullptr, nullptr, opt);
+  if (rc != EK_OK) return rc;
+  be->launches += launch_ep_signal(pt.flags, c.ep_size, EK_EP_MAX_RANKS + c.ep_rank, step + 1, be->stream);
+  CK(cudaGetLastError());
+  return EK_OK;
+}
+
+int32_t ek_ep_peer_finish(ek_backend_t* be, int32_t layer, int32_t T, uint32_t step, void* y_dev) {
+  (void)layer;
+  if (!be || !y_dev) return EK_INVALID_INPUT;
+  int rc = check_peer_step(be, T);
+  if (rc != EK_OK) return rc;
+  const ek_config_t& c = be->cfg;
+  const int H = c.hidden;
+  if (c.n_shared_experts > 0 && be->ep_T != T) return fail(be, EK_INVALID_INPUT, "ek_ep_peer_partial must run on the same step first");
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  PeerTable& pt = be->peers;
+  const size_t Ta = (size_t)T * c.ep_size;
+  const size_t off = (size_t)(step & 1u) * Ta * H + (size_t)c.ep_rank * T * H;   // this rank's token slice in every partial
+  const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(pt.flags[c.ep_rank]) + EK_EP_MAX_RANKS;
+  be->launches += launch_ep_pull_finish(pt.partial, off, c.ep_size, my_flags, step + 1,
+                                        be->obuf + (size_t)be->ep_rows * c.hidden, c.n_shared_experts, T, H,
+                                        reinterpret_cast<__nv_bfloat16*>(y_dev), be->status, be->stream);
   CK(cudaGetLastError());
   return EK_OK;
 }

@@ -222,6 +222,13 @@ int launch_unpermute(const __nv_bfloat16* obuf, const int32_t* inv, __nv_bfloat1
 struct RowSegment {
   int32_t src, dst, n, pad;
 };
+int launch_ep_push(const __nv_bfloat16* x, int32_t T, int32_t H, void* const* xall, void* const* flags, int32_t world,
+                   int32_t rank, uint32_t step_no, size_t dst_elem_off, uint32_t* counters, cudaStream_t s);
+int launch_ep_wait(const uint32_t* flags, int32_t world, uint32_t step_no, DevStatus* st, int32_t where, cudaStream_t s);
+int launch_ep_signal(void* const* flags, int32_t world, int32_t slot, uint32_t step_no, cudaStream_t s);
+int launch_ep_pull_finish(void* const* partial, size_t src_elem_off, int32_t world, const uint32_t* my_flags,
+                          uint32_t step_no, const __nv_bfloat16* shared, int32_t n_shared, int32_t T, int32_t H,
+                          __nv_bfloat16* y, DevStatus* st, cudaStream_t s);
 int launch_segment_copy(const __nv_bfloat16* src, __nv_bfloat16* dst, const RowSegment* segs, int32_t n_segs,
                         int32_t max_rows_per_seg, int32_t H, cudaStream_t s);
 

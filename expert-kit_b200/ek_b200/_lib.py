@@ -20,6 +20,10 @@ EK_BF16, EK_F32, EK_F8_E4M3, EK_I8, EK_I32, EK_F16, EK_U8, EK_I64 = range(8)
 EK_SCORE_SOFTMAX, EK_SCORE_SIGMOID = 0, 1
 EK_QUANT_BF16, EK_QUANT_FP8_BLOCK128, EK_QUANT_INT8_BLOCK128 = 0, 1, 2
 EK_TILE_LAYOUT_VERSION = 3   # include/ek_b200.h
+EK_EP_MAX_RANKS = 16
+
+
+EK_IPC_HANDLE_BYTES = 64
 EK_STAGE_COUNT = 5
 STAGE_NAMES = ("route", "permute", "gateup", "down", "combine")
 
@@ -72,6 +76,12 @@ SIGNATURES = {
     "ek_stage_timing_enable": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ek_stage_times": (C.c_int32, [C.c_void_p, C.POINTER(C.c_float)]),
     "ek_kernel_launches": (C.c_int64, [C.c_void_p]),
+    "ek_ep_peer_alloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "ek_ep_peer_open": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "ek_ep_peer_close": (C.c_int32, [C.c_void_p]),
+    "ek_ep_peer_push": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32]),
+    "ek_ep_peer_partial": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_uint32]),
+    "ek_ep_peer_finish": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]),
     "ek_expert_export_tiles": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "ek_expert_register_tiles": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]),
     "ek_worker_batch_stats": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),

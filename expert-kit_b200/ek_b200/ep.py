@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import List, Optional, Tuple
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
@@ -59,6 +61,46 @@ class BackendStages:
     def finish(self, layer: int, reduced: torch.Tensor, y: torch.Tensor):
         self.be.ep_finish(layer, reduced, y)
 
+    # --- the same scheme over peer memory (no collectives) ---
+    def peer_setup(self, group, tokens_per_rank: int):
+        return PeerWorkspace(self.be, group, tokens_per_rank)
+
+    def peer_step(self, layer: int, x: torch.Tensor, y: torch.Tensor, step: int):
+        lib, h, T = self.be._lib, self.be._h, x.shape[0]
+        self.be._check(lib.ek_ep_peer_push(h, x.data_ptr(), T, step))
+        self.be._check(lib.ek_ep_peer_partial(h, layer, T, step))
+        self.be._check(lib.ek_ep_peer_finish(h, layer, T, step, y.data_ptr()))
+
+
+class PeerWorkspace:
+    """The backend's peer buffers (gathered tokens, fp32 partial sums, flag words): allocated by the
+    library, their CUDA IPC handles exchanged over the process group, every peer's opened."""
+
+    def __init__(self, backend, group, tokens_per_rank: int):
+        from . import _lib as L
+        self.be, self.group = backend, group
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        self.tokens_per_rank = tokens_per_rank
+        mine = (C.c_uint8 * (3 * L.EK_IPC_HANDLE_BYTES))()
+        backend._check(backend._lib.ek_ep_peer_alloc(backend._h, tokens_per_rank, mine))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, bytes(mine), group=group)
+        for r in range(world):
+            if r != rank:
+                buf = (C.c_uint8 * (3 * L.EK_IPC_HANDLE_BYTES)).from_buffer_copy(everyone[r])
+                backend._check(backend._lib.ek_ep_peer_open(backend._h, r, buf))
+        self.open = True
+        dist.barrier(group=group)     # nobody steps before every rank has mapped everything
+
+    def close(self):
+        """Unmaps the peers' buffers, then synchronises the ranks: a rank may only destroy its
+        backend (and free its own buffers) once nobody has them mapped."""
+        if not self.open:
+            return
+        self.open = False
+        self.be._check(self.be._lib.ek_ep_peer_close(self.be._h))
+        dist.barrier(group=self.group)
+
 
 class ExpertParallelMoE:
     """y = shared(x) + sum_k w_k expert_k(x) with the experts sharded over `group`.
@@ -69,11 +111,15 @@ class ExpertParallelMoE:
               the tokens, every rank runs its experts on the rows routed to them, reduce-scatter the
               fp32 partial sums.  Two collectives of fixed size, no host synchronisation.
     "a2a"     rows travel only to the ranks that own their experts (two all-to-alls whose split
-              sizes come from the all-gathered per-expert counts: one host synchronisation)."""
+              sizes come from the all-gathered per-expert counts: one host synchronisation).
+    "peer"    the gather scheme without collectives: this library's kernels store the tokens into
+              every rank's memory and load the partial sums from every rank's memory (CUDA IPC
+              mappings), synchronised by flag words; GPU only."""
 
     def __init__(self, stages, group: Optional[dist.ProcessGroup] = None, max_recv_rows: Optional[int] = None,
-                 mode: str = "auto", gather_max_tokens: int = 2048):
+                 mode: str = "auto", gather_max_tokens: int = 2048, peer_tokens: Optional[int] = None):
         self.mode = mode
+        self.peer_tokens = peer_tokens      # per-rank capacity of the peer buffers (default: the first batch)
         self.gather_max_tokens = gather_max_tokens
         self.stages = stages
         self.group = group
@@ -98,7 +144,32 @@ class ExpertParallelMoE:
             mode = "gather" if equal_batches and x.shape[0] * self.world <= self.gather_max_tokens else "a2a"
         if mode == "gather":
             return self._forward_gather(layer, x)
+        if mode == "peer":
+            return self._forward_peer(layer, x)
         return self._forward_a2a(layer, x)
+
+    def close(self):
+        """Releases the peer-memory workspace (collective: every rank calls it)."""
+        ws = self._bufs.pop("peer_ws", None)
+        if ws is not None:
+            ws.close()
+
+    def _forward_peer(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        """The gather scheme with the library's own kernels over NVLink: tokens are stored into every
+        rank's buffer, the partial sums are loaded from every rank by the finishing kernel.  Equal
+        batches, at most the size the workspace was made for; every rank must call in lockstep."""
+        T = x.shape[0]
+        ws = self._bufs.get("peer_ws")
+        if ws is None:
+            ws = self.stages.peer_setup(self.group, self.peer_tokens or T)
+            self._bufs["peer_ws"] = ws
+            self._peer_step = 0
+        if T > ws.tokens_per_rank:
+            raise ValueError(f"{T} tokens per rank, the peer buffers were made for {ws.tokens_per_rank}")
+        y = torch.empty_like(x)
+        self.stages.peer_step(layer, x, y, self._peer_step)
+        self._peer_step += 1
+        return y
 
     def _forward_gather(self, layer: int, x: torch.Tensor) -> torch.Tensor:
         st = self.stages

@@ -215,6 +215,35 @@ int32_t ek_w8a16_activate(ek_backend_t* be, const void* w, int32_t w_dtype, cons
 int32_t ek_worker_forward_wire(ek_backend_t* be, const char* expert_id, const void* req_tensor,
                                size_t req_len, void* resp, size_t resp_cap, size_t* resp_len);
 
+/* ---- expert parallel over peer memory ----------------------------------------------------
+ * The gather scheme with this library's own kernels over NVLink instead of an all-gather and a
+ * reduce-scatter.  One process per GPU.  Each rank allocates three buffers
+ *   xall     gathered tokens   [2][world*T][H] bf16   (written by every rank)
+ *   partial  partial sums      [2][world*T][H] fp32   (written by the owner, read by all)
+ *   flags    flag words        [2*EK_EP_MAX_RANKS] u32
+ * with ek_ep_peer_alloc, which returns their CUDA IPC handles; the host exchanges the handles (any
+ * transport) and every rank opens every other rank's with ek_ep_peer_open.  `step` counts the layer
+ * passes of the group (the same value on every rank, increasing by one from 0 after alloc); buffers
+ * are used alternately by step parity.  push / partial / finish are asynchronous on the backend's
+ * stream and must be called by every rank in the same order.  Device-side waits for a peer are
+ * bounded: a rank that never arrives surfaces as EK_TIMEOUT at the next ek_sync, the context stays
+ * usable.  ek_ep_peer_close unmaps the peers' buffers; call it on every rank, then synchronise the
+ * ranks, before a rank destroys its backend (which frees its own buffers).  No reference
+ * counterpart: the reference moves rows by gRPC (ek-computation/src/controller/executor.rs:141-226). */
+#define EK_EP_MAX_RANKS 16
+#define EK_IPC_HANDLE_BYTES 64
+int32_t ek_ep_peer_alloc(ek_backend_t* be, int32_t tokens_per_rank, uint8_t* handles /* out [3*EK_IPC_HANDLE_BYTES] */);
+int32_t ek_ep_peer_open(ek_backend_t* be, int32_t rank, const uint8_t* handles /* that rank's [3*EK_IPC_HANDLE_BYTES] */);
+int32_t ek_ep_peer_close(ek_backend_t* be);
+/* Stores this rank's tokens x[T,H] into every rank's xall and publishes the step there. */
+int32_t ek_ep_peer_push(ek_backend_t* be, const void* x_dev, int32_t T, uint32_t step);
+/* Waits for every rank's tokens, then routes the gathered batch, runs this rank's experts and leaves
+ * the fp32 partial sums in this rank's `partial`; publishes the step to every rank. */
+int32_t ek_ep_peer_partial(ek_backend_t* be, int32_t layer, int32_t T, uint32_t step);
+/* Waits for every rank's partial sums, loads this rank's token slice from all of them, adds in rank
+ * order, adds the shared expert, rounds: y[T,H] bf16. */
+int32_t ek_ep_peer_finish(ek_backend_t* be, int32_t layer, int32_t T, uint32_t step, void* y_dev);
+
 /* ---- observability -------------------------------------------------------------------- */
 
 /* Rows per expert seen by the last fused/controller-level call on `layer`: the quantity the

@@ -98,7 +98,7 @@ def main():
     layer = OC.make_layer(cfg, 777)
     x = OC.make_inputs(cfg, T_global, 778)
     ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
-    if scheme == "gather":        # equal batches
+    if scheme in ("gather", "peer"):        # equal batches
         T_global -= T_global % world
         x = x[:T_global]
         ref = {"y": ref["y"][:T_global]}
@@ -129,7 +129,7 @@ def main():
         stages = ek_b200.BackendStages(be)
         xl = x[lo:hi].contiguous().cuda()
     moe = ExpertParallelMoE(stages, mode=scheme)
-    for _ in range(2):                      # twice: buffers and staging areas are reused
+    for _ in range(3):                      # several times: buffers, staging areas and step parities are reused
         y = moe.forward(0, xl)
     if be is not None:
         be.sync()
@@ -146,6 +146,7 @@ def main():
     print(f"rank {rank}/{world} tokens {hi - lo} max-rel {max_rel:.3e} mean-abs {d.mean().item():.3e} {'OK' if ok else 'FAIL'}",
           flush=True)
     if be is not None:
+        moe.close()
         be.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -42,11 +42,13 @@ def test_expert_parallel_over_gloo_matches_single_process_oracle(world, scheme):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("scheme", ["a2a", "gather"])
+@pytest.mark.parametrize("scheme", ["a2a", "gather", "peer"])
 def test_expert_parallel_over_nccl_matches_oracle(scheme):
+    """"peer": dispatch and combine by the library's own kernels over peer memory (NCCL only sets
+    the process group up and exchanges the IPC handles)."""
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
-    r = _launch(2, "gpu", 29650 + (1 if scheme == "gather" else 0), scheme)
+    r = _launch(2, "gpu", 29650 + {"a2a": 0, "gather": 1, "peer": 2}[scheme], scheme)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == 2
