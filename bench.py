@@ -282,8 +282,10 @@ def workload_config(T: int, n_gpus: int, n_exp: int = E):
             "tokens_per_gpu": T // n_gpus,
             "parallelism": "single GPU" if n_gpus == 1 else
             f"ep{n_gpus}: {n_exp // n_gpus} routed experts per GPU, shared expert and router replicated, "
-            "NCCL over NVLink (all-gather + reduce-scatter of fp32 partial sums for decode-sized batches, "
-            "all-to-all dispatch/combine above 2048 tokens), global batch fixed (strong scaling)",
+            "decode-sized batches: tokens stored into every rank's memory and fp32 partial sums loaded from every "
+            "rank's memory by the library's own kernels over NVLink (CUDA IPC mappings; NCCL all-gather + "
+            "reduce-scatter if the mappings cannot be made), NCCL all-to-all dispatch/combine above 2048 tokens; "
+            "global batch fixed (strong scaling)",
             "l2": "weights streamed per step (11.3 GB) exceed the 126 MB L2; no flush needed"}
 
 

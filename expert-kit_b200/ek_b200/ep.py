@@ -81,14 +81,33 @@ class PeerWorkspace:
         self.be, self.group = backend, group
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         self.tokens_per_rank = tokens_per_rank
+        self.open = False
+
+        def agree(ok: bool, what: str):
+            """Every rank learns whether all ranks got through the last phase; raises on all if not."""
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if not bool(flag.item()):
+                backend._lib.ek_ep_peer_close(backend._h)
+                raise RuntimeError(f"peer-memory workspace: {what} failed on at least one rank")
+
         mine = (C.c_uint8 * (3 * L.EK_IPC_HANDLE_BYTES))()
-        backend._check(backend._lib.ek_ep_peer_alloc(backend._h, tokens_per_rank, mine))
+        err = None
+        try:
+            backend._check(backend._lib.ek_ep_peer_alloc(backend._h, tokens_per_rank, mine))
+        except Exception as ex:   # noqa: BLE001
+            err = ex
+        agree(err is None, f"allocation ({err})")
         everyone = [None] * world
         dist.all_gather_object(everyone, bytes(mine), group=group)
-        for r in range(world):
-            if r != rank:
-                buf = (C.c_uint8 * (3 * L.EK_IPC_HANDLE_BYTES)).from_buffer_copy(everyone[r])
-                backend._check(backend._lib.ek_ep_peer_open(backend._h, r, buf))
+        try:
+            for r in range(world):
+                if r != rank:
+                    buf = (C.c_uint8 * (3 * L.EK_IPC_HANDLE_BYTES)).from_buffer_copy(everyone[r])
+                    backend._check(backend._lib.ek_ep_peer_open(backend._h, r, buf))
+        except Exception as ex:   # noqa: BLE001
+            err = ex
+        agree(err is None, f"mapping the peers' buffers ({err})")
         self.open = True
         dist.barrier(group=group)     # nobody steps before every rank has mapped everything
 
@@ -128,6 +147,7 @@ class ExpertParallelMoE:
         self.max_recv_rows = max_recv_rows
         self._bufs = {}
         self.last_counts_all = None
+        self._peer_ok = None                # auto mode: None = not tried yet
 
     def _buf(self, name: str, rows: int, like: torch.Tensor) -> torch.Tensor:
         b = self._bufs.get(name)
@@ -141,12 +161,39 @@ class ExpertParallelMoE:
         the "gather" scheme; with "auto" unequal batches use the all-to-all scheme)."""
         mode = self.mode
         if mode == "auto":
-            mode = "gather" if equal_batches and x.shape[0] * self.world <= self.gather_max_tokens else "a2a"
+            small = equal_batches and x.shape[0] * self.world <= self.gather_max_tokens
+            if small and x.is_cuda and hasattr(self.stages, "peer_setup") and self._peer_ok is not False:
+                mode = "peer" if self._try_peer(x.shape[0]) else "gather"
+            else:
+                mode = "gather" if small else "a2a"
         if mode == "gather":
             return self._forward_gather(layer, x)
         if mode == "peer":
             return self._forward_peer(layer, x)
         return self._forward_a2a(layer, x)
+
+    def _try_peer(self, T: int) -> bool:
+        """Sets the peer buffers up once; every rank learns whether ALL ranks succeeded, so the
+        group takes the same scheme."""
+        if self._peer_ok is None:
+            ok = 1
+            try:
+                self._bufs["peer_ws"] = self.stages.peer_setup(self.group, max(self.peer_tokens or 0, T))
+                self._peer_step = 0
+            except Exception as ex:   # noqa: BLE001
+                import sys
+                print(f"[ek_b200] peer-memory exchange unavailable on rank {self.rank}: {ex}; using the collective scheme",
+                      file=sys.stderr)
+                ok = 0
+            flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            self._peer_ok = bool(flag.item())
+            if not self._peer_ok:
+                ws = self._bufs.pop("peer_ws", None)
+                if ws is not None:
+                    ws.close()
+        ws = self._bufs.get("peer_ws")
+        return self._peer_ok and ws is not None and T <= ws.tokens_per_rank
 
     def close(self):
         """Releases the peer-memory workspace (collective: every rank calls it)."""
