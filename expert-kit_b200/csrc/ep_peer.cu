@@ -18,7 +18,7 @@ namespace ek {
 namespace {
 
 constexpr int kMaxRanks = EK_EP_MAX_RANKS;
-constexpr uint32_t kPollLimit = 1u << 21;   // x ~100 ns back-off: a fraction of a second
+constexpr uint32_t kPollLimit = 1u << 20;   // polls with a ~100 ns back-off: about a second
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;

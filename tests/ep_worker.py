@@ -98,6 +98,9 @@ def main():
     layer = OC.make_layer(cfg, 777)
     x = OC.make_inputs(cfg, T_global, 778)
     ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
+    timeout_case = scheme == "peer_timeout"
+    if timeout_case:
+        scheme = "peer"
     if scheme in ("gather", "peer"):        # equal batches
         T_global -= T_global % world
         x = x[:T_global]
@@ -133,6 +136,30 @@ def main():
         y = moe.forward(0, xl)
     if be is not None:
         be.sync()
+    if timeout_case:
+        # Failure detection without a fault: rank 1 sits the next pass out (it leaves between passes,
+        # nothing of its own in flight); rank 0's device-side waits for rank 1's step number run out and
+        # the host reads EK_TIMEOUT at the next synchronisation.  The context stays usable.
+        import ek_b200
+        seen = None
+        if rank == 0:
+            moe.forward(0, xl)
+            try:
+                be.sync()
+            except ek_b200.EKError as ex:
+                seen = ex.status
+            y0 = be.expert_forward(be.expert_id(0, 0), xl[:4])          # a local call still works
+            usable = bool(torch.isfinite(y0.float()).all())
+            ok = seen == 17 and usable
+        else:
+            ok = True
+        dist.barrier()
+        print(f"rank {rank}/{world} timeout case: status {seen} {'OK' if ok else 'FAIL'}", flush=True)
+        moe.close()
+        be.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if ok else 1)
     y = y.cpu()
     if scheme == "a2a":
         # plan consistency: what I send to d equals what d expects from me

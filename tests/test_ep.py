@@ -52,3 +52,18 @@ def test_expert_parallel_over_nccl_matches_oracle(scheme):
     r = _launch(2, "gpu", 29650 + {"a2a": 0, "gather": 1, "peer": 2}[scheme], scheme)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == 2
+
+
+@pytest.mark.gpu
+def test_peer_scheme_reports_a_missing_rank_as_timeout():
+    """A rank that does not show up for a pass: the other rank's bounded device-side waits run out,
+    the host reads EK_TIMEOUT and the backend keeps working.  No fault, no hang: the missing rank
+    left between passes."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29655", os.path.join(ROOT, "tests", "ep_worker.py"), "gpu", "peer_timeout"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == 2 and "status 17" in r.stdout
