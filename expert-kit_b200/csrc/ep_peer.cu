@@ -47,6 +47,8 @@ struct PeerPtrs {
 __global__ void __launch_bounds__(256) ep_push_kernel(const __nv_bfloat16* __restrict__ x, int32_t T, int32_t H,
                                                       PeerPtrs xall, PeerPtrs flags, int32_t rank, uint32_t step_no,
                                                       size_t dst_elem_off, uint32_t* __restrict__ counters) {
+  pdl_wait();
+  pdl_trigger();
   const int dst = blockIdx.x, slices = gridDim.y;
   const int per = (T + slices - 1) / slices;
   const int r_lo = blockIdx.y * per, r_hi = min(T, r_lo + per);
@@ -72,6 +74,8 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const __nv_bfloat16* __res
 // One warp: lane r waits for rank r's step number in this rank's own flag words.
 __global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int32_t world, uint32_t step_no, DevStatus* st,
                                int32_t where) {
+  pdl_wait();
+  pdl_trigger();
   const int r = threadIdx.x;
   if (r < world && !wait_flag(flags + r, step_no)) {
     if (atomicCAS(&st->code, DEV_OK, DEV_TIMEOUT) == DEV_OK) {
@@ -85,6 +89,8 @@ __global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int32_t world
 // Tells every rank that this rank's partial sums of the step are complete (they were written by the
 // kernels before this one on the stream).
 __global__ void ep_signal_kernel(PeerPtrs flags, int32_t world, int32_t slot, uint32_t step_no) {
+  pdl_wait();
+  pdl_trigger();
   const int r = threadIdx.x;
   if (r < world) {
     __threadfence_system();
@@ -101,6 +107,8 @@ __global__ void __launch_bounds__(256) ep_pull_finish_kernel(PeerPtrs partial, s
                                                              const __nv_bfloat16* __restrict__ shared, int32_t n_shared,
                                                              int32_t T, int32_t H, __nv_bfloat16* __restrict__ y,
                                                              DevStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -184,18 +192,18 @@ int launch_ep_push(const __nv_bfloat16* x, int32_t T, int32_t H, void* const* xa
                    int32_t rank, uint32_t step_no, size_t dst_elem_off, uint32_t* counters, cudaStream_t s) {
   int slices = T < 16 ? T : 16;
   if (slices < 1) slices = 1;
-  ep_push_kernel<<<dim3(world, slices), 256, 0, s>>>(x, T, H, ptrs_of(xall, world), ptrs_of(flags, world), rank, step_no,
-                                                     dst_elem_off, counters);
+  launch_pdl(ep_push_kernel, dim3(world, slices), dim3(256), 0, s, x, T, H, ptrs_of(xall, world), ptrs_of(flags, world), rank,
+             step_no, dst_elem_off, counters);
   return 1;
 }
 
 int launch_ep_wait(const uint32_t* flags, int32_t world, uint32_t step_no, DevStatus* st, int32_t where, cudaStream_t s) {
-  ep_wait_kernel<<<1, 32, 0, s>>>(flags, world, step_no, st, where);
+  launch_pdl(ep_wait_kernel, dim3(1), dim3(32), 0, s, flags, world, step_no, st, where);
   return 1;
 }
 
 int launch_ep_signal(void* const* flags, int32_t world, int32_t slot, uint32_t step_no, cudaStream_t s) {
-  ep_signal_kernel<<<1, 32, 0, s>>>(ptrs_of(flags, world), world, slot, step_no);
+  launch_pdl(ep_signal_kernel, dim3(1), dim3(32), 0, s, ptrs_of(flags, world), world, slot, step_no);
   return 1;
 }
 
@@ -207,8 +215,8 @@ int launch_ep_pull_finish(void* const* partial, size_t src_elem_off, int32_t wor
   const int most = (H / 8 + 255) / 256;
   if (parts > most) parts = most;
   if (parts < 1) parts = 1;
-  ep_pull_finish_kernel<<<dim3(T, parts), 256, 0, s>>>(ptrs_of(partial, world), src_elem_off, world, my_flags, step_no,
-                                                       shared, n_shared, T, H, y, st);
+  launch_pdl(ep_pull_finish_kernel, dim3(T, parts), dim3(256), 0, s, ptrs_of(partial, world), src_elem_off, world, my_flags,
+             step_no, shared, n_shared, T, H, y, st);
   return 1;
 }
 
