@@ -16,8 +16,10 @@
  *     soon as the call returns (the reference aliases them instead:
  *     ek-computation/src/backend/torch/mod.rs:119-130).
  *   - All workspace is sized from `max_tokens` at create time; forward calls allocate nothing.
- *   - A backend may be used from many host threads; forward calls on one backend are
- *     serialised on the backend's stream, registration/eviction may run concurrently.
+ *   - A backend may be used from many host threads; forward calls on one backend share one
+ *     workspace and run one after the other on the backend's stream, except that worker-level
+ *     calls (ek_expert_forward, ek_worker_forward_wire) that arrive together are served as one
+ *     grouped launch; registration/eviction may run concurrently.
  */
 #ifndef EK_B200_H_
 #define EK_B200_H_
