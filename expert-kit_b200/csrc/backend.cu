@@ -80,7 +80,10 @@ struct ek_backend {
   cudaStream_t own_stream = nullptr;
   cudaStream_t load_stream = nullptr;
   cudaEvent_t fwd_done = nullptr;
-  cudaEvent_t ev[EK_STAGE_COUNT + 1] = {};
+  // stage timers: one set of events per layer pass, for up to kTimingRing passes between two reads
+  static constexpr int kTimingRing = 64;
+  cudaEvent_t ev[kTimingRing][EK_STAGE_COUNT + 1] = {};
+  int ev_pass = 0;                     // passes recorded since the last read
   bool timing = false;
   float stage_ms[EK_STAGE_COUNT] = {};
   int ffn_impl = 0;                    // 0 tensor cores, 1 CUDA-core checker
@@ -325,6 +328,18 @@ const ek_tensor_view_t* find_exact(const ek_tensor_view_t* t, int n, const std::
   return nullptr;
 }
 
+// Clears the device and host flags of an expert's slot(s) (a shared expert occupies
+// n_shared_experts virtual slots from its first one).  Forwards already queued keep reading the
+// slot; the flags flip behind them on the forward stream and the call waits for that.  Caller
+// holds reg_mu exclusively, so no forward is being enqueued meanwhile.
+void unregister_slots(ek_backend* be, Layer& L, int slot0) {
+  const int n = slot0 >= be->n_local ? be->cfg.n_shared_experts : 1;
+  static const int32_t zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int v = 0; v < n; ++v) L.host_registered[slot0 + v] = 0;
+  cudaMemcpyAsync(L.registered + slot0, zeros, sizeof(int32_t) * n, cudaMemcpyHostToDevice, be->stream);
+  cudaStreamSynchronize(be->stream);
+}
+
 FfnParams ffn_params(ek_backend* be, const Layer& L) {
   FfnParams p;
   p.d = be->d;
@@ -356,14 +371,28 @@ int pick_nmax(int rows, int n_segments) {
   return avg <= 20 ? 32 : avg <= 48 ? 64 : 128;
 }
 
+// Event i of the current pass; the last one closes the pass.
 void mark(ek_backend* be, int i) {
-  if (be->timing) cudaEventRecord(be->ev[i], be->stream);
+  if (!be->timing) return;
+  cudaEventRecord(be->ev[be->ev_pass % ek_backend::kTimingRing][i], be->stream);
+  if (i == EK_STAGE_COUNT) ++be->ev_pass;
 }
 
+// Mean stage times over the passes recorded since the last read (the newest kTimingRing of them).
 int finish_timing(ek_backend* be) {
-  if (!be->timing) return EK_OK;
-  CK(cudaEventSynchronize(be->ev[EK_STAGE_COUNT]));
-  for (int i = 0; i < EK_STAGE_COUNT; ++i) cudaEventElapsedTime(&be->stage_ms[i], be->ev[i], be->ev[i + 1]);
+  if (!be->timing || be->ev_pass == 0) return EK_OK;
+  const int R = ek_backend::kTimingRing;
+  const int n = std::min(be->ev_pass, R);
+  CK(cudaEventSynchronize(be->ev[(be->ev_pass - 1) % R][EK_STAGE_COUNT]));
+  double sum[EK_STAGE_COUNT] = {};
+  for (int p = be->ev_pass - n; p < be->ev_pass; ++p)
+    for (int i = 0; i < EK_STAGE_COUNT; ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, be->ev[p % R][i], be->ev[p % R][i + 1]);
+      sum[i] += ms;
+    }
+  for (int i = 0; i < EK_STAGE_COUNT; ++i) be->stage_ms[i] = (float)(sum[i] / n);
+  be->ev_pass = 0;
   return EK_OK;
 }
 
@@ -564,6 +593,12 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
     return bad("ep_size must divide n_experts and ep_rank be in [0,ep_size)");
   if (c.n_shared_experts < 0 || c.n_shared_experts > 8) return bad("n_shared_experts must be in [0,8]");
   if (c.max_layers < 1) return bad("max_layers must be positive");
+  // a quantised shared expert is cut into virtual experts at multiples of `intermediate`; the
+  // 128x128 scale blocks only line up with those cuts when intermediate is a multiple of 128
+  if (c.quant != EK_QUANT_BF16 && c.n_shared_experts > 1 && c.intermediate % 128) {
+    g_create_error = "quantised weights with n_shared_experts > 1 need intermediate to be a multiple of 128";
+    return EK_UNSUPPORTED;
+  }
 
   ek_backend* be = new ek_backend();
   be->cfg = c;
@@ -620,7 +655,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaEventCreateWithFlags(&be->fwd_done, cudaEventDisableTiming));
   CKC(cudaEventCreateWithFlags(&be->ep_upload_done, cudaEventDisableTiming));
   CKC(cudaMallocHost(&be->h_ep_count, 64));
-  for (auto& e : be->ev) CKC(cudaEventCreate(&e));
+  for (auto& pass : be->ev)
+    for (auto& e : pass) CKC(cudaEventCreate(&e));
   const size_t T = c.max_tokens, H = c.hidden, E = c.n_experts, K = c.top_k;
   CKC(cudaMalloc(&be->x_dev, T * H * 2));
   CKC(cudaMalloc(&be->y_dev, T * H * 2));
@@ -696,7 +732,8 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
   cudaFree(be->stage_cvt);
-  for (auto& e : be->ev) if (e) cudaEventDestroy(e);
+  for (auto& pass : be->ev)
+    for (auto& e : pass) if (e) cudaEventDestroy(e);
   if (be->fwd_done) cudaEventDestroy(be->fwd_done);
   if (be->ep_upload_done) cudaEventDestroy(be->ep_upload_done);
   cudaFreeHost(be->h_ep_count);
@@ -752,12 +789,7 @@ int32_t ek_expert_evict(ek_backend_t* be, const char* id) {
   auto it = be->experts.find(id);
   if (it == be->experts.end()) return EK_OK;   // ExpertDB::remove ignores unknown ids
   Layer& L = be->layers[it->second.layer];
-  const int slot = it->second.slot;
-  L.host_registered[slot] = 0;
-  // forwards already queued keep reading the slot; the flag flips behind them on the same stream
-  const int32_t zero = 0;
-  cudaMemcpyAsync(L.registered + slot, &zero, sizeof zero, cudaMemcpyHostToDevice, be->stream);
-  cudaStreamSynchronize(be->stream);
+  unregister_slots(be, L, it->second.slot);
   be->experts.erase(it);
   return EK_OK;
 }
@@ -817,6 +849,14 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     std::unique_lock<std::shared_mutex> g(be->reg_mu);
     int rc = ensure_layer(be, layer, &L);
     if (rc != EK_OK) return rc;
+    // replacing a live expert: take it out first, so that a forward enqueued while the new tiles
+    // are being written reports EK_EXPERT_NOT_FOUND instead of reading half old, half new weights
+    // (the reference swaps the Arc in one step, worker/manager.rs insert)
+    auto live = be->experts.find(id);
+    if (live != be->experts.end()) {
+      unregister_slots(be, *L, live->second.slot);
+      be->experts.erase(live);
+    }
   }
   cudaStream_t ls = be->load_stream;
   // the slot may still be read by forwards queued before an eviction
@@ -1040,6 +1080,11 @@ int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* b
     std::unique_lock<std::shared_mutex> g(be->reg_mu);
     rc = ensure_layer(be, layer, &L);
     if (rc != EK_OK) return rc;
+    auto live = be->experts.find(id);   // replacing a live expert: see ek_expert_register
+    if (live != be->experts.end()) {
+      unregister_slots(be, *L, live->second.slot);
+      be->experts.erase(live);
+    }
   }
   cudaStream_t ls = be->load_stream;
   // the slot may still be read by forwards queued before an eviction
@@ -1516,6 +1561,10 @@ int32_t ek_combine(ek_backend_t* be, const void* out, const float* weights, int3
   if (!be || !out || !weights || !y) return EK_INVALID_INPUT;
   const ek_config_t& c = be->cfg;
   if (T < 1 || T > c.max_tokens || k < 1 || k > c.top_k) return fail(be, EK_INVALID_INPUT, "T or k out of range");
+  // `out` and `shared` are staged back to back in the output workspace, which holds rows_cap rows
+  if ((int64_t)T * k + (shared ? T : 0) > be->rows_cap)
+    return fail(be, EK_INVALID_INPUT, "T*k%s = %lld rows exceed the workspace of %d rows: raise max_tokens",
+                shared ? " + T" : "", (long long)T * k + (shared ? T : 0), be->rows_cap);
   cudaSetDevice(c.device);
   std::lock_guard<std::mutex> fg(be->fwd_mu);
   cudaStream_t s = be->stream;
@@ -1984,10 +2033,24 @@ int32_t ek_expert_counts(ek_backend_t* be, int32_t layer, int32_t* counts) {
   return EK_OK;
 }
 
+int32_t ek_last_routing(ek_backend_t* be, int32_t T, int32_t* ids, float* weights) {
+  if (!be || (!ids && !weights)) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  if (T < 1 || T > c.max_tokens) return fail(be, EK_INVALID_INPUT, "T=%d outside [1,%d]", T, c.max_tokens);
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  const size_t n = (size_t)T * c.top_k;
+  if (ids) CK(cudaMemcpyAsync(ids, be->ids, n * 4, cudaMemcpyDefault, be->stream));
+  if (weights) CK(cudaMemcpyAsync(weights, be->weights, n * 4, cudaMemcpyDefault, be->stream));
+  CK(cudaStreamSynchronize(be->stream));
+  return EK_OK;
+}
+
 int32_t ek_stage_timing_enable(ek_backend_t* be, int32_t on) {
   if (!be) return EK_INVALID_INPUT;
   std::lock_guard<std::mutex> fg(be->fwd_mu);
   be->timing = on != 0;
+  be->ev_pass = 0;
   return EK_OK;
 }
 int32_t ek_stage_times(ek_backend_t* be, float* ms) {

@@ -230,8 +230,9 @@ int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_
 // library holds until the process exits.
 //
 // Host code cannot use the array's name as a device address; its address is looked up once per
-// device with cudaGetSymbolAddress while that device is current.  The first call on a device
-// performs this look-up, so make that first call outside any stream capture.
+// device with cudaGetSymbolAddress while that device is current (the first call on a device does
+// it).  Every call reads the device status word back and synchronises the stream before it
+// returns, so no call may be made on a stream that is being captured.
 // All calls share the one array: two calls whose kernels overlap on the same GPU race on it.
 // =============================================================================================
 namespace {

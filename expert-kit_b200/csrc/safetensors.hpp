@@ -173,8 +173,14 @@ inline bool parse_blob(const void* blob, size_t len, std::vector<Entry>& out, st
     if (e.begin > e.end || e.end > avail) { err = "data_offsets out of range for '" + e.name + "'"; return false; }
     int dt = dtype_from_string(e.dtype);
     if (dt < 0) { err = "unsupported dtype '" + e.dtype + "'"; return false; }
+    // element count with refusal of negative dimensions and of products that leave 64 bits
     uint64_t cnt = 1;
-    for (auto d : e.shape) cnt *= (uint64_t)d;
+    bool dims_ok = true;
+    for (auto d : e.shape) {
+      if (d < 0 || (d > 0 && cnt > (UINT64_MAX / 16) / (uint64_t)d)) { dims_ok = false; break; }
+      cnt *= (uint64_t)d;
+    }
+    if (!dims_ok) { err = "shape of '" + e.name + "' is negative or too large"; return false; }
     if (cnt * dtype_size(dt) != e.end - e.begin) { err = "size mismatch for '" + e.name + "'"; return false; }
     e.data = base + e.begin;
   }

@@ -73,6 +73,7 @@ SIGNATURES = {
     "ek_worker_forward_wire": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t,
                                            C.POINTER(C.c_size_t)]),
     "ek_expert_counts": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "ek_last_routing": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "ek_stage_timing_enable": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ek_stage_times": (C.c_int32, [C.c_void_p, C.POINTER(C.c_float)]),
     "ek_kernel_launches": (C.c_int64, [C.c_void_p]),

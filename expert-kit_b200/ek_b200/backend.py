@@ -239,6 +239,15 @@ class Backend:
         """Run on the given CUDA stream handle (0 = the default stream); None = the backend's own."""
         h = C.c_void_p(-1) if cuda_stream is None else C.c_void_p(int(cuda_stream))
         self._check(self._lib.ek_set_stream(self._h, h))
+        self._stream = cuda_stream
+
+    def use_torch_stream(self):
+        """Moves the backend to torch's current stream if it is not there already.  The backend has
+        ONE stream, whoever calls: modules of different layers that share a backend all go through
+        here, so none of them can keep running on a stream another one has left."""
+        s = torch.cuda.current_stream(self.cfg.device).cuda_stream
+        if getattr(self, "_stream", -2) != s:
+            self.set_stream(s)     # synchronises the old stream once, at the switch
 
     # ---- expert-parallel stages (device tensors, asynchronous on the backend stream) -------------
     def ep_route(self, layer: int, x: torch.Tensor, send_rows: torch.Tensor, counts: torch.Tensor):
@@ -316,6 +325,14 @@ class Backend:
         out = torch.empty(self.cfg.n_experts, dtype=torch.int32)
         self._check(self._lib.ek_expert_counts(self._h, layer, _ptr(out)))
         return out
+
+    def last_routing(self, T: int):
+        """(ids [T,k] int32, weights [T,k] fp32) of the last routing pass, on the host."""
+        k = self.cfg.top_k
+        ids = torch.empty(T, k, dtype=torch.int32)
+        w = torch.empty(T, k, dtype=torch.float32)
+        self._check(self._lib.ek_last_routing(self._h, T, _ptr(ids), _ptr(w)))
+        return ids, w
 
     def stage_timing(self, on: bool):
         self._check(self._lib.ek_stage_timing_enable(self._h, int(on)))

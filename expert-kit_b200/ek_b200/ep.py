@@ -148,6 +148,7 @@ class ExpertParallelMoE:
         self._bufs = {}
         self.last_counts_all = None
         self._peer_ok = None                # auto mode: None = not tried yet
+        self.last_mode = None               # scheme the last forward used
 
     def _buf(self, name: str, rows: int, like: torch.Tensor) -> torch.Tensor:
         b = self._bufs.get(name)
@@ -166,6 +167,7 @@ class ExpertParallelMoE:
                 mode = "peer" if self._try_peer(x.shape[0]) else "gather"
             else:
                 mode = "gather" if small else "a2a"
+        self.last_mode = mode
         if mode == "gather":
             return self._forward_gather(layer, x)
         if mode == "peer":

@@ -7,6 +7,8 @@ has the same call shape -- `forward(hidden_states[..., H])` returning the block 
 router logits for the Qwen3 form) -- but router, bucketing, expert FFNs, weighted combine and the
 shared expert run as the fused device-resident call, on torch's current stream, with no host
 synchronisation: it can sit inside a decoder layer exactly where the intercepted block sits.
+Because nothing synchronises, device-side errors surface only through `check()`: call it once per
+model forward.
 """
 from __future__ import annotations
 
@@ -27,20 +29,22 @@ class B200MoEBlock(torch.nn.Module):
         self.backend = backend
         self.layer_idx = layer_idx
         self.return_router_logits = return_router_logits
-        self._stream: Optional[int] = None
 
-    def _use_current_stream(self):
-        s = torch.cuda.current_stream().cuda_stream
-        if s != self._stream:
-            self.backend.set_stream(s)     # synchronises the old stream once, at the switch
-            self._stream = s
+    def check(self):
+        """Synchronises the backend's stream and raises `EKError` if any pass since the last check
+        recorded a device-side error (an unregistered expert selected by routing, a failed index
+        check, a bounded wait that ran out).  The DeepSeek-V3 form of `forward` is asynchronous and
+        cannot report such an error itself; the device status word is sticky and every later pass
+        on the backend skips its expert GEMMs until it has been read.  Call this once per model
+        forward (after the last decoder layer), not per block."""
+        self.backend.sync()
 
     def forward(self, hidden_states: torch.Tensor):
         if not hidden_states.is_cuda:
             raise RuntimeError("B200MoEBlock runs on CUDA tensors only")
         shape = hidden_states.shape
         x = hidden_states.reshape(-1, shape[-1]).to(torch.bfloat16).contiguous()
-        self._use_current_stream()
+        self.backend.use_torch_stream()
         if self.return_router_logits:
             y, art = self.backend.moe_forward_fused(self.layer_idx, x, debug=True)
             return y.view(shape).to(hidden_states.dtype), art["logits"].to(x.device)

@@ -252,10 +252,18 @@ int32_t ek_ep_peer_finish(ek_backend_t* be, int32_t layer, int32_t T, uint32_t s
  * worker exports as `worker_expert_activation` (ek-computation/src/metrics.rs:22-71). */
 int32_t ek_expert_counts(ek_backend_t* be, int32_t layer, int32_t* counts /* [n_experts] */);
 
+/* Expert ids [T,k] and routing weights [T,k] that the last routing pass of this backend produced
+ * (fused, expert-parallel partial or route stage), for checks against the frontend's own routing
+ * (expertkit_torch/models/qwen3_moe.py:161-169; deepseek_v3/model.py:142).  Either pointer may be
+ * NULL; host or device.  Synchronises the backend's stream. */
+int32_t ek_last_routing(ek_backend_t* be, int32_t T, int32_t* ids, float* weights);
+
 enum { EK_STAGE_ROUTE = 0, EK_STAGE_PERMUTE = 1, EK_STAGE_GATEUP = 2, EK_STAGE_DOWN = 3,
        EK_STAGE_COMBINE = 4, EK_STAGE_COUNT = 5 };
-/* Device time (ms, CUDA events on the backend's stream) of each stage of the last forward
- * call when stage timing is enabled; the analogue of PerfTimer (ek-base/src/utils.rs:4-45). */
+/* Device time (ms, CUDA events on the backend's stream) of each stage when stage timing is
+ * enabled: the mean over the layer passes issued since the previous ek_sync (the newest 64 of
+ * them), so that a back-to-back run can be profiled without a host synchronisation per pass;
+ * the analogue of PerfTimer (ek-base/src/utils.rs:4-45). */
 int32_t ek_stage_timing_enable(ek_backend_t* be, int32_t on);
 int32_t ek_stage_times(ek_backend_t* be, float* ms /* [EK_STAGE_COUNT] */);
 
@@ -333,10 +341,12 @@ int32_t ek_ep_finish(ek_backend_t* be, int32_t layer, const float* reduced_dev, 
  *   ids_dev[T*k] (device, values in [0,n_experts))  ->  counts_dev[n_experts],
  *   offsets_dev[n_experts+1], perm_dev[T*k]  (device), same definition as ek_route_debug_t.
  *
- * Runs on `cuda_stream` of the CURRENT device and returns after it has completed.  T*k beyond
- * EK_NOALLOC_MAX_ASSIGNMENTS is refused with EK_INVALID_INPUT; `errbuf` (may be NULL) receives a
- * message.  The first call on a device resolves the scratch address: make it before any stream
- * capture.  Calls share the scratch: do not overlap two of them on one GPU. */
+ * Runs on `cuda_stream` of the CURRENT device.  EVERY call ends by copying the device status word
+ * back and synchronising that stream, so it returns only after the kernels have completed and it
+ * must never be issued on a stream that is being captured.  The first call on a device also
+ * resolves the scratch address.  T*k beyond EK_NOALLOC_MAX_ASSIGNMENTS is refused with
+ * EK_INVALID_INPUT; `errbuf` (may be NULL) receives a message.  Calls share the scratch: do not
+ * overlap two of them on one GPU. */
 #define EK_NOALLOC_MAX_ASSIGNMENTS 65536
 int32_t ek_bucket_noalloc(const int32_t* ids_dev, int32_t T, int32_t k, int32_t n_experts,
                           int32_t* counts_dev, int32_t* offsets_dev, int32_t* perm_dev,

@@ -24,6 +24,19 @@ def output_errors(got: torch.Tensor, ref: torch.Tensor):
     return (d.max() / scale).item(), d.mean().item()
 
 
+def record(what: str, **numbers):
+    """One line per parity case with the measured figures (shown by `pytest -rP` / `-s`); appended to
+    the file named by EK_PARITY_REPORT when that is set, so that a GPU run leaves the margins to
+    the tolerances on record."""
+    line = "PARITY " + what + ": " + ", ".join(
+        f"{k}={v:.3e}" if isinstance(v, float) else f"{k}={v}" for k, v in numbers.items())
+    print(line)
+    path = os.environ.get("EK_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(line + "\n")
+
+
 def assert_outputs_close(got, ref, what=""):
     max_rel, mean_abs = output_errors(got, ref)
     assert max_rel <= MAX_REL and mean_abs <= MEAN_ABS, f"{what}: max-rel {max_rel:.3e}, mean-abs {mean_abs:.3e}"

@@ -5,8 +5,8 @@ step, cannot let this library call cudaMalloc.  `ek_bucket_noalloc` is the entry
 callers: no backend handle, no allocator calls, scratch built into the library image.  Here it is
 driven through the C ABI with caller-owned device buffers and must reproduce, bit for bit, the
 counts / offsets / permutation that the regular routing entry point reports for the same
-assignments -- on two calls in a row, since the second call meets the scratch the first one left
-behind.
+assignments -- and that the CPU oracle's stable counting sort gives -- on two calls in a row,
+since the second call meets the scratch the first one left behind.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -15,6 +15,8 @@ import ctypes as C
 
 import pytest
 import torch
+
+from oracle import ek_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -51,6 +53,9 @@ def test_bucket_noalloc_matches_regular_entry_point_twice_in_a_row():
         assert torch.equal(counts, want["counts"])
         assert torch.equal(offsets, want["offsets"])
         assert torch.equal(perm, want["perm"])
+        # and, independently of this library, against the CPU restatement of the reference's bucketing
+        c, o, p = O.bucket(want["ids"], E)
+        assert torch.equal(counts, c) and torch.equal(offsets, o) and torch.equal(perm, p)
     be.close()
 
 
