@@ -28,6 +28,7 @@ struct Layer {
   uint8_t* dn = nullptr;
   float* gu_scale = nullptr;
   float* dn_scale = nullptr;
+  float* pow2 = nullptr;             // [2][n_slots]: gate/up and down activation powers of two (quantised only)
   int32_t* registered = nullptr;     // device flags [n_slots]
   std::vector<char> host_registered;
   void* router_w = nullptr;
@@ -39,6 +40,12 @@ struct Layer {
   float* router_bias = nullptr;
   int32_t* last_counts = nullptr;    // device [E]
   bool have_counts = false;
+  // replicas: slot of every expert this rank holds (own window and replica slots), -1 otherwise
+  int32_t* slot_of = nullptr;        // device [E]
+  std::vector<int32_t> host_slot_of;
+  std::vector<int32_t> replica_expert;   // [replica_slots] expert held by each replica slot, -1 = free
+  int32_t* owners = nullptr;         // device [E]: per-pass owner table (valid while has_owners)
+  bool has_owners = false;
 };
 
 struct ExpertRef {
@@ -104,7 +111,9 @@ struct ek_backend {
   ChunkDesc* chunks = nullptr;
   int32_t* n_chunks = nullptr;
   DevStatus* status = nullptr;
-  long long* prof = nullptr;           // 4 roles x 8 counters (profile builds)
+  float* sk_buf = nullptr;             // partial accumulators of K-split work items
+  uint32_t* sk_flags = nullptr;
+  int split_k = 1;
   DevStatus* h_status = nullptr;       // pinned
   ChunkDesc* h_chunks = nullptr;       // pinned, worker-level call
   int h_chunks_cap = 0;
@@ -277,6 +286,8 @@ int ensure_layer(ek_backend* be, int layer, Layer** out) {
   if (d.quant != EK_QUANT_BF16) {
     CK(cudaMalloc(&L.gu_scale, (size_t)be->n_slots * d.it * d.kt_gu * 2 * sizeof(float)));
     CK(cudaMalloc(&L.dn_scale, (size_t)be->n_slots * d.hp * d.kt_dn * 2 * sizeof(float)));
+    CK(cudaMalloc(&L.pow2, (size_t)be->n_slots * 2 * sizeof(float)));
+    be->launches += launch_fill_f32(L.pow2, 1.f, (int64_t)be->n_slots * 2, be->load_stream);
   }
   // clear on the load stream and wait: the backend's streams are non-blocking, so a memset on the
   // default stream could land after a later flag update
@@ -284,6 +295,13 @@ int ensure_layer(ek_backend* be, int layer, Layer** out) {
   CK(cudaMemsetAsync(L.registered, 0, sizeof(int32_t) * be->n_slots, be->load_stream));
   CK(cudaMalloc(&L.last_counts, sizeof(int32_t) * be->cfg.n_experts));
   CK(cudaMemsetAsync(L.last_counts, 0, sizeof(int32_t) * be->cfg.n_experts, be->load_stream));
+  L.host_slot_of.assign(be->cfg.n_experts, -1);
+  for (int e = be->e_lo; e < be->e_hi; ++e) L.host_slot_of[e] = e - be->e_lo;
+  L.replica_expert.assign(be->cfg.replica_slots, -1);
+  CK(cudaMalloc(&L.slot_of, sizeof(int32_t) * be->cfg.n_experts));
+  CK(cudaMalloc(&L.owners, sizeof(int32_t) * be->cfg.n_experts));
+  CK(cudaMemcpyAsync(L.slot_of, L.host_slot_of.data(), sizeof(int32_t) * be->cfg.n_experts, cudaMemcpyHostToDevice,
+                     be->load_stream));
   CK(cudaStreamSynchronize(be->load_stream));
   L.host_registered.assign(be->n_slots, 0);
   auto ins = be->layers.emplace(layer, L);
@@ -296,11 +314,14 @@ void free_layer(Layer& L) {
   cudaFree(L.dn);
   cudaFree(L.gu_scale);
   cudaFree(L.dn_scale);
+  cudaFree(L.pow2);
   cudaFree(L.registered);
   cudaFree(L.router_w);
   if (L.router_bf16_owned) cudaFree(L.router_bf16);
   cudaFree(L.router_bias);
   cudaFree(L.last_counts);
+  cudaFree(L.slot_of);
+  cudaFree(L.owners);
 }
 
 int grow(ek_backend* be, void** buf, size_t* cap, size_t need) {
@@ -333,10 +354,34 @@ const ek_tensor_view_t* find_exact(const ek_tensor_view_t* t, int n, const std::
 // slot; the flags flip behind them on the forward stream and the call waits for that.  Caller
 // holds reg_mu exclusively, so no forward is being enqueued meanwhile.
 void unregister_slots(ek_backend* be, Layer& L, int slot0) {
-  const int n = slot0 >= be->n_local ? be->cfg.n_shared_experts : 1;
+  const bool shared = slot0 == be->n_local && be->cfg.n_shared_experts > 0;
+  const int n = shared ? be->cfg.n_shared_experts : 1;
   static const int32_t zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   for (int v = 0; v < n; ++v) L.host_registered[slot0 + v] = 0;
   cudaMemcpyAsync(L.registered + slot0, zeros, sizeof(int32_t) * n, cudaMemcpyHostToDevice, be->stream);
+  cudaStreamSynchronize(be->stream);
+}
+
+// Slot of a routed expert on this rank: its place in the window, the replica slot that holds it,
+// or (allocate) a free replica slot.  -1: this rank cannot hold it.  Caller holds reg_mu exclusively
+// when allocating.
+int routed_slot(ek_backend* be, Layer& L, int expert, bool allocate) {
+  if (expert >= be->e_lo && expert < be->e_hi) return expert - be->e_lo;
+  const int base = be->n_local + be->cfg.n_shared_experts;
+  int free_slot = -1;
+  for (int i = 0; i < be->cfg.replica_slots; ++i) {
+    if (L.replica_expert[i] == expert) return base + i;
+    if (L.replica_expert[i] < 0 && free_slot < 0) free_slot = i;
+  }
+  if (!allocate || free_slot < 0) return -1;
+  L.replica_expert[free_slot] = expert;
+  return base + free_slot;
+}
+
+// Publishes (or withdraws, slot = -1) the slot of an expert outside the window on the device.
+void publish_replica(ek_backend* be, Layer& L, int expert, int slot) {
+  L.host_slot_of[expert] = slot;
+  cudaMemcpyAsync(L.slot_of + expert, &L.host_slot_of[expert], sizeof(int32_t), cudaMemcpyHostToDevice, be->stream);
   cudaStreamSynchronize(be->stream);
 }
 
@@ -347,6 +392,8 @@ FfnParams ffn_params(ek_backend* be, const Layer& L) {
   p.w.dn_tiles = L.dn;
   p.w.gu_scale = L.gu_scale;
   p.w.dn_scale = L.dn_scale;
+  p.w.gu_pow = L.pow2;
+  p.w.dn_pow = L.pow2 ? L.pow2 + be->n_slots : nullptr;
   p.w.registered = L.registered;
   p.w.n_slots = be->n_slots;
   p.chunks = be->chunks;
@@ -362,8 +409,17 @@ FfnParams ffn_params(ek_backend* be, const Layer& L) {
   p.h_maps = be->maps + 4;
   p.n_sm = be->n_sm;
   p.precise = be->precise;
-  p.prof = be->prof;
+  p.split_k = be->split_k;
+  p.sk_buf = be->sk_buf;
+  p.sk_flags = be->sk_flags;
   return p;
+}
+
+// Activation type the GEMMs of the next pass expect in the permuted-row buffer: f16 for the
+// quantised tensor-core modes, bf16 for bf16 weights, the reference-formula mode and the CUDA-core
+// checker.
+bool f16_rows(const ek_backend* be) {
+  return be->ffn_impl == 0 && ffn_tc_f16_activations(be->cfg.quant, be->precise);
 }
 
 int pick_nmax(int rows, int n_segments) {
@@ -372,6 +428,18 @@ int pick_nmax(int rows, int n_segments) {
 }
 
 // Event i of the current pass; the last one closes the pass.
+// EK_B200_DEBUG_SYNC=1: synchronise after every stage of a layer pass and name the stage a CUDA
+// error surfaced behind (diagnosis only: it removes all overlap between kernels)
+bool debug_sync_failed(ek_backend* be, const char* what) {
+  static const bool on = getenv("EK_B200_DEBUG_SYNC") && getenv("EK_B200_DEBUG_SYNC")[0] == '1';
+  if (!on) return false;
+  const cudaError_t e = cudaStreamSynchronize(be->stream);
+  if (e == cudaSuccess) return false;
+  fail(be, EK_CUDA, "CUDA error behind stage '%s': %s", what, cudaGetErrorString(e));
+  fprintf(stderr, "[ek_b200] CUDA error behind stage '%s': %s\n", what, cudaGetErrorString(e));
+  return true;
+}
+
 void mark(ek_backend* be, int i) {
   if (!be->timing) return;
   cudaEventRecord(be->ev[be->ev_pass % ek_backend::kTimingRing][i], be->stream);
@@ -397,8 +465,9 @@ int finish_timing(ek_backend* be) {
 }
 
 // Runs gate/up + down over the work list already on the device.
-void run_ffn(ek_backend* be, const Layer& L, int nmax, int which) {
+void run_ffn(ek_backend* be, const Layer& L, int nmax, int which, bool allow_split = true) {
   FfnParams p = ffn_params(be, L);
+  if (!allow_split) p.split_k = 0;
   if (be->ffn_impl == 1) {
     p.chunk_rows = 16;
     be->launches += launch_ffn_simt(p, which, be->stream);
@@ -414,6 +483,8 @@ int check_status(ek_backend* be) {
   const DevStatus st = *be->h_status;
   if (st.code == DEV_OK) return EK_OK;
   cudaMemsetAsync(be->status, 0, sizeof(DevStatus), be->stream);
+  // a pass that gave up may have left split-item flags raised
+  cudaMemsetAsync(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t), be->stream);
   cudaStreamSynchronize(be->stream);
   switch (st.code) {
     case DEV_TIMEOUT:
@@ -484,7 +555,9 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
       }
     }
     if (!tc_done) be->launches += launch_router_logits(rp, s);
+    if (debug_sync_failed(be, "router logits")) return EK_CUDA;
     be->launches += launch_route_select(rp, s, tc_done);
+    if (debug_sync_failed(be, "route select")) return EK_CUDA;
     ids = be->ids;
   } else {
     // caller-supplied ids may be invalid: rows that no expert claims must read as "absent"
@@ -495,25 +568,33 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   PermuteParams pp;
   pp.ids = ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
   pp.T = T; pp.k = k; pp.E = c.n_experts; pp.e_lo = be->e_lo; pp.e_hi = be->e_hi;
+  pp.owners = L.has_owners ? L.owners : nullptr; pp.rank = c.ep_rank;
   be->launches += launch_permute(pp, s);
+  if (debug_sync_failed(be, "permute")) return EK_CUDA;
   // expected rows per local expert: Tk / n_experts whatever the sharding
   const int nmax = pick_nmax((int)((int64_t)Tk * be->n_local / c.n_experts), be->n_local);
   WorklistParams wp;
   wp.counts = be->counts; wp.offsets = be->offsets; wp.registered = L.registered;
   wp.chunks = be->chunks; wp.n_chunks = be->n_chunks;
   wp.E = c.n_experts; wp.e_lo = be->e_lo; wp.e_hi = be->e_hi;
+  wp.owners = pp.owners; wp.slot_of = L.slot_of; wp.rank = c.ep_rank;
   wp.chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
   wp.n_shared = sh_T > 0 ? n_shared : 0; wp.T = sh_T; wp.Tk = Tk;
   wp.max_chunks = be->max_chunks;
   wp.status = be->status;
   wp.counts_copy = L.last_counts;   // the layer's activation metric, read back by ek_expert_counts
   be->launches += launch_worklist(wp, s);
-  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T, s);
+  if (debug_sync_failed(be, "worklist")) return EK_CUDA;
+  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T,
+                                f16_rows(be), s);
+  if (debug_sync_failed(be, "gather")) return EK_CUDA;
   L.have_counts = true;
   mark(be, 2);
   run_ffn(be, L, nmax, 0);
+  if (debug_sync_failed(be, "gate/up GEMM")) return EK_CUDA;
   mark(be, 3);
   run_ffn(be, L, nmax, 1);
+  if (debug_sync_failed(be, "down GEMM")) return EK_CUDA;
   mark(be, 4);
   if (fused && opt.partial) {
     CombineParams cp;
@@ -533,6 +614,7 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
     be->launches += launch_unpermute(be->obuf, be->inv, out_tk, T, k, c.hidden, s);
   }
   mark(be, 5);
+  if (debug_sync_failed(be, "combine")) return EK_CUDA;
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(be, EK_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return EK_OK;
@@ -593,6 +675,7 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
     return bad("ep_size must divide n_experts and ep_rank be in [0,ep_size)");
   if (c.n_shared_experts < 0 || c.n_shared_experts > 8) return bad("n_shared_experts must be in [0,8]");
   if (c.max_layers < 1) return bad("max_layers must be positive");
+  if (c.replica_slots < 0 || c.replica_slots > c.n_experts) return bad("replica_slots must be in [0,n_experts]");
   // a quantised shared expert is cut into virtual experts at multiples of `intermediate`; the
   // 128x128 scale blocks only line up with those cuts when intermediate is a multiple of 128
   if (c.quant != EK_QUANT_BF16 && c.n_shared_experts > 1 && c.intermediate % 128) {
@@ -637,7 +720,7 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   be->n_local = c.n_experts / c.ep_size;
   be->e_lo = c.ep_rank * be->n_local;
   be->e_hi = be->e_lo + be->n_local;
-  be->n_slots = be->n_local + c.n_shared_experts;
+  be->n_slots = be->n_local + c.n_shared_experts + c.replica_slots;
   be->rows_cap = round_up(c.max_tokens * (c.top_k + c.n_shared_experts), 128) + 128;
   be->max_chunks = be->rows_cap / 16 + be->n_slots + c.n_shared_experts * (c.max_tokens / 16 + 1) + 8;
 
@@ -681,8 +764,9 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
   CKC(cudaMalloc(&be->ep_counters, EK_EP_MAX_RANKS * sizeof(uint32_t)));
   CKC(cudaMemset(be->ep_counters, 0, EK_EP_MAX_RANKS * sizeof(uint32_t)));
-  CKC(cudaMalloc(&be->prof, kProfWords * sizeof(long long)));
-  CKC(cudaMemset(be->prof, 0, kProfWords * sizeof(long long)));
+  CKC(cudaMalloc(&be->sk_buf, ffn_tc_scratch_floats(be->n_sm) * sizeof(float)));
+  CKC(cudaMalloc(&be->sk_flags, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
+  CKC(cudaMemset(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
   CKC(cudaMallocHost(&be->h_status, sizeof(DevStatus)));
   be->h_chunks_cap = std::max(1024, be->max_chunks);
   CKC(cudaMallocHost(&be->h_chunks, sizeof(ChunkDesc) * be->h_chunks_cap));
@@ -706,6 +790,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   if (impl && std::string(impl) == "simt") be->ffn_impl = 1;
   const char* prec = getenv("EK_B200_PRECISE_DEQUANT");
   if (prec && prec[0] == '1') be->precise = 1;
+  const char* sk = getenv("EK_B200_SPLIT_K");
+  if (sk && sk[0] == '0') be->split_k = 0;
   *out = be;
   return EK_OK;
 }
@@ -727,7 +813,7 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaFree(be->tk_dev);
   cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->partial); cudaFree(be->flag_dev); cudaFree(be->ids); cudaFree(be->counts);
   cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
-  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->prof); cudaFree(be->ep_counters); cudaFree(be->maps);
+  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->sk_buf); cudaFree(be->sk_flags); cudaFree(be->ep_counters); cudaFree(be->maps);
   cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_segs); cudaFree(be->segs); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
@@ -790,6 +876,11 @@ int32_t ek_expert_evict(ek_backend_t* be, const char* id) {
   if (it == be->experts.end()) return EK_OK;   // ExpertDB::remove ignores unknown ids
   Layer& L = be->layers[it->second.layer];
   unregister_slots(be, L, it->second.slot);
+  const int ri = it->second.slot - be->n_local - be->cfg.n_shared_experts;
+  if (ri >= 0) {   // a replica slot: withdraw it
+    publish_replica(be, L, L.replica_expert[ri], -1);
+    L.replica_expert[ri] = -1;
+  }
   be->experts.erase(it);
   return EK_OK;
 }
@@ -806,8 +897,11 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
   if (c.model_name[0] && model != c.model_name)
     return fail(be, EK_INVALID_INPUT, "expert id %s does not belong to model %s", id, c.model_name);
   if (shared && c.n_shared_experts == 0) return fail(be, EK_INVALID_INPUT, "layer has no shared expert: %s", id);
-  if (!shared && (expert < be->e_lo || expert >= be->e_hi))
-    return fail(be, EK_INVALID_INPUT, "expert %d is not in this rank's range [%d,%d)", expert, be->e_lo, be->e_hi);
+  if (!shared && (expert < 0 || expert >= c.n_experts))
+    return fail(be, EK_INVALID_INPUT, "expert %d outside [0,%d)", expert, c.n_experts);
+  if (!shared && (expert < be->e_lo || expert >= be->e_hi) && c.replica_slots == 0)
+    return fail(be, EK_INVALID_INPUT, "expert %d is not in this rank's range [%d,%d) and the backend has no replica slots",
+                expert, be->e_lo, be->e_hi);
 
   // ExpertWeight::from_safetensor (ek-computation/src/ffn/meta.rs:57-75)
   const ek_tensor_view_t* up = find_suffix(t, n, "w1.weight", "up_proj.weight");
@@ -845,6 +939,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
 
   std::lock_guard<std::mutex> lg(be->load_mu);
   Layer* L = nullptr;
+  int slot_routed = -1;
   {
     std::unique_lock<std::shared_mutex> g(be->reg_mu);
     int rc = ensure_layer(be, layer, &L);
@@ -856,6 +951,11 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     if (live != be->experts.end()) {
       unregister_slots(be, *L, live->second.slot);
       be->experts.erase(live);
+    }
+    if (!shared) {
+      slot_routed = routed_slot(be, *L, expert, true);
+      if (slot_routed < 0)
+        return fail(be, EK_NO_MEMORY, "all %d replica slots of layer %d are taken", c.replica_slots, layer);
     }
   }
   cudaStream_t ls = be->load_stream;
@@ -902,7 +1002,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
 
   const int n_virtual = shared ? c.n_shared_experts : 1;
   for (int v = 0; v < n_virtual; ++v) {
-    const int slot = shared ? be->n_local + v : expert - be->e_lo;
+    const int slot = shared ? be->n_local + v : slot_routed;
     uint8_t* gu0 = L->gu + (size_t)slot * d.it * d.kt_gu * 2 * kTileBytes;
     uint8_t* dn0 = L->dn + (size_t)slot * d.hp * d.kt_dn * 2 * kTileBytes;
     for (int m = 0; m < 2; ++m) {   // 0 gate, 1 up
@@ -911,7 +1011,6 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
       rp.row0 = v * c.intermediate; rp.n_rows = c.intermediate;
       rp.col0 = 0; rp.n_cols = c.hidden;
       rp.esz = esz;
-      rp.pair_interleave = c.quant == EK_QUANT_FP8_BLOCK128;
       rp.dst = gu0 + (size_t)m * kTileBytes;
       rp.rt_stride = (int64_t)d.kt_gu * 2 * kTileBytes;
       rp.kt_stride = 2 * kTileBytes;
@@ -933,7 +1032,6 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     rp.row0 = 0; rp.n_rows = c.hidden;
     rp.col0 = v * c.intermediate; rp.n_cols = c.intermediate;
     rp.esz = esz;
-    rp.pair_interleave = c.quant == EK_QUANT_FP8_BLOCK128;
     rp.dst = dn0;
     rp.rt_stride = 0; rp.kt_stride = 0;
     rp.rt_pairs = 1;                       // row tiles 2j, 2j+1 adjacent per K tile; an odd tail is zero-filled
@@ -948,6 +1046,13 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
       sp.stride = 1; sp.lane = 0; sp.rt_pairs = 1;
       be->launches += launch_scale_retile(sp, ls);
     }
+    if (c.quant != EK_QUANT_BF16) {
+      // one power of two per expert and GEMM, from the largest block scale of its matrices
+      be->launches += launch_scale_pow(ssrc[0], (int64_t)sc[0]->shape[0] * sc[0]->shape[1], ssrc[1],
+                                       (int64_t)sc[1]->shape[0] * sc[1]->shape[1], L->pow2 + slot, ls);
+      be->launches += launch_scale_pow(ssrc[2], (int64_t)sc[2]->shape[0] * sc[2]->shape[1], nullptr, 0,
+                                       L->pow2 + be->n_slots + slot, ls);
+    }
     const int32_t one = 1;
     CK(cudaMemcpyAsync(L->registered + slot, &one, sizeof one, cudaMemcpyHostToDevice, ls));
   }
@@ -955,10 +1060,11 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
   CK(cudaGetLastError());
   {
     std::unique_lock<std::shared_mutex> g(be->reg_mu);
-    for (int v = 0; v < n_virtual; ++v) L->host_registered[shared ? be->n_local + v : expert - be->e_lo] = 1;
+    for (int v = 0; v < n_virtual; ++v) L->host_registered[shared ? be->n_local + v : slot_routed] = 1;
     be->loading.erase(id);
-    ExpertRef ref{layer, shared ? be->n_local : expert - be->e_lo};
+    ExpertRef ref{layer, shared ? be->n_local : slot_routed};
     be->experts[id] = ref;
+    if (!shared && (expert < be->e_lo || expert >= be->e_hi)) publish_replica(be, *L, expert, slot_routed);
   }
   return EK_OK;
 }
@@ -975,8 +1081,10 @@ struct TileBlobHeader {
   uint32_t version;         // EK_TILE_LAYOUT_VERSION
   int32_t quant, hidden, intermediate, n_virtual;
   uint32_t reserved;
-  uint64_t gu_bytes, dn_bytes, gu_scale_bytes, dn_scale_bytes;   // per virtual slot
+  uint64_t gu_bytes, dn_bytes, gu_scale_bytes, dn_scale_bytes;   // per virtual slot; quantised slots end with
+                                                                 // two floats: the gate/up and down powers of two
 };
+constexpr size_t kBlobPowBytes = 2 * sizeof(float);
 static_assert(sizeof(TileBlobHeader) == 64, "blob header is 64 bytes");
 
 void tile_sizes(const ek_backend* be, TileBlobHeader* h) {
@@ -995,8 +1103,11 @@ int check_expert_id(ek_backend* be, const char* id, int* layer, int* expert, boo
   if (c.model_name[0] && model != c.model_name)
     return fail(be, EK_INVALID_INPUT, "expert id %s does not belong to model %s", id, c.model_name);
   if (*shared && c.n_shared_experts == 0) return fail(be, EK_INVALID_INPUT, "layer has no shared expert: %s", id);
-  if (!*shared && (*expert < be->e_lo || *expert >= be->e_hi))
-    return fail(be, EK_INVALID_INPUT, "expert %d is not in this rank's range [%d,%d)", *expert, be->e_lo, be->e_hi);
+  if (!*shared && (*expert < 0 || *expert >= c.n_experts))
+    return fail(be, EK_INVALID_INPUT, "expert %d outside [0,%d)", *expert, c.n_experts);
+  if (!*shared && (*expert < be->e_lo || *expert >= be->e_hi) && c.replica_slots == 0)
+    return fail(be, EK_INVALID_INPUT, "expert %d is not in this rank's range [%d,%d) and the backend has no replica slots",
+                *expert, be->e_lo, be->e_hi);
   return EK_OK;
 }
 
@@ -1016,7 +1127,7 @@ int32_t ek_expert_export_tiles(ek_backend_t* be, const char* id, void* blob, siz
   h.quant = be->cfg.quant; h.hidden = be->cfg.hidden; h.intermediate = be->cfg.intermediate;
   h.n_virtual = shared ? be->cfg.n_shared_experts : 1;
   tile_sizes(be, &h);
-  const size_t per = h.gu_bytes + h.dn_bytes + h.gu_scale_bytes + h.dn_scale_bytes;
+  const size_t per = h.gu_bytes + h.dn_bytes + h.gu_scale_bytes + h.dn_scale_bytes + (h.gu_scale_bytes ? kBlobPowBytes : 0);
   *needed = sizeof h + per * h.n_virtual;
   if (!blob || cap < *needed) return fail(be, EK_INVALID_INPUT, "tile blob needs %zu bytes", *needed);
   std::lock_guard<std::mutex> lg(be->load_mu);
@@ -1044,6 +1155,9 @@ int32_t ek_expert_export_tiles(ek_backend_t* be, const char* id, void* blob, siz
       o += h.gu_scale_bytes;
       CK(cudaMemcpyAsync(o, reinterpret_cast<const uint8_t*>(L->dn_scale) + (size_t)slot * h.dn_scale_bytes, h.dn_scale_bytes, cudaMemcpyDeviceToHost, ls));
       o += h.dn_scale_bytes;
+      CK(cudaMemcpyAsync(o, L->pow2 + slot, sizeof(float), cudaMemcpyDeviceToHost, ls));
+      CK(cudaMemcpyAsync(o + sizeof(float), L->pow2 + be->n_slots + slot, sizeof(float), cudaMemcpyDeviceToHost, ls));
+      o += kBlobPowBytes;
     }
   }
   CK(cudaStreamSynchronize(ls));
@@ -1071,11 +1185,12 @@ int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* b
       h.gu_scale_bytes != want.gu_scale_bytes || h.dn_scale_bytes != want.dn_scale_bytes)
     return fail(be, EK_INVALID_INPUT, "tile blob was written for another configuration (quant %d, H %d, I %d, %d slots)",
                 h.quant, h.hidden, h.intermediate, h.n_virtual);
-  const size_t per = h.gu_bytes + h.dn_bytes + h.gu_scale_bytes + h.dn_scale_bytes;
+  const size_t per = h.gu_bytes + h.dn_bytes + h.gu_scale_bytes + h.dn_scale_bytes + (h.gu_scale_bytes ? kBlobPowBytes : 0);
   if (len != sizeof h + per * n_virtual) return fail(be, EK_SAFETENSOR, "tile blob has %zu bytes, expected %zu", len, sizeof h + per * n_virtual);
 
   std::lock_guard<std::mutex> lg(be->load_mu);
   Layer* L = nullptr;
+  int slot_routed = -1;
   {
     std::unique_lock<std::shared_mutex> g(be->reg_mu);
     rc = ensure_layer(be, layer, &L);
@@ -1085,6 +1200,11 @@ int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* b
       unregister_slots(be, *L, live->second.slot);
       be->experts.erase(live);
     }
+    if (!shared) {
+      slot_routed = routed_slot(be, *L, expert, true);
+      if (slot_routed < 0)
+        return fail(be, EK_NO_MEMORY, "all %d replica slots of layer %d are taken", be->cfg.replica_slots, layer);
+    }
   }
   cudaStream_t ls = be->load_stream;
   // the slot may still be read by forwards queued before an eviction
@@ -1092,7 +1212,7 @@ int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* b
   CK(cudaStreamWaitEvent(ls, be->fwd_done, 0));
   const uint8_t* in = reinterpret_cast<const uint8_t*>(blob) + sizeof h;
   for (int v = 0; v < n_virtual; ++v) {
-    const int slot = shared ? be->n_local + v : expert - be->e_lo;
+    const int slot = shared ? be->n_local + v : slot_routed;
     CK(cudaMemcpyAsync(L->gu + (size_t)slot * h.gu_bytes, in, h.gu_bytes, cudaMemcpyHostToDevice, ls));
     in += h.gu_bytes;
     CK(cudaMemcpyAsync(L->dn + (size_t)slot * h.dn_bytes, in, h.dn_bytes, cudaMemcpyHostToDevice, ls));
@@ -1102,6 +1222,9 @@ int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* b
       in += h.gu_scale_bytes;
       CK(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(L->dn_scale) + (size_t)slot * h.dn_scale_bytes, in, h.dn_scale_bytes, cudaMemcpyHostToDevice, ls));
       in += h.dn_scale_bytes;
+      CK(cudaMemcpyAsync(L->pow2 + slot, in, sizeof(float), cudaMemcpyHostToDevice, ls));
+      CK(cudaMemcpyAsync(L->pow2 + be->n_slots + slot, in + sizeof(float), sizeof(float), cudaMemcpyHostToDevice, ls));
+      in += kBlobPowBytes;
     }
     const int32_t one = 1;
     CK(cudaMemcpyAsync(L->registered + slot, &one, sizeof one, cudaMemcpyHostToDevice, ls));
@@ -1109,10 +1232,11 @@ int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* b
   CK(cudaStreamSynchronize(ls));
   {
     std::unique_lock<std::shared_mutex> g(be->reg_mu);
-    for (int v = 0; v < n_virtual; ++v) L->host_registered[shared ? be->n_local + v : expert - be->e_lo] = 1;
+    for (int v = 0; v < n_virtual; ++v) L->host_registered[shared ? be->n_local + v : slot_routed] = 1;
     be->loading.erase(id);
-    ExpertRef ref{layer, shared ? be->n_local : expert - be->e_lo};
+    ExpertRef ref{layer, shared ? be->n_local : slot_routed};
     be->experts[id] = ref;
+    if (!shared && (expert < be->e_lo || expert >= be->e_hi)) publish_replica(be, *L, expert, slot_routed);
   }
   return EK_OK;
 }
@@ -1208,6 +1332,7 @@ int serve_shared(ek_backend* be, ExpertReq& r, const ExpertRef& ent) {
   const size_t H = c.hidden;
   cudaStream_t s = be->stream;
   CK(cudaMemcpyAsync(be->xp, r.x, (size_t)n * H * 2, cudaMemcpyDefault, s));
+  if (f16_rows(be)) be->launches += launch_rows_to_f16(be->xp, n, c.hidden, s);
   const int nmax = n <= 32 ? 32 : n <= 64 ? 64 : 128;
   const int chunk_rows = be->ffn_impl == 1 ? 16 : nmax;
   const int per = (n + chunk_rows - 1) / chunk_rows;
@@ -1225,8 +1350,8 @@ int serve_shared(ek_backend* be, ExpertReq& r, const ExpertRef& ent) {
   CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * total, cudaMemcpyHostToDevice, s));
   be->h_status->aux1 = total;   // pinned word as the source of the count
   CK(cudaMemcpyAsync(be->n_chunks, &be->h_status->aux1, 4, cudaMemcpyHostToDevice, s));
-  run_ffn(be, L, nmax, 0);
-  run_ffn(be, L, nmax, 1);
+  run_ffn(be, L, nmax, 0, false);   // worker-level replies must not depend on what else was grouped
+  run_ffn(be, L, nmax, 1, false);   // worker-level replies must not depend on what else was grouped
   CombineParams cp;
   cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = be->y_dev;
   cp.T = n; cp.k = 0; cp.H = c.hidden; cp.n_shared = n_virtual; cp.Tk = 0; cp.bf16_products = 0;
@@ -1265,11 +1390,12 @@ int serve_group(ek_backend* be, int layer, std::vector<std::pair<ExpertReq*, int
     r.row0 = row;
     row += r.n;
   }
+  if (f16_rows(be)) be->launches += launch_rows_to_f16(be->xp, row, c.hidden, s);
   CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * n_chunks, cudaMemcpyHostToDevice, s));
   be->h_status->aux1 = n_chunks;
   CK(cudaMemcpyAsync(be->n_chunks, &be->h_status->aux1, 4, cudaMemcpyHostToDevice, s));
-  run_ffn(be, L, nmax, 0);
-  run_ffn(be, L, nmax, 1);
+  run_ffn(be, L, nmax, 0, false);   // worker-level replies must not depend on what else was grouped
+  run_ffn(be, L, nmax, 1, false);   // worker-level replies must not depend on what else was grouped
   for (auto& g : group) {
     ExpertReq& r = *g.first;
     CK(cudaMemcpyAsync(r.y, be->obuf + (size_t)r.row0 * H, (size_t)r.n * H * 2, cudaMemcpyDefault, s));
@@ -1694,7 +1820,7 @@ int32_t ek_ep_route(ek_backend_t* be, int32_t layer, const void* x_dev, int32_t 
   pp.T = T; pp.k = c.top_k; pp.E = c.n_experts; pp.e_lo = 0; pp.e_hi = c.n_experts;
   be->launches += launch_permute(pp, s);
   be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, reinterpret_cast<__nv_bfloat16*>(send_rows_dev),
-                                T, c.top_k, c.hidden, 0, 0, s);
+                                T, c.top_k, c.hidden, 0, 0, false, s);
   CK(cudaMemcpyAsync(counts_dev, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s));
   CK(cudaMemcpyAsync(L.last_counts, be->counts, sizeof(int32_t) * c.n_experts, cudaMemcpyDeviceToDevice, s));
   L.have_counts = true;
@@ -1782,6 +1908,7 @@ int32_t ek_ep_ffn(ek_backend_t* be, int32_t layer, const void* rows_dev, const i
   }
   if (S > 0)
     CK(cudaMemcpyAsync(be->xp + (size_t)rows_total * c.hidden, x_dev, (size_t)T * c.hidden * 2, cudaMemcpyDeviceToDevice, s));
+  if (f16_rows(be)) be->launches += launch_rows_to_f16(be->xp, (int64_t)rows_total + (S > 0 ? T : 0), c.hidden, s);
   CK(cudaMemcpyAsync(be->chunks, be->h_chunks, sizeof(ChunkDesc) * n_chunks, cudaMemcpyHostToDevice, s));
   be->h_ep_count[0] = n_chunks;
   CK(cudaMemcpyAsync(be->n_chunks, &be->h_ep_count[0], 4, cudaMemcpyHostToDevice, s));
@@ -2019,6 +2146,31 @@ int32_t ek_ep_peer_finish(ek_backend_t* be, int32_t layer, int32_t T, uint32_t s
   return EK_OK;
 }
 
+int32_t ek_ep_set_owners(ek_backend_t* be, int32_t layer, const int32_t* owners) {
+  if (!be) return EK_INVALID_INPUT;
+  const ek_config_t& c = be->cfg;
+  cudaSetDevice(c.device);
+  std::lock_guard<std::mutex> fg(be->fwd_mu);
+  std::shared_lock<std::shared_mutex> g(be->reg_mu);
+  auto li = be->layers.find(layer);
+  if (li == be->layers.end()) return fail(be, EK_EXPERT_NOT_FOUND, "layer %d holds no experts", layer);
+  Layer& L = li->second;
+  if (!owners) {
+    L.has_owners = false;
+    return EK_OK;
+  }
+  for (int e = 0; e < c.n_experts; ++e) {
+    if (owners[e] < 0 || owners[e] >= c.ep_size)
+      return fail(be, EK_INVALID_INPUT, "owner %d of expert %d outside [0,%d)", owners[e], e, c.ep_size);
+    if (owners[e] == c.ep_rank && (L.host_slot_of[e] < 0 || !L.host_registered[L.host_slot_of[e]]))
+      return fail(be, EK_EXPERT_NOT_FOUND, "expert %d is assigned to this rank but not registered here", e);
+  }
+  CK(cudaMemcpyAsync(L.owners, owners, sizeof(int32_t) * c.n_experts, cudaMemcpyHostToDevice, be->stream));
+  CK(cudaStreamSynchronize(be->stream));   // `owners` may be pageable and reused by the caller
+  L.has_owners = true;
+  return EK_OK;
+}
+
 // ---- observability -----------------------------------------------------------------------------
 
 int32_t ek_expert_counts(ek_backend_t* be, int32_t layer, int32_t* counts) {
@@ -2076,27 +2228,6 @@ int32_t ek_set_precise_dequant(ek_backend_t* be, int32_t on) {
   return EK_OK;
 }
 
-#ifdef EK_TC_PROFILE
-// Profile builds only: read and clear the per-role cycle counters of the tensor-core kernels.
-int32_t ek_debug_profile(ek_backend_t* be, long long* out32) {
-  if (!be || !out32) return EK_INVALID_INPUT;
-  cudaSetDevice(be->cfg.device);
-  std::lock_guard<std::mutex> fg(be->fwd_mu);
-  cudaStreamSynchronize(be->stream);
-  cudaMemcpy(out32, be->prof, 32 * sizeof(long long), cudaMemcpyDeviceToHost);
-  cudaMemset(be->prof, 0, 32 * sizeof(long long));
-  return EK_OK;
-}
-// Event trace of one CTA of the gate/up kernel: kTraceSteps K steps x kTraceEvents clock values.
-int32_t ek_debug_trace(ek_backend_t* be, long long* out, int32_t n_words) {
-  if (!be || !out || n_words > kProfWords - 32) return EK_INVALID_INPUT;
-  cudaSetDevice(be->cfg.device);
-  std::lock_guard<std::mutex> fg(be->fwd_mu);
-  cudaStreamSynchronize(be->stream);
-  cudaMemcpy(out, be->prof + 32, n_words * sizeof(long long), cudaMemcpyDeviceToHost);
-  return EK_OK;
-}
-#endif
 
 int32_t ek_debug_set_ffn_impl(ek_backend_t* be, int32_t impl) {
   if (!be || impl < 0 || impl > 1) return EK_INVALID_INPUT;

@@ -8,6 +8,7 @@
 #include "../../include/ek_b200.h"
 
 #ifdef __CUDACC__
+#include <cstdlib>
 #include <utility>
 // Programmatic dependent launch: the kernels of one layer pass are launched back to back with this
 // attribute, each begins with pdl_wait() (returns when every earlier kernel of the stream has
@@ -29,7 +30,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  // EK_B200_NO_PDL=1: plain stream order (griddepcontrol.* are no-ops then); for diagnosis
+  static const bool pdl = !(getenv("EK_B200_NO_PDL") && getenv("EK_B200_NO_PDL")[0] == '1');
+  cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 #endif
@@ -78,6 +81,8 @@ struct LayerWeights {
   const uint8_t* dn_tiles;   // [slot][hp][kt][row tile 2hp | 2hp+1][16 KiB]
   const float* gu_scale;     // [slot][it][kt][2]   (quantised only; K tile == 128-wide scale block)
   const float* dn_scale;     // [slot][hp][kt][2]
+  const float* gu_pow;       // [slot] power of two applied to the scaled activations of the gate/up GEMM
+  const float* dn_pow;       // [slot] same for the down GEMM (quantised only)
   const int32_t* registered; // [slots] 1 when the slot holds weights
   int32_t n_slots;
 };
@@ -142,6 +147,9 @@ struct PermuteParams {
   int32_t T, k, E;
   // expert-parallel window: experts [e_lo, e_hi) are local; rows of other experts are left out
   int32_t e_lo, e_hi;
+  // per-pass owner table [E] -> rank (replicated experts): when set it replaces the window rule
+  const int32_t* owners = nullptr;
+  int32_t rank = 0;
 };
 int launch_permute(const PermuteParams& p, cudaStream_t s);
 
@@ -153,6 +161,9 @@ struct WorklistParams {
   int32_t* n_chunks;         // out (single int)
   int32_t* counts_copy = nullptr;   // out [E]: copy of counts kept per layer for the activation metric (may be null)
   int32_t E, e_lo, e_hi;     // local expert window; slot = e - e_lo
+  const int32_t* owners = nullptr;   // [E] -> rank; replaces the window rule when set
+  const int32_t* slot_of = nullptr;  // [E] slot of every expert this rank holds (-1: none); needed with `owners`
+  int32_t rank = 0;
   int32_t chunk_rows;        // rows per chunk
   int32_t n_shared, T;       // shared virtual experts: slot = (e_hi-e_lo)+j, in_row = Tk, out_row = Tk+j*T
   int32_t Tk;
@@ -164,12 +175,13 @@ int launch_worklist(const WorklistParams& p, cudaStream_t s);
 // rows [0,Tk): xp[r] = x[perm[r]/k]; rows [Tk, Tk+T) = x (only when with_shared)
 // `n_routed` (device) = number of permuted rows that exist on this rank (offsets[E]).
 // The shared expert's rows are tokens [shared_t0, shared_t0 + shared_T) of x (shared_T = 0: none).
+// `to_f16`: write the rows as f16 (round to nearest, saturating), the activation type of the
+// quantised GEMM modes.
 int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_routed,
                   __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t shared_t0, int32_t shared_T,
-                  cudaStream_t s);
-
-constexpr int kTraceSteps = 96, kTraceEvents = 24;
-constexpr int kProfWords = 32 + kTraceSteps * kTraceEvents;
+                  bool to_f16, cudaStream_t s);
+// rows[0 .. n_rows) of a [*, H] bf16 buffer -> f16 in place (same size)
+int launch_rows_to_f16(__nv_bfloat16* rows, int64_t n_rows, int32_t H, cudaStream_t s);
 
 struct FfnParams {
   Dims d;
@@ -187,9 +199,14 @@ struct FfnParams {
   const CUtensorMap* x_maps;   // device array[4]
   const CUtensorMap* h_maps;   // device array[4]
   int32_t n_sm;
-  int32_t precise;           // fp8: apply block scales in fp32 (bit-exact reference dequantisation)
-  long long* prof;           // cycle counters of a -DEK_TC_PROFILE build, else unused
+  int32_t precise;           // quantised weights: bf16_rne(float(w) * scale) as the A operand (bit-exact reference dequantisation)
+  int32_t split_k;           // cut the work items left over after the last full wave along K over all CTAs
+  float* sk_buf;             // [n_sm][2][128][128] fp32 partial accumulators of split items
+  uint32_t* sk_flags;        // [n_sm][32] one word per (CTA, warp): partial written; zero between launches
 };
+size_t ffn_tc_scratch_floats(int n_sm);
+// true: the tensor-core GEMMs of this configuration take (and, gate/up, produce) f16 activations
+bool ffn_tc_f16_activations(int quant, int precise);
 // Straightforward CUDA-core evaluation of the same tiled weights; used by the tests as an
 // independent check of the tensor-core path at sizes the CPU oracle cannot reach.
 // `which`: 0 = gate/up + SwiGLU (xp -> hbuf), 1 = down projection (hbuf -> obuf).
@@ -239,7 +256,6 @@ struct RetileParams {
   int32_t row0, n_rows;   // source row window written as tiles (virtual shared experts)
   int32_t col0, n_cols;   // source column window
   int32_t esz;            // 1 or 2
-  int32_t pair_interleave;  // fp8: store K-consecutive pairs in the form the GEMM decodes cheaply
   int32_t rt_pairs;         // 1: row tiles 2j and 2j+1 are stored next to each other per K tile:
                             //    tile(rt,kt) at dst + (((rt>>1)*n_kt + kt)*2 + (rt&1)) * 16 KiB
   uint8_t* dst;           // first tile of (row tile 0, k tile 0)
@@ -259,6 +275,7 @@ struct ScaleRetileParams {
   int32_t rt_pairs;       // 1: dst[(((rt>>1)*n_kt + kt)*2 + (rt&1))]
 };
 int launch_scale_retile(const ScaleRetileParams& p, cudaStream_t s);
+int launch_scale_pow(const float* a, int64_t na, const float* b, int64_t nb, float* out, cudaStream_t s);
 int launch_fill_f32(float* dst, float v, int64_t n, cudaStream_t s);
 int launch_dequant(const void* w, int32_t w_dtype, const float* scale, int32_t rows, int32_t cols,
                    __nv_bfloat16* out, cudaStream_t s);

@@ -31,10 +31,8 @@ __device__ __forceinline__ void decode16(const uint4& raw, float scale, float* o
     for (int i = 0; i < 16; ++i) {
       float v;
       if (QUANT == EK_QUANT_FP8_BLOCK128) {
-        // undo the pair interleave of layout.cu, byte by byte
-        const uint32_t mine = b[i], other = b[i ^ 1];
         __nv_fp8_e4m3 q;
-        q.__x = static_cast<unsigned char>((mine & 0x80) | ((mine & 0x07) << 4) | ((other >> 3) & 0x0F));
+        q.__x = b[i];
         v = static_cast<float>(q);
       } else {
         v = static_cast<float>(static_cast<int8_t>(b[i]));

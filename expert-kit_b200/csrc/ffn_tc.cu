@@ -4,26 +4,58 @@
 // w8a16_activate (expert_torch.rs:24-53) for ALL experts of a layer in two launches.
 //
 // Formulation ("weights as the M operand"): for one work item (chunk of <= NMAX activation
-// rows of one expert, one tile of 128 weight rows)
+// rows of one expert, one pair of 128-row weight tiles)
 //        D[128 weight rows, N rows of x] (+)= W_tile[128, K] * X_chunk[N, K]^T
 // so the MMA always runs at M = 128 no matter how few tokens an expert received, and the
 // weight stream - the thing that is HBM-bound at decode batch sizes - is read exactly once.
 //
-//   producer warp   : bulk-copies the next 16 KiB weight tile(s) (fp8 / int8 / bf16, already
-//                     laid out for conflict-free reads) and TMA-loads the matching [N, K]
-//                     activation tile (128-byte swizzle) into a ring of shared-memory stages
-//   converter warps : thread r reads weight row r of the tile from shared memory, dequantises
-//                     it to bf16 (block scale applied in fp32, one rounding - the reference
-//                     formula) and stores it into tensor memory with tcgen05.st as the A operand
-//   MMA warp        : one thread issues tcgen05.mma (A from tensor memory, B from shared
-//                     memory through a swizzled descriptor, fp32 accumulators in tensor memory)
-//   epilogue        : the converter warps read the accumulators with tcgen05.ld; gate/up mode
-//                     applies silu(gate) * up in fp32 and writes h (bf16); down mode writes
-//                     the expert output rows (bf16)
+// Roles of the 640 threads of a CTA (one persistent CTA per SM):
+//   2 producer threads : one bulk-copies the next 32 KiB of weight tiles (fp8 / int8 / bf16,
+//                        already laid out for conflict-free reads) into the stage ring, the
+//                        other TMA-loads the matching [N, K] activation tile (128-byte swizzle)
+//   16 converter warps : two groups of 8 on alternating K steps.  Thread r reads weight row r
+//                        of its tile from shared memory, turns it into the 16-bit A operand and
+//                        stores it into tensor memory with tcgen05.st (the A operand never goes
+//                        back through shared memory).  How the block scale is applied depends on
+//                        the mode, see below.  The same warps run the epilogue.
+//   2 MMA threads      : each issues tcgen05.mma for one of the two tiles of a stage (A from
+//                        tensor memory, B from shared memory through a swizzled descriptor,
+//                        fp32 accumulators in tensor memory): one thread's instruction stream
+//                        between MMAs costs about as much as the MMAs take.
 //
-// Every mbarrier wait is bounded (see ptx.cuh); on a timeout the CTA records DEV_TIMEOUT in
-// the status word, drains what it has in flight and leaves, so a protocol error can never
-// hang the device.
+// Quantised weights (fp8 e4m3 / int8 with one fp32 scale per 128x128 block; K tile == scale block).
+// The activations of these GEMMs are kept in f16 (the gather kernel and the gate/up epilogue write
+// f16: exact for bf16 inputs inside the f16 range, saturating outside) and the weights are converted
+// EXACTLY to f16 with no arithmetic: cvt.rn.f16x2.e4m3x2, or for int8 a magic-number subtraction - 2
+// instructions per 4 weights.  kind::f16 needs both operands in the same 16-bit type (an f16 A with
+// a bf16 B is an illegal instruction).  Where the block scale s goes depends on the chunk size:
+//   scale-on-B  (chunks of <= 64 rows) the converters of the step rewrite the activation tile as
+//               f16(x * s * 2^c) before the MMA reads it, one scaled copy per tile of the stage.  One
+//               rounding per product term, to 11 bits, on the activation factor - where the
+//               reference's bf16(w * s) * x rounds the weight factor to 8 bits.
+//   scale-on-A  (128-row chunks: rewriting 128 activation rows per step costs more than scaling 128
+//               weight rows) A = f16(w) * (s * 2^c') as a two-term packed f16 multiply, B = the f16
+//               activations as TMA delivers them.
+//   c, c' are powers of two per expert and GEMM, chosen at registration from the largest block
+//   scale so that the scaled operand sits in the middle of the f16 range; the epilogue multiplies
+//   the accumulators by 2^-c.
+//   reference   (ek_set_precise_dequant) A = bf16_rne(float(w) * s), bf16 activations: the bit-exact
+//               reference formula (expert_torch.rs:24-53), about 6 instructions per weight pair.
+// bf16 weights pass through unconverted.
+//
+// Work decomposition: items are strided over the CTAs; the items left over after the last full
+// wave are cut along K into equal parts over all CTAs ("stream-K tail").  The CTA holding the
+// first part of a split item is its owner: the others leave fp32 partial accumulators in a
+// scratch buffer and raise a flag, the owner adds them in part order (deterministic) before its
+// epilogue and clears the flags.  A CTA computes the part it does not own FIRST and the part it
+// owns LAST, so the owner practically never waits.
+//
+// Every wait (mbarrier or flag) is bounded; on a timeout the CTA records DEV_TIMEOUT in the
+// status word, drains what it has in flight, frees its tensor memory and leaves.
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
 #include "ek_internal.h"
 #include "ptx.cuh"
 
@@ -33,54 +65,45 @@ namespace {
 
 using namespace ekptx;
 
-// Converter warps come in groups of 8 (two warpgroups: one per tile of the stage, one warp per
-// tensor-memory lane quarter).  Group g converts the K steps kt = g, g + kGroups, ...: with two
-// groups, two steps are in conversion at any time and each scheduler holds four converter warps
-// instead of two, whose conversion phases (bound by the half-rate integer pipe and by dependent
-// issue) overlap instead of taking turns.  Splitting a tile row between two warps instead doubled
-// the per-warp barrier work and measured 4-9 % slower.
-#ifndef EK_CONV_WARPS
-#define EK_CONV_WARPS 16
-#endif
-constexpr int kConvWarps = EK_CONV_WARPS;
+// Converter warps come in two groups of 8 (two warpgroups each: one per tile of the stage, one
+// warp per tensor-memory lane quarter).  A group converts every other K step: two steps are in
+// conversion at any time and each scheduler holds four converter warps whose dense phases overlap.
+constexpr int kConvWarps = 16;
 constexpr int kGroupWarps = 8;
 constexpr int kGroups = kConvWarps / kGroupWarps;
-static_assert(kConvWarps % kGroupWarps == 0 && kGroups >= 1 && kGroups <= 2,
-              "converter warps come in one or two groups of 8 (three groups faulted at launch and are not supported)");
+static_assert(kGroups == 2, "the stage / A-slot protocol below is written for two converter groups");
 constexpr int kMmaWarps = 2;
 constexpr int kProdWarps = 2;                 // weight ring, activation ring: one warp each
 constexpr int kFirstMmaWarp = kConvWarps + kProdWarps;
-#ifdef EK_TC_PROFILE
-constexpr int kObserverWarps = 1;   // watches the weight barriers: true issue -> landed time
-#else
-constexpr int kObserverWarps = 0;
-#endif
-constexpr int kThreads = (kConvWarps + kProdWarps + kMmaWarps + kObserverWarps) * 32;
-constexpr int kASlotCols = 64;   // tensor-memory columns per A staging slot (128 bf16 along K)
+constexpr int kThreads = (kConvWarps + kProdWarps + kMmaWarps) * 32;
+constexpr int kASlotCols = 64;   // tensor-memory columns per A staging slot (128 16-bit values along K)
 constexpr int kTmemCols = 512;
-#ifndef EK_MAX_A_SLOTS
-#define EK_MAX_A_SLOTS 6
-#endif
-constexpr int kMaxASlots = EK_MAX_A_SLOTS;
+constexpr int kMaxASlots = 6;
 constexpr int kSmemLimit = 232448 - 4096;
+constexpr int kMinPart = 8;      // K steps: smallest part of a split work item
 
-template <int QUANT, bool GATEUP, int NMAX>
+enum { kModeRaw = 0, kModeScaleB2 = 1, kModeScaleAH = 2, kModeScaleA = 3 };
+
+template <int QUANT, bool GATEUP, int NMAX, int MODE>
 struct Cfg {
   static constexpr int TKE = QUANT == EK_QUANT_BF16 ? 64 : 128;   // K elements per tile
   // A stage holds two weight tiles of the same K step, one per converter warpgroup / MMA chain,
-  // and the one activation tile both multiply:
+  // and the activation tile both multiply (two scaled copies of it in mode ScaleB2):
   //   gate/up : the gate and the up tile of intermediate-row tile rt
   //   down    : the tiles of hidden-row tiles 2*rp and 2*rp+1
   static constexpr int W_BYTES = 2 * kTileBytes;
   static constexpr int X_ATOMS = TKE / 64;                        // 64-element swizzle atoms along K
   static constexpr int X_BYTES = NMAX * X_ATOMS * 128;
-  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int X_COPIES = MODE == kModeScaleB2 ? 2 : 1;
+  static constexpr int STAGE_BYTES = W_BYTES + X_COPIES * X_BYTES;
   static constexpr int STAGES_RAW = kSmemLimit / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int MMAS = TKE / 16;                           // MMA instructions per tile
   static constexpr int NCH = 8;                                   // 16-byte chunks per thread (its tile row)
   static constexpr int WPC = QUANT == EK_QUANT_BF16 ? 4 : 8;      // 32-bit A words per chunk
   static constexpr int NW = NCH * WPC;
+  static constexpr bool SCALE_B = MODE == kModeScaleB2;
+  static constexpr bool F16 = MODE == kModeScaleB2 || MODE == kModeScaleAH;   // both MMA operands f16, h written as f16
   // tensor memory: two accumulators of NMAX columns, the rest is a ring of A staging slots (an
   // even number, shared by the two chains): 6 slots for the decode variants, 4 at NMAX = 128
   static constexpr int A_BASE = 2 * NMAX;
@@ -89,29 +112,13 @@ struct Cfg {
   static constexpr int A_PER = A_SLOTS / 2;                       // slots per chain
   static_assert(A_SLOTS >= 4, "need at least two A slots per chain");
   // a converter reaches step it + STAGES only after its chain completed step it + STAGES - A_PER >= it,
-  // i.e. after the ready barrier of step it has flipped: arrivals of two laps never mix
-  static_assert(A_PER <= STAGES_RAW, "A slots per chain must not exceed the stage count");
+  // i.e. after the ready barrier of step it has flipped: arrivals of two laps never mix; the same
+  // inequality makes the converters' parity waits exact (see the converter loop)
+  static_assert(A_PER <= STAGES, "A slots per chain must not exceed the stage count");
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
   static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
+  static_assert(QUANT != EK_QUANT_BF16 || MODE == kModeRaw, "bf16 weights are not converted");
 };
-
-
-
-// Optional per-role cycle accounting (build with -DEK_TC_PROFILE): where each role's time goes.
-#ifdef EK_TC_PROFILE
-#define PROF_DECL long long pt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pc_ = clock64();
-#define PROF_LAP(i) { long long n_ = clock64(); pt_[i] += n_ - pc_; pc_ = n_; }
-#define PROF_DUMP(role) \
-  if (p.prof) for (int i_ = 0; i_ < 6; ++i_) atomicAdd((unsigned long long*)&p.prof[(role) * 8 + i_], (unsigned long long)pt_[i_]);
-#define TRACE(itv, ev) \
-  if (GATEUP && blockIdx.x == 7 && p.prof && (itv) >= 300u && (itv) < 300u + kTraceSteps) \
-    p.prof[32 + ((itv) - 300u) * kTraceEvents + (ev)] = clock64();
-#else
-#define PROF_DECL
-#define PROF_LAP(i)
-#define PROF_DUMP(role)
-#define TRACE(itv, ev)
-#endif
 
 __device__ __forceinline__ void report(DevStatus* st, int code, int where, int a0, int a1) {
   if (atomicCAS(&st->code, DEV_OK, code) == DEV_OK) {
@@ -121,76 +128,136 @@ __device__ __forceinline__ void report(DevStatus* st, int code, int where, int a
   }
 }
 
-// ---- dequantisation of one 16-byte chunk into packed bf16 pairs ---------------------------
-// fp8 e4m3 payloads are stored pair-interleaved (see layout.cu): for two K-consecutive
-// weights a, b the stored bytes are
-//     p = [sa . . . . ea3 ea2 ea1] | [. eb0 mb2 mb1 mb0 . . .]
-//     q = [sb . . . . eb3 eb2 eb1] | [. ea0 ma2 ma1 ma0 . . .]
-// so that with w1 = w << 1 one byte permute and one AND yield, per 16-bit lane,
-//     [s 0000 eeee mmm 0000]  =  bf16 bits of  value * 2^-120   (exact, subnormals included).
-// One shift per four weights, one permute + one AND per two: 1.25 integer ops per weight
-// instead of 4 for plain e4m3 bytes - the integer pipe is what bounds this kernel otherwise.
-//
-// The block scale is then applied either
-//   fast   : packed, with the scale split into two bf16 terms s = hi + lo (hi = bf16(s * 2^120),
-//            lo = bf16(s * 2^120 - hi)):  out = fma(y, hi, y * lo)  - two bf16x2 ops per two
-//            weights, 16 significant bits of the scale, one final rounding; differs from the
-//            reference formula only where the product lies within 2^-17 of a rounding boundary, or
-//   precise: in fp32, one rounding to bf16 - bit-exact bf16_rne(float(w) * scale), the reference
-//            formula (ek-computation/src/ffn/expert_torch.rs:24-53).
+// ---- work decomposition ----------------------------------------------------------------------
+// The same sequence of units is walked by every role of a CTA.
+struct Unit {
+  int item, kt0, kt1;
+};
+struct Sched {
+  int KT, n_full, tail_hi, next_item, g, L;
+  __device__ __forceinline__ Sched(int total, int KT_, int split_k) {
+    KT = KT_;
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    n_full = split_k ? (total / G) * G : total;
+    int tk = (total - n_full) * KT;              // K steps of the left-over items (< G * KT)
+    L = (tk + G - 1) / G;
+    if (L < kMinPart) L = kMinPart;
+    if (L * 10 > KT * 9) {   // cutting would shorten the tail by less than a tenth: not worth the partial sums
+      n_full = total;
+      L = KT;
+      tk = 0;
+    }
+    const int lo = min(c * L, tk);
+    tail_hi = min(lo + L, tk);
+    next_item = c;
+    g = lo;
+  }
+  __device__ __forceinline__ bool next(Unit& u) {
+    if (next_item < n_full) {
+      u.item = next_item; u.kt0 = 0; u.kt1 = KT;
+      next_item += (int)gridDim.x;
+      return true;
+    }
+    if (g < tail_hi) {
+      u.item = n_full + g / KT;
+      u.kt0 = g % KT;
+      u.kt1 = min(KT, u.kt0 + (tail_hi - g));
+      g += u.kt1 - u.kt0;
+      return true;
+    }
+    return false;
+  }
+  // CTAs after this one that hold the remaining parts of an item this CTA owns up to kt1
+  __device__ __forceinline__ int followers(const Unit& u) const { return (KT - u.kt1 + L - 1) / L; }
+};
+
+// ---- conversion of a weight row into packed 16-bit A words --------------------------------------
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
   uint32_t r;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+__device__ __forceinline__ uint32_t fma_f16x2(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t r;
-  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
-template <bool PRECISE>
-__device__ __forceinline__ void cvt_fp8_word(uint32_t w, float scale, uint32_t s_hi, uint32_t s_lo, uint32_t* out) {
-  const uint32_t w1 = w << 1;
-  const uint32_t y0 = __byte_perm(w, w1, 0x1405) & 0x87F087F0u;
-  const uint32_t y1 = __byte_perm(w, w1, 0x3627) & 0x87F087F0u;
-  if (PRECISE) {
-    const float k = 0x1p120f;
-    out[0] = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(y0 << 16), k), scale),
-                       __fmul_rn(__fmul_rn(__uint_as_float(y0 & 0xFFFF0000u), k), scale));
-    out[1] = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(y1 << 16), k), scale),
-                       __fmul_rn(__fmul_rn(__uint_as_float(y1 & 0xFFFF0000u), k), scale));
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// two e4m3 bytes -> two f16, exact (every e4m3 value, subnormals included, is an f16 value)
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<unsigned short>(two_bytes)));
+  return r;
+}
+// four int8 -> four f16, exact: 0x6400 | (b ^ 0x80) is the f16 value 1024 + (b + 128); subtract 1152
+__device__ __forceinline__ void s8x4_to_f16(uint32_t w, uint32_t* out) {
+  const uint32_t lo = __byte_perm(w, 0x64646464u, 0x4140) ^ 0x00800080u;
+  const uint32_t hi = __byte_perm(w, 0x64646464u, 0x4342) ^ 0x00800080u;
+  out[0] = sub_f16x2(lo, 0x64806480u);
+  out[1] = sub_f16x2(hi, 0x64806480u);
+}
+__device__ __forceinline__ float2 f16x2_to_float2(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
+// One 32-bit word of four quantised weights -> two A words.
+//   kModeScaleA  : bf16_rne(float(w) * scale), the reference formula (expert_torch.rs:24-53)
+//   kModeScaleAH : f16(w) * (s_hi + s_lo), packed f16
+//   kModeScaleB2 : f16(w) exactly
+template <int QUANT, int MODE>
+__device__ __forceinline__ void cvt_word(uint32_t w, float scale, uint32_t s_hi, uint32_t s_lo, uint32_t* out) {
+  if (MODE == kModeScaleA) {
+    if (QUANT == EK_QUANT_FP8_BLOCK128) {
+      const float2 a = f16x2_to_float2(e4m3x2_to_f16x2(w & 0xFFFFu)), b = f16x2_to_float2(e4m3x2_to_f16x2(w >> 16));
+      out[0] = pack_bf16(__fmul_rn(a.x, scale), __fmul_rn(a.y, scale));
+      out[1] = pack_bf16(__fmul_rn(b.x, scale), __fmul_rn(b.y, scale));
+    } else {
+      const float f0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w & 0xff)));
+      const float f1 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 8) & 0xff)));
+      const float f2 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 16) & 0xff)));
+      const float f3 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 24) & 0xff)));
+      out[0] = pack_bf16(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
+      out[1] = pack_bf16(__fmul_rn(f2, scale), __fmul_rn(f3, scale));
+    }
   } else {
-    out[0] = fma_bf16x2(y0, s_hi, mul_bf16x2(y0, s_lo));
-    out[1] = fma_bf16x2(y1, s_hi, mul_bf16x2(y1, s_lo));
+    if (QUANT == EK_QUANT_FP8_BLOCK128) {
+      out[0] = e4m3x2_to_f16x2(w & 0xFFFFu);
+      out[1] = e4m3x2_to_f16x2(w >> 16);
+    } else {
+      s8x4_to_f16(w, out);
+    }
+    if (MODE == kModeScaleAH) {
+      out[0] = fma_f16x2(out[0], s_hi, mul_f16x2(out[0], s_lo));
+      out[1] = fma_f16x2(out[1], s_hi, mul_f16x2(out[1], s_lo));
+    }
   }
 }
-__device__ __forceinline__ void cvt_int8_word(uint32_t w, float scale, uint32_t* out) {
-  float f0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w & 0xff)));
-  float f1 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 8) & 0xff)));
-  float f2 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 16) & 0xff)));
-  float f3 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 24) & 0xff)));
-  out[0] = pack_bf16(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
-  out[1] = pack_bf16(__fmul_rn(f2, scale), __fmul_rn(f3, scale));
+
+// a factor split into two packed f16 terms (hi + lo): a two-instruction packed multiply then keeps
+// 22 significant bits of the factor
+__device__ __forceinline__ void split_f16x2(float v, uint32_t& hi2, uint32_t& lo2) {
+  const __half hi = __float2half_rn(v);
+  const __half2 h2 = __halves2half2(hi, hi);
+  const __half2 l2 = __float2half2_rn(v - __half2float(hi));
+  hi2 = *reinterpret_cast<const uint32_t*>(&h2);
+  lo2 = *reinterpret_cast<const uint32_t*>(&l2);
 }
-template <int QUANT, bool PRECISE>
-__device__ __forceinline__ void cvt_chunk(const uint4& raw, float scale, uint32_t s_hi, uint32_t s_lo, uint32_t* out) {
-  if (QUANT == EK_QUANT_BF16) {
-    out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
-  } else if (QUANT == EK_QUANT_FP8_BLOCK128) {
-    cvt_fp8_word<PRECISE>(raw.x, scale, s_hi, s_lo, out + 0);
-    cvt_fp8_word<PRECISE>(raw.y, scale, s_hi, s_lo, out + 2);
-    cvt_fp8_word<PRECISE>(raw.z, scale, s_hi, s_lo, out + 4);
-    cvt_fp8_word<PRECISE>(raw.w, scale, s_hi, s_lo, out + 6);
-  } else {
-    cvt_int8_word(raw.x, scale, out + 0);
-    cvt_int8_word(raw.y, scale, out + 2);
-    cvt_int8_word(raw.z, scale, out + 4);
-    cvt_int8_word(raw.w, scale, out + 6);
-  }
+// eight f16 activations times the split factor
+__device__ __forceinline__ uint4 scale_f16x8(const uint4& x, uint32_t hi2, uint32_t lo2) {
+  uint4 o;
+  o.x = fma_f16x2(x.x, hi2, mul_f16x2(x.x, lo2));
+  o.y = fma_f16x2(x.y, hi2, mul_f16x2(x.y, lo2));
+  o.z = fma_f16x2(x.z, hi2, mul_f16x2(x.z, lo2));
+  o.w = fma_f16x2(x.w, hi2, mul_f16x2(x.w, lo2));
+  return o;
 }
 
 __device__ __forceinline__ int pick_n(int rows, int nmax) {
@@ -199,20 +266,38 @@ __device__ __forceinline__ int pick_n(int rows, int nmax) {
 }
 __device__ __forceinline__ int map_index(int n) { return n == 16 ? 0 : n == 32 ? 1 : n == 64 ? 2 : 3; }
 
-template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
+// Instruction descriptor: D fp32, A and B both f16 or both bf16, both K-major, M = 128.
+__device__ __forceinline__ uint32_t idesc_for(uint32_t n, bool f16) {
+  return (1u << 4) | (f16 ? 0u : ((1u << 7) | (1u << 10))) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int W>
+__device__ __forceinline__ void tmem_ld_pair_wait(uint32_t ta, uint32_t tb, uint32_t* a, uint32_t* b) {
+  if constexpr (W == 32) tmem_ld32x2_wait(ta, tb, a, b);
+  else tmem_ld8x2_wait(ta, tb, a, b);
+}
+
+template <int QUANT, bool GATEUP, int NMAX, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
-  using C = Cfg<QUANT, GATEUP, NMAX>;
+  using C = Cfg<QUANT, GATEUP, NMAX, MODE>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_wfull[8], bar_wempty[8], bar_ready[8], bar_done[kMmaWarps][8];
+  __shared__ __align__(8) uint64_t bar_wfull[8], bar_wempty[8], bar_xfull[8], bar_ready[8], bar_done[kMmaWarps][8];
   __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
-#ifdef EK_TC_PROFILE
-  __shared__ long long s_issue[8];   // when the weight copy of each stage was issued
-#endif
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* const stage0_ptr = smem_raw + (stage0 - smem_u32(smem_raw));
   volatile int* abortp = &s_abort;
 
   if (tid == 0) {
@@ -220,9 +305,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(smem_u32(&bar_wfull[i]), 1);               // weight tiles of the stage have landed
       mbar_init(smem_u32(&bar_wempty[i]), kGroupWarps);    // the step's converter group has read the weight tiles
+      mbar_init(smem_u32(&bar_xfull[i]), 1);               // scale-on-B: the raw activation tile has landed
       // both A tiles of the step are in tensor memory (one arrival per converter warp) and the
-      // activation tile has landed (the producer's expect_tx arrival + the copy's bytes)
-      mbar_init(smem_u32(&bar_ready[i]), kGroupWarps + 1);
+      // activation tile is in place: landed (the producer's expect_tx arrival + the copy's bytes)
+      // or, scale-on-B, rewritten by those same converter warps
+      mbar_init(smem_u32(&bar_ready[i]), C::SCALE_B ? kGroupWarps : kGroupWarps + 1);
       for (int c = 0; c < kMmaWarps; ++c) mbar_init(smem_u32(&bar_done[c][i]), 1);   // chain c's MMAs of the step are complete
     }
     mbar_init(smem_u32(&bar_accfull), kMmaWarps);
@@ -243,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   pdl_wait();
   pdl_trigger();
   const int n_chunks = *p.n_chunks;
-  const int n_rt = GATEUP ? p.d.it : p.d.hp;   // work items per chunk
+  const int n_rt = GATEUP ? p.d.it : p.d.hp;       // work items per chunk
   const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;   // K tiles of the GEMM = pipeline stages per work item
   const int total = n_chunks * n_rt;
 
@@ -252,29 +339,29 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     // Two threads in two warps, two independent rings over the same stages: one refills the weight
     // tiles of a stage as soon as the converters have read them, the other the activation tile once
     // both MMA chains are done with the stage.  The weights (the long-latency HBM stream) thereby
-    // start their next trip a whole MMA phase earlier than the activations.  The activation copy
-    // signals the stage's `ready` barrier, the one the MMA threads wait on.
+    // start their next trip a whole MMA phase earlier than the activations.
     if (lane == 0) {
       const bool weights = warp == kConvWarps;
       const CUtensorMap* maps = GATEUP ? p.x_maps : p.h_maps;
       const uint64_t stream_once = policy_evict_first();   // weights read exactly once per pass
-      uint64_t* bar_full = weights ? bar_wfull : bar_ready;
+      uint64_t* bar_full = weights ? bar_wfull : (C::SCALE_B ? bar_xfull : bar_ready);
       uint32_t it = 0;
       bool ok = true;
-      PROF_DECL
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        ChunkDesc cd = p.chunks[item / n_rt];
+      Sched sched(total, KT, p.split_k);
+      Unit u;
+      while (ok && sched.next(u)) {
+        ChunkDesc cd = p.chunks[u.item / n_rt];
         // weights that the neighbouring items read again stay in L2; the rest is streamed through
         const bool reread = (cd.n_rows & kChunkMulti) != 0;
         cd.n_rows &= kChunkRowsMask;
-        const int rt = item % n_rt;
+        const int rt = u.item % n_rt;
         const int N = pick_n(cd.n_rows, NMAX);
         const CUtensorMap* map = maps + map_index(N);
         const uint8_t* wsrc =
             GATEUP ? p.w.gu_tiles + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * C::W_BYTES
                    : p.w.dn_tiles + ((size_t)cd.slot * p.d.hp + rt) * (size_t)p.d.kt_dn * C::W_BYTES;
         const int brow = GATEUP ? cd.in_row : cd.out_row;
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        for (int kt = u.kt0; kt < u.kt1; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
           // a fresh barrier passes a wait on parity 1: the first lap over the ring does not block
           bool free_ok;
@@ -285,34 +372,25 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
                       mbar_wait(smem_u32(&bar_done[1][s]), ph ^ 1u, abortp);
           }
           if (!free_ok) {
-            report(p.status, DEV_TIMEOUT, weights ? 100 : 101, item, kt);
+            report(p.status, DEV_TIMEOUT, weights ? 100 : 101, u.item, kt);
             ok = false;
             break;
           }
-          PROF_LAP(0)
           const uint32_t full = smem_u32(&bar_full[s]);
           const uint32_t dst = stage0 + s * C::STAGE_BYTES;
           if (weights) {
-#ifdef EK_TC_PROFILE
-            s_issue[s] = clock64();
-#endif
-            TRACE(it, 0)
             mbar_arrive_expect_tx(full, C::W_BYTES);
             // one 32 KiB bulk copy per stage (tiled TMA or smaller pieces measured no faster)
             if (reread) bulk_g2s(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full);
             else bulk_g2s_hint(dst, wsrc + (size_t)kt * C::W_BYTES, C::W_BYTES, full, stream_once);
-            TRACE(it, 1)
           } else {
-            TRACE(it, 19)
             mbar_arrive_expect_tx(full, C::X_ATOMS * N * 128);
 #pragma unroll
             for (int a = 0; a < C::X_ATOMS; ++a)
               tma_load_2d(dst + C::W_BYTES + a * N * 128, map, kt * C::TKE + a * 64, brow, full);
           }
-          PROF_LAP(1)
         }
       }
-      if (weights) { PROF_DUMP(0) }
       // never leave with copies in flight: wait (bounded) for every stage armed in the last lap
       const uint32_t lo = it > (uint32_t)C::STAGES ? it - C::STAGES : 0;
       for (uint32_t i = lo; i < it; ++i) {
@@ -323,56 +401,35 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         }
       }
     }
-#ifdef EK_TC_PROFILE
-  } else if (warp >= kFirstMmaWarp + kMmaWarps) {
-    if (lane == 0 && p.prof) {
-      uint32_t it = 0;
-      unsigned long long sum = 0, n = 0, mx = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        for (int kt = 0; kt < KT; ++kt, ++it) {
-          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, abortp)) { ok = false; break; }
-          const unsigned long long lat = (unsigned long long)(clock64() - s_issue[s]);
-          TRACE(it, 2)
-          sum += lat; ++n;
-          if (lat > mx) mx = lat;
-        }
-      }
-      atomicAdd((unsigned long long*)&p.prof[30], sum);
-      atomicAdd((unsigned long long*)&p.prof[31], n);
-      atomicMax((unsigned long long*)&p.prof[29], mx);
-    }
-#endif
   } else if (warp >= kFirstMmaWarp) {
     // =============================== MMA issuers ===========================================
-    // Two issuing threads in two warps ("chains"), each with its own accumulator: the instruction
-    // stream of one thread between MMAs (barrier waits, descriptors, commits) costs about as much
-    // time as the MMAs take, so a single issuer leaves the tensor pipe idle half of the time.  For
-    // the same reason each chain does one wait and one commit per K step and nothing else.
+    // Two issuing threads in two warps ("chains"), each with its own accumulator.  Each chain does
+    // one wait and one commit per K step and nothing else.
     //   gate/up : chain 0 issues the gate tile, chain 1 the up tile of every K step
     //   down    : chain c issues hidden-row tile 2*rp + c
     if (lane == 0) {
       const uint32_t chain = warp - kFirstMmaWarp;
-      uint32_t it = 0, items_done = 0, s = 0, ph = 0, ai = 0;
+      uint32_t it = 0, units_done = 0, s = 0, ph = 0, ai = 0;
       bool ok = true;
-      PROF_DECL
       const uint32_t d_tmem = tmem + chain * NMAX;
-      // descriptor of stage 0's activation tile; stages are a constant number of 16-byte units apart
-      const uint64_t b_base = umma_desc_sw128(stage0 + C::W_BYTES);
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
-        const ChunkDesc cd = p.chunks[item / n_rt];
+      // descriptor of stage 0's activation tile (this chain's copy); stages are a constant number of
+      // 16-byte units apart
+      const uint64_t b_base =
+          umma_desc_sw128(stage0 + C::W_BYTES + (C::SCALE_B ? chain * C::X_BYTES : 0));
+      Sched sched(total, KT, p.split_k);
+      Unit u;
+      while (ok && sched.next(u)) {
+        const ChunkDesc cd = p.chunks[u.item / n_rt];
         const int N = pick_n(cd.n_rows & kChunkRowsMask, NMAX);
-        const uint32_t idesc = umma_idesc_bf16(N);
+        const uint32_t idesc = idesc_for(N, C::F16);
         const uint32_t atom_step = (uint32_t)(N * 128) >> 4;   // descriptor units between 64-element K atoms
-        if (!mbar_wait(smem_u32(&bar_accempty), (items_done & 1u) ^ 1u, abortp)) {
-          report(p.status, DEV_TIMEOUT, 200, item, 0);
+        if (!mbar_wait(smem_u32(&bar_accempty), (units_done & 1u) ^ 1u, abortp)) {
+          report(p.status, DEV_TIMEOUT, 200, u.item, 0);
           ok = false;
           break;
         }
         tc_fence_after();
-        PROF_LAP(0)
-        for (int kt = 0; kt < KT; ++kt, ++it) {
+        for (int kt = u.kt0; kt < u.kt1; ++kt, ++it) {
           const uint32_t cs = s, cph = ph;
           if (++s == (uint32_t)C::STAGES) { s = 0; ph ^= 1u; }
           const uint32_t a_tmem = tmem + C::A_BASE + (ai * 2 + chain) * kASlotCols;
@@ -382,28 +439,20 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           uint64_t bd[C::MMAS];
 #pragma unroll
           for (int j = 0; j < C::MMAS; ++j) bd[j] = b0 + (uint64_t)((j / 4) * atom_step + (j % 4) * 2);
-          PROF_LAP(1)
-          if (chain == 0) { TRACE(it, 21) }
-          // both A tiles stored and the activation tile landed
+          // both A tiles stored and the activation tile in place
           if (!mbar_wait(smem_u32(&bar_ready[cs]), cph, abortp)) {
-            report(p.status, DEV_TIMEOUT, 201, item, kt);
+            report(p.status, DEV_TIMEOUT, 201, u.item, kt);
             ok = false;
             break;
           }
           tc_fence_after();
-          PROF_LAP(2)
-          TRACE(it, 12 + 4 * chain)
-          if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
-          else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > 0 ? 1u : 0u);
-          PROF_LAP(3)
-          TRACE(it, 13 + 4 * chain)
+          if (C::MMAS == 8) umma_ts_x8(d_tmem, a_tmem, bd, idesc, kt > u.kt0 ? 1u : 0u);
+          else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > u.kt0 ? 1u : 0u);
           tc_commit(smem_u32(&bar_done[chain][cs]));
-          PROF_LAP(4)
-          TRACE(it, 14 + 4 * chain)
         }
         if (ok) tc_commit(smem_u32(&bar_accfull));
+        ++units_done;
       }
-      if (chain == 0) { PROF_DUMP(1) }
       // drain: every MMA issued by this thread has completed before tensor memory is freed
       tc_commit(smem_u32(&bar_drain[chain]));
       for (uint32_t poll = 0; poll < (1u << 20); ++poll) {
@@ -413,68 +462,92 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     }
   } else {
     // =============================== converters + epilogue =================================
-    // warp -> (tile of the stage, K part of the tile row, lane quarter of tensor memory)
+    // warp -> (group, tile of the stage, lane quarter of tensor memory)
     const int grp = warp / kGroupWarps, wg = (warp % kGroupWarps) >> 2, q = warp & 3;
     const int r = q * 32 + lane;
+    const int gt = (warp % kGroupWarps) * 32 + lane;     // thread index inside the group (activation rescale)
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
-    uint32_t it_base = 0, items_done = 0;
+    uint32_t it_base = 0, units_done = 0;
     bool ok = true;
-    PROF_DECL
-    for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++items_done) {
-      ChunkDesc cd = p.chunks[item / n_rt];
+    Sched sched(total, KT, p.split_k);
+    Unit u;
+    while (ok && sched.next(u)) {
+      ChunkDesc cd = p.chunks[u.item / n_rt];
       cd.n_rows &= kChunkRowsMask;
-      const int rt = item % n_rt;
+      const int rt = u.item % n_rt;
       const int N = pick_n(cd.n_rows, NMAX);
-      // block scale of this warpgroup's tile: [K step][warpgroup] in both modes
-      const float* sc = nullptr;
+      // block scales of the two tiles of a stage: [K step][tile] in both GEMMs
+      const float2* sc2 = nullptr;
       if (QUANT != EK_QUANT_BF16) {
-        sc = GATEUP ? p.w.gu_scale + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * 2 + wg
-                    : p.w.dn_scale + ((size_t)cd.slot * p.d.hp + rt) * (size_t)p.d.kt_dn * 2 + wg;
+        sc2 = reinterpret_cast<const float2*>(
+            GATEUP ? p.w.gu_scale + ((size_t)cd.slot * p.d.it + rt) * (size_t)p.d.kt_gu * 2
+                   : p.w.dn_scale + ((size_t)cd.slot * p.d.hp + rt) * (size_t)p.d.kt_dn * 2);
       }
-      float scale_next = 1.f;
-      if (QUANT != EK_QUANT_BF16 && grp < KT) scale_next = __ldg(sc + (size_t)grp * 2);
-      const uint32_t it0 = it_base;   // global index of the item's first K step (the same in every role)
-      for (int kt = grp; kt < KT; kt += kGroups) {
-        const uint32_t it = it0 + kt;
-        const float scale = scale_next;
-        if (QUANT != EK_QUANT_BF16 && kt + kGroups < KT) scale_next = __ldg(sc + (size_t)(kt + kGroups) * 2);
+      // power of two that keeps the scaled operand in the middle of the f16 range (scale-on-B: the
+      // largest block scale times 2^c lies in [2^-5, 2^-4); scale-on-A: 2^9 higher, since the weight
+      // codes reach 448); the epilogue takes it out again
+      float op_pow = 1.f, out_pow = 1.f;
+      if (C::F16) {
+        op_pow = __ldg((GATEUP ? p.w.gu_pow : p.w.dn_pow) + cd.slot) * (MODE == kModeScaleAH ? 512.f : 1.f);
+        out_pow = 1.f / op_pow;                  // exact: a power of two
+      }
+      // this group's steps of the unit: those whose ring index is congruent to the group
+      const uint32_t it0 = it_base;
+      int kt = u.kt0 + (int)((grp + kGroups - it0 % kGroups) % kGroups);
+      float2 scale_next = make_float2(1.f, 1.f);
+      if (QUANT != EK_QUANT_BF16 && kt < u.kt1) scale_next = __ldg(sc2 + kt);
+      for (; kt < u.kt1; kt += kGroups) {
+        const uint32_t it = it0 + (uint32_t)(kt - u.kt0);
+        const float2 scale = scale_next;
+        if (QUANT != EK_QUANT_BF16 && kt + kGroups < u.kt1) scale_next = __ldg(sc2 + kt + kGroups);
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
-        if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, abortp)) {
-          report(p.status, DEV_TIMEOUT, 300, item, kt);
-          ok = false;
-          break;
-        }
-        PROF_LAP(0)
-        if (q == 0 && lane == 0) { TRACE(it, 3 + 4 * wg) }
-        // A slot of this step: free once this warpgroup's chain has completed step it - A_PER
+        // A slot of this step: free once this warpgroup's chain has completed step it - A_PER.
+        // This wait comes FIRST.  A group sees a stage only on every other lap when the stage count
+        // is odd, and a parity wait cannot tell "lap L has completed" from "lap L-2 has completed":
+        // it is exact only if lap L-1 is known to be over.  MMA completion of step it - A_PER (in
+        // order, so of every earlier step too) says exactly that for the stage's weight and
+        // activation barriers, because A_PER <= STAGES.  Waiting for the weights first let a fast
+        // converter pass on the stale lap, release the stage a lap early and make the producer arm
+        // a barrier whose previous transaction was still pending - an mbarrier fault.
         const uint32_t a = (it % C::A_PER) * 2 + wg;
         if (it >= (uint32_t)C::A_PER) {
           const uint32_t j = it - C::A_PER;
           if (!mbar_wait(smem_u32(&bar_done[wg][j % C::STAGES]), (j / C::STAGES) & 1u, abortp)) {
-            report(p.status, DEV_TIMEOUT, 301, item, kt);
+            report(p.status, DEV_TIMEOUT, 301, u.item, kt);
             ok = false;
             break;
           }
         }
-        PROF_LAP(1)
-        if (q == 0 && lane == 0) { TRACE(it, 4 + 4 * wg) }
-        const uint8_t* tile = smem_raw + (stage0 - smem_u32(smem_raw)) + s * C::STAGE_BYTES + wg * kTileBytes;
+        if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, abortp)) {
+          report(p.status, DEV_TIMEOUT, 300, u.item, kt);
+          ok = false;
+          break;
+        }
+        uint8_t* const stage_ptr = stage0_ptr + (size_t)s * C::STAGE_BYTES;
+        const uint8_t* tile = stage_ptr + wg * kTileBytes;
         uint4 raw[C::NCH];
 #pragma unroll
         for (int j = 0; j < C::NCH; ++j)
           raw[j] = *reinterpret_cast<const uint4*>(tile + (size_t)(j * kTileRows + r) * 16);
+        // how this tile's block scale is applied (see the file header)
+        const float my_scale = wg == 0 ? scale.x : scale.y;
+        uint32_t a_hi = 0, a_lo = 0;
+        if (MODE == kModeScaleAH) split_f16x2(my_scale * op_pow, a_hi, a_lo);
         uint32_t aw[C::NW];
-        uint32_t s_hi = 0, s_lo = 0;
-        if (QUANT == EK_QUANT_FP8_BLOCK128 && !PRECISE) {
-          const float sk = scale * 0x1p120f;
-          const __nv_bfloat16 hi = __float2bfloat16_rn(sk);
-          const __nv_bfloat162 h2 = __halves2bfloat162(hi, hi);
-          const __nv_bfloat162 l2 = __float2bfloat162_rn(sk - __bfloat162float(hi));
-          s_hi = *reinterpret_cast<const uint32_t*>(&h2);
-          s_lo = *reinterpret_cast<const uint32_t*>(&l2);
-        }
+        if (MODE == kModeRaw) {
 #pragma unroll
-        for (int j = 0; j < C::NCH; ++j) cvt_chunk<QUANT, PRECISE>(raw[j], scale, s_hi, s_lo, aw + j * C::WPC);
+          for (int j = 0; j < C::NCH; ++j) {
+            aw[4 * j] = raw[j].x; aw[4 * j + 1] = raw[j].y; aw[4 * j + 2] = raw[j].z; aw[4 * j + 3] = raw[j].w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < C::NCH; ++j) {
+            cvt_word<QUANT, MODE>(raw[j].x, my_scale, a_hi, a_lo, aw + (j * 8 + 0) % C::NW);
+            cvt_word<QUANT, MODE>(raw[j].y, my_scale, a_hi, a_lo, aw + (j * 8 + 2) % C::NW);
+            cvt_word<QUANT, MODE>(raw[j].z, my_scale, a_hi, a_lo, aw + (j * 8 + 4) % C::NW);
+            cvt_word<QUANT, MODE>(raw[j].w, my_scale, a_hi, a_lo, aw + (j * 8 + 6) % C::NW);
+          }
+        }
         const uint32_t col0 = C::A_BASE + a * kASlotCols;
         tc_fence_after();
         if (C::NW >= 32) {
@@ -483,28 +556,73 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         } else {
           tmem_st16(lane_base + col0, aw);
         }
-        PROF_LAP(2)
-        if (q == 0 && lane == 0) { TRACE(it, 5 + 4 * wg) }
+        if (C::SCALE_B) {
+          // the weights are in registers / on their way to tensor memory: the producer may refill
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_wempty[s]));
+          // rewrite the activation tile of the step as bf16(x * block scale) while the stores fly
+          if (!mbar_wait(smem_u32(&bar_xfull[s]), ph, abortp)) {
+            report(p.status, DEV_TIMEOUT, 303, u.item, kt);
+            ok = false;
+            break;
+          }
+          uint32_t h0, l0, h1, l1;
+          split_f16x2(scale.x * op_pow, h0, l0);
+          split_f16x2(scale.y * op_pow, h1, l1);
+          uint4* xt = reinterpret_cast<uint4*>(stage_ptr + C::W_BYTES);
+          const int nvec = N * C::X_ATOMS * 8;           // 16-byte vectors of the [N, TKE] tile
+          for (int v = gt; v < nvec; v += kGroupWarps * 32) {
+            const uint4 x = xt[v];
+            xt[v] = scale_f16x8(x, h0, l0);
+            xt[v + C::X_BYTES / 16] = scale_f16x8(x, h1, l1);
+          }
+          fence_proxy_async();                           // generic-proxy writes -> tensor-core reads
+        }
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(smem_u32(&bar_ready[s]));
-          mbar_arrive(smem_u32(&bar_wempty[s]));
+          if (!C::SCALE_B) mbar_arrive(smem_u32(&bar_wempty[s]));
         }
-        PROF_LAP(3)
-        if (q == 0 && lane == 0) { TRACE(it, 6 + 4 * wg) }
       }
-      it_base += (uint32_t)KT;
+      it_base += (uint32_t)(u.kt1 - u.kt0);
       if (!ok) break;
       // ---- epilogue ----
-      if (!mbar_wait(smem_u32(&bar_accfull), items_done & 1u, abortp)) {
-        report(p.status, DEV_TIMEOUT, 302, item, 0);
+      if (!mbar_wait(smem_u32(&bar_accfull), units_done & 1u, abortp)) {
+        report(p.status, DEV_TIMEOUT, 302, u.item, 0);
         ok = false;
         break;
       }
       tc_fence_after();
-      PROF_LAP(4)
+      // a split item: parts that do not start at K step 0 leave their accumulators in the scratch
+      // buffer; the part that does adds them, in part order, before the epilogue proper
+      const bool part_write = u.kt0 > 0;
+      const int n_follow = (u.kt0 == 0 && u.kt1 < KT) ? sched.followers(u) : 0;
+      float* const sk_mine = p.sk_buf + (size_t)blockIdx.x * (2 * NMAX * 128);
+      if (n_follow > 0) {
+        int got = 1;
+        if (lane == 0) {
+          for (int j = 1; j <= n_follow && got; ++j) {
+            const uint32_t* f = p.sk_flags + ((size_t)blockIdx.x + j) * 32 + warp;
+            got = 0;
+            for (uint32_t poll = 0; poll < (1u << 21); ++poll) {
+              if (ld_acquire_gpu(f) != 0u) { got = 1; break; }
+              if (poll > 64) __nanosleep(100);
+              if ((poll & 1023u) == 1023u && *abortp) break;
+            }
+          }
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          if (lane == 0) {
+            report(p.status, DEV_TIMEOUT, 304, u.item, u.kt1);
+            *abortp = 1;
+          }
+          ok = false;
+          break;
+        }
+      }
       // gate/up: this thread owns intermediate feature rt*128 + r (gate in accumulator 0, up in 1);
       // down: hidden features (2*rt)*128 + r (accumulator 0) and (2*rt+1)*128 + r (accumulator 1)
       const int feat = (GATEUP ? rt : 2 * rt) * kTileRows + r;
@@ -513,52 +631,76 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       __nv_bfloat16* obase = (GATEUP ? p.hbuf : p.obuf) + (size_t)cd.out_row * ostride + feat;
       const bool f0 = GATEUP || feat < p.d.H, f1 = !GATEUP && feat + kTileRows < p.d.H;
       auto emit = [&](__nv_bfloat16* o, float gv, float uv) {
+        if (C::F16) {
+          gv *= out_pow;
+          uv *= out_pow;
+        }
         if (GATEUP) {
-          *o = __float2bfloat16_rn(uv * __fdividef(gv, 1.f + __expf(-gv)));
+          const float h = uv * __fdividef(gv, 1.f + __expf(-gv));
+          if (C::F16) {   // the down GEMM of these modes takes f16 activations
+            const __half hh = __float2half_rn(fminf(fmaxf(h, -65504.f), 65504.f));
+            *reinterpret_cast<__half*>(o) = hh;
+          } else {
+            *o = __float2bfloat16_rn(h);
+          }
         } else {
           if (f0) *o = __float2bfloat16_rn(gv);
           if (f1) o[kTileRows] = __float2bfloat16_rn(uv);
         }
       };
-      if (NMAX >= 64 && N >= 64) {
-        // wide tiles: 32 columns of both accumulators per tensor-memory round trip
-        for (int cb = warp >> 2; cb < N / 32; cb += kConvWarps / 4) {
-          const int c0 = cb * 32;
+      auto columns = [&](auto wtag) {
+        constexpr int W = decltype(wtag)::value;
+        for (int cb = warp >> 2; cb < N / W; cb += kConvWarps / 4) {
+          const int c0 = cb * W;
           if (c0 >= cd.n_rows) break;
-          uint32_t g[32], u[32];
-          tmem_ld32(lane_base + c0, g);
-          tmem_ld32(lane_base + NMAX + c0, u);
-          tc_wait_ld();
-          __nv_bfloat16* o = obase + (size_t)c0 * ostride;
-          if (c0 + 32 <= cd.n_rows) {
+          uint32_t g[W], uu[W];
+          tmem_ld_pair_wait<W>(lane_base + c0, lane_base + NMAX + c0, g, uu);
+          if (part_write) {
+            float* d = sk_mine + (size_t)c0 * 128 + r;
 #pragma unroll
-            for (int i = 0; i < 32; ++i, o += ostride) emit(o, __uint_as_float(g[i]), __uint_as_float(u[i]));
+            for (int i = 0; i < W; ++i)
+              if (c0 + i < cd.n_rows) {
+                d[(size_t)i * 128] = __uint_as_float(g[i]);
+                d[(size_t)(NMAX + i) * 128] = __uint_as_float(uu[i]);
+              }
+            continue;
+          }
+          for (int j = 1; j <= n_follow; ++j) {
+            const float* sp = p.sk_buf + ((size_t)blockIdx.x + j) * (2 * NMAX * 128) + (size_t)c0 * 128 + r;
+#pragma unroll
+            for (int i = 0; i < W; ++i)
+              if (c0 + i < cd.n_rows) {
+                g[i] = __float_as_uint(__uint_as_float(g[i]) + __ldcg(sp + (size_t)i * 128));
+                uu[i] = __float_as_uint(__uint_as_float(uu[i]) + __ldcg(sp + (size_t)(NMAX + i) * 128));
+              }
+          }
+          __nv_bfloat16* o = obase + (size_t)c0 * ostride;
+          if (c0 + W <= cd.n_rows) {
+#pragma unroll
+            for (int i = 0; i < W; ++i, o += ostride) emit(o, __uint_as_float(g[i]), __uint_as_float(uu[i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i, o += ostride)
-              if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(u[i]));
+            for (int i = 0; i < W; ++i, o += ostride)
+              if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(uu[i]));
           }
         }
-      } else {
-        for (int cb = warp >> 2; cb < N / 8; cb += kConvWarps / 4) {
-          const int c0 = cb * 8;
-          if (c0 >= cd.n_rows) break;
-          uint32_t g[8], u[8];
-          tmem_ld8(lane_base + c0, g);
-          tmem_ld8(lane_base + NMAX + c0, u);
-          tc_wait_ld();
-          __nv_bfloat16* o = obase + (size_t)c0 * ostride;
-#pragma unroll
-          for (int i = 0; i < 8; ++i, o += ostride)
-            if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(u[i]));
-        }
+      };
+      if (NMAX >= 64 && N >= 64) columns(std::integral_constant<int, 32>());   // 32 columns per tensor-memory round trip
+      else columns(std::integral_constant<int, 8>());
+      if (part_write) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(p.sk_flags + (size_t)blockIdx.x * 32 + warp, 1u);
+      } else if (n_follow > 0) {
+        __syncwarp();
+        if (lane == 0)
+          for (int j = 1; j <= n_follow; ++j) p.sk_flags[((size_t)blockIdx.x + j) * 32 + warp] = 0u;   // consumed
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_accempty));
-      PROF_LAP(5)
+      ++units_done;
     }
-    if (lane == 0 && (warp == 0 || warp == 4)) { PROF_DUMP(2 + wg) }
   }
 
   tc_fence_before();
@@ -569,33 +711,39 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   }
 }
 
-template <int QUANT, bool GATEUP, int NMAX, bool PRECISE>
+template <int QUANT, bool GATEUP, int NMAX, int MODE>
 int launch_one(const FfnParams& p, cudaStream_t s) {
-  using C = Cfg<QUANT, GATEUP, NMAX>;
+  using C = Cfg<QUANT, GATEUP, NMAX, MODE>;
   const int smem = C::STAGES * C::STAGE_BYTES + 1024;
-  cudaFuncSetAttribute(ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  launch_pdl(ffn_tc_kernel<QUANT, GATEUP, NMAX, PRECISE>, dim3(p.n_sm), dim3(kThreads), (size_t)smem, s, p);
+  cudaFuncSetAttribute(ffn_tc_kernel<QUANT, GATEUP, NMAX, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  launch_pdl(ffn_tc_kernel<QUANT, GATEUP, NMAX, MODE>, dim3(p.n_sm), dim3(kThreads), (size_t)smem, s, p);
   return 1;
 }
 
-template <int QUANT, bool PRECISE>
+template <int QUANT, int MODE_DECODE, int MODE_PREFILL>
 int launch_quant(const FfnParams& p, int nmax, int which, cudaStream_t s) {
   if (nmax <= 32)
-    return which == 0 ? launch_one<QUANT, true, 32, PRECISE>(p, s) : launch_one<QUANT, false, 32, PRECISE>(p, s);
+    return which == 0 ? launch_one<QUANT, true, 32, MODE_DECODE>(p, s) : launch_one<QUANT, false, 32, MODE_DECODE>(p, s);
   if (nmax <= 64)
-    return which == 0 ? launch_one<QUANT, true, 64, PRECISE>(p, s) : launch_one<QUANT, false, 64, PRECISE>(p, s);
-  return which == 0 ? launch_one<QUANT, true, 128, PRECISE>(p, s) : launch_one<QUANT, false, 128, PRECISE>(p, s);
+    return which == 0 ? launch_one<QUANT, true, 64, MODE_DECODE>(p, s) : launch_one<QUANT, false, 64, MODE_DECODE>(p, s);
+  return which == 0 ? launch_one<QUANT, true, 128, MODE_PREFILL>(p, s) : launch_one<QUANT, false, 128, MODE_PREFILL>(p, s);
 }
 
 }  // namespace
 
+size_t ffn_tc_scratch_floats(int n_sm) { return (size_t)n_sm * 2 * 128 * 128; }
+
+bool ffn_tc_f16_activations(int quant, int precise) { return quant != EK_QUANT_BF16 && !precise; }
+
 int launch_ffn_tc(const FfnParams& p, int nmax, int which, cudaStream_t s) {
   switch (p.d.quant) {
-    case EK_QUANT_BF16: return launch_quant<EK_QUANT_BF16, true>(p, nmax, which, s);
+    case EK_QUANT_BF16: return launch_quant<EK_QUANT_BF16, kModeRaw, kModeRaw>(p, nmax, which, s);
     case EK_QUANT_FP8_BLOCK128:
-      return p.precise ? launch_quant<EK_QUANT_FP8_BLOCK128, true>(p, nmax, which, s)
-                       : launch_quant<EK_QUANT_FP8_BLOCK128, false>(p, nmax, which, s);
-    default: return launch_quant<EK_QUANT_INT8_BLOCK128, true>(p, nmax, which, s);
+      return p.precise ? launch_quant<EK_QUANT_FP8_BLOCK128, kModeScaleA, kModeScaleA>(p, nmax, which, s)
+                       : launch_quant<EK_QUANT_FP8_BLOCK128, kModeScaleB2, kModeScaleAH>(p, nmax, which, s);
+    default:
+      return p.precise ? launch_quant<EK_QUANT_INT8_BLOCK128, kModeScaleA, kModeScaleA>(p, nmax, which, s)
+                       : launch_quant<EK_QUANT_INT8_BLOCK128, kModeScaleB2, kModeScaleAH>(p, nmax, which, s);
   }
 }
 

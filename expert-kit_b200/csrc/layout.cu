@@ -10,23 +10,6 @@ namespace ek {
 
 namespace {
 
-// Pair interleave of fp8 e4m3 bytes (decoded in ffn_tc.cu / ffn_simt.cu): for K-consecutive
-// weights a, b store
-//   p = (a & 0x80) | ((a >> 4) & 0x07) | ((b & 0x0F) << 3)
-//   q = (b & 0x80) | ((b >> 4) & 0x07) | ((a & 0x0F) << 3)
-// a lossless re-arrangement of the same 16 bits.
-__device__ __forceinline__ uint32_t interleave_word(uint32_t w) {
-  uint32_t out = 0;
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t a = (w >> (16 * h)) & 0xFF, b = (w >> (16 * h + 8)) & 0xFF;
-    const uint32_t p = (a & 0x80) | ((a >> 4) & 0x07) | ((b & 0x0F) << 3);
-    const uint32_t q = (b & 0x80) | ((b >> 4) & 0x07) | ((a & 0x0F) << 3);
-    out |= (p | (q << 8)) << (16 * h);
-  }
-  return out;
-}
-
 // One CTA per tile; thread handles 4 of the tile's 1024 16-byte chunks.
 __global__ void __launch_bounds__(256) retile_kernel(RetileParams p) {
   const int rt = blockIdx.y, kt = blockIdx.x;
@@ -53,12 +36,6 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileParams p) {
         v = *reinterpret_cast<uint4*>(tmp);
       }
     }
-    if (p.pair_interleave) {
-      v.x = interleave_word(v.x);
-      v.y = interleave_word(v.y);
-      v.z = interleave_word(v.z);
-      v.w = interleave_word(v.w);
-    }
     *reinterpret_cast<uint4*>(tile + (size_t)(j * kTileRows + r) * 16) = v;
   }
 }
@@ -72,6 +49,31 @@ __global__ void scale_retile_kernel(ScaleRetileParams p) {
   if (sr < p.src_rows && scol < p.src_cols) v = p.src[(size_t)sr * p.src_cols + scol];
   if (p.rt_pairs) p.dst[((size_t)(rt >> 1) * p.n_kt + kt) * 2 + (rt & 1)] = v;
   else p.dst[(size_t)i * p.stride + p.lane] = v;
+}
+
+// out[0] = 2^c with max|scale| * 2^c in (2^-5, 2^-4]: the power of two that keeps the scaled
+// activation operand of the GEMM (x * block scale * 2^c) in the middle of the f16 range.
+__global__ void __launch_bounds__(256) scale_pow_kernel(const float* a, int64_t na, const float* b, int64_t nb, float* out) {
+  __shared__ float s_max[256];
+  float m = 0.f;
+  for (int64_t i = threadIdx.x; i < na; i += 256) m = fmaxf(m, fabsf(a[i]));
+  for (int64_t i = threadIdx.x; i < nb; i += 256) m = fmaxf(m, fabsf(b[i]));
+  s_max[threadIdx.x] = m;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) s_max[threadIdx.x] = fmaxf(s_max[threadIdx.x], s_max[threadIdx.x + o]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float mx = s_max[0];
+    float pw = 1.f;
+    if (mx > 0.f && isfinite(mx)) {
+      int e;
+      frexpf(mx, &e);                 // mx = f * 2^e, f in [0.5, 1)
+      pw = ldexpf(1.f, -e - 4);       // mx * pw in [2^-5, 2^-4)
+    }
+    out[0] = pw;
+  }
 }
 
 __global__ void fill_f32_kernel(float* dst, float v, int64_t n) {
@@ -113,6 +115,10 @@ int launch_retile(const RetileParams& p, cudaStream_t s) {
 int launch_scale_retile(const ScaleRetileParams& p, cudaStream_t s) {
   const int n = p.n_rt * p.n_kt;
   scale_retile_kernel<<<(n + 255) / 256, 256, 0, s>>>(p);
+  return 1;
+}
+int launch_scale_pow(const float* a, int64_t na, const float* b, int64_t nb, float* out, cudaStream_t s) {
+  scale_pow_kernel<<<1, 256, 0, s>>>(a, na, b, nb, out);
   return 1;
 }
 int launch_fill_f32(float* dst, float v, int64_t n, cudaStream_t s) {

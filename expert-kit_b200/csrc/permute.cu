@@ -23,11 +23,17 @@ __global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
   __shared__ int s_base;
   const int e = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool local = e >= p.e_lo && e < p.e_hi;
+  // experts this rank serves in this pass: its window, or whatever the owner table says
+  auto is_local = [&](int j) { return p.owners ? p.owners[j] == p.rank : (j >= p.e_lo && j < p.e_hi); };
+  const bool local = is_local(e);
 
-  // exclusive prefix over the local window
+  // exclusive prefix over the local experts below e
   int part = 0;
-  for (int j = p.e_lo + tid; j < min(e, p.e_hi); j += 256) part += p.counts[j];
+  if (p.owners) {
+    for (int j = tid; j < e; j += 256) part += is_local(j) ? p.counts[j] : 0;
+  } else {
+    for (int j = p.e_lo + tid; j < min(e, p.e_hi); j += 256) part += p.counts[j];
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
   if (lane == 0) s_red[warp] = part;
@@ -98,17 +104,21 @@ __global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
   const int n_local = p.e_hi - p.e_lo;
   if (p.counts_copy)
     for (int e = tid; e < p.E; e += 1024) p.counts_copy[e] = p.counts[e];
+  // experts this rank serves: its window (slot = e - e_lo), or, with an owner table, every expert
+  // the table gives to this rank (slot from the layer's slot table: own experts and replicas)
+  const int first = p.owners ? 0 : p.e_lo, last = p.owners ? p.E : p.e_hi;
   int running = 0;
-  for (int e0 = 0; e0 < n_local; e0 += 1024) {
-    const int le = e0 + tid;
-    int cnt = 0, nch = 0;
-    if (le < n_local) {
-      cnt = p.counts[p.e_lo + le];
+  for (int e0 = first; e0 < last; e0 += 1024) {
+    const int e = e0 + tid;
+    int cnt = 0, nch = 0, slot = -1;
+    if (e < last && (!p.owners || p.owners[e] == p.rank)) {
+      cnt = p.counts[e];
+      slot = p.slot_of ? p.slot_of[e] : e - p.e_lo;
       nch = (cnt + p.chunk_rows - 1) / p.chunk_rows;
-      if (cnt > 0 && !p.registered[le]) {
+      if (cnt > 0 && (slot < 0 || !p.registered[slot])) {
         if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
           p.status->where = 2;
-          p.status->aux0 = p.e_lo + le;
+          p.status->aux0 = e;
         }
         nch = 0;
       }
@@ -121,18 +131,18 @@ __global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
       s_scan[tid] += v;
       __syncthreads();
     }
-    int first = running + s_scan[tid] - nch;
+    int first_chunk = running + s_scan[tid] - nch;
     if (tid == 1023) s_total = s_scan[tid];
-    if (le < n_local && nch > 0) {
-      const int off = p.offsets[p.e_lo + le];
+    if (nch > 0) {
+      const int off = p.offsets[e];
       for (int c = 0; c < nch; ++c) {
-        if (first + c >= p.max_chunks) break;
+        if (first_chunk + c >= p.max_chunks) break;
         ChunkDesc d;
-        d.slot = le;
+        d.slot = slot;
         d.in_row = off + c * p.chunk_rows;
         d.out_row = d.in_row;
         d.n_rows = min(p.chunk_rows, cnt - c * p.chunk_rows) | (nch > 1 ? kChunkMulti : 0);
-        p.chunks[first + c] = d;
+        p.chunks[first_chunk + c] = d;
       }
     }
     __syncthreads();
@@ -173,8 +183,20 @@ __global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
   }
 }
 
+// eight bf16 -> eight f16 (round to nearest, saturating at +-65504)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(v & 0xFFFF0000u)), "f"(__uint_as_float(v << 16)));
+  return r;
+}
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
+  v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y); v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
+  return v;
+}
+
 // xp[r,:] = x[perm[r] / k, :] for permuted rows, then (optionally) a straight copy of x for
-// the shared expert.  16-byte vectors.
+// the shared expert.  16-byte vectors; F16: the rows are written as f16.
+template <bool F16>
 __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __restrict__ x,
                                                      const int32_t* __restrict__ perm,
                                                      const int32_t* __restrict__ n_routed,
@@ -193,7 +215,12 @@ __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __rest
   }
   const uint4* s = reinterpret_cast<const uint4*>(x + (size_t)src * H);
   uint4* d = reinterpret_cast<uint4*>(xp + (size_t)r * H);
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = s[v];
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = F16 ? bf16x8_to_f16x8(s[v]) : s[v];
+}
+
+__global__ void __launch_bounds__(128) rows_to_f16_kernel(__nv_bfloat16* rows, int32_t H) {
+  uint4* d = reinterpret_cast<uint4*>(rows + (size_t)blockIdx.x * H);
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = bf16x8_to_f16x8(d[v]);
 }
 
 }  // namespace
@@ -210,10 +237,18 @@ int launch_worklist(const WorklistParams& p, cudaStream_t s) {
 
 int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_routed,
                   __nv_bfloat16* xp, int32_t T, int32_t k, int32_t H, int32_t shared_t0, int32_t shared_T,
-                  cudaStream_t s) {
+                  bool to_f16, cudaStream_t s) {
   const int rows = T * k + shared_T;
-  if (rows > 0) launch_pdl(gather_kernel, dim3(rows), dim3(128), 0, s, x, perm, n_routed, xp, T, k, H, shared_t0);
+  if (rows > 0) {
+    if (to_f16) launch_pdl(gather_kernel<true>, dim3(rows), dim3(128), 0, s, x, perm, n_routed, xp, T, k, H, shared_t0);
+    else launch_pdl(gather_kernel<false>, dim3(rows), dim3(128), 0, s, x, perm, n_routed, xp, T, k, H, shared_t0);
+  }
   return rows > 0 ? 1 : 0;
+}
+
+int launch_rows_to_f16(__nv_bfloat16* rows, int64_t n_rows, int32_t H, cudaStream_t s) {
+  if (n_rows > 0) rows_to_f16_kernel<<<(unsigned)n_rows, 128, 0, s>>>(rows, H);
+  return n_rows > 0 ? 1 : 0;
 }
 
 }  // namespace ek

@@ -104,8 +104,7 @@ __global__ void __launch_bounds__(192, 1) router_tc_kernel(const __grid_constant
         float* dst = p.partial + ((size_t)blockIdx.y * p.T + t) * p.E;
         for (int c = 0; c < p.E; c += 16) {
           uint32_t v[16];
-          tmem_ld16(lane_base + c, v);
-          tc_wait_ld();
+          tmem_ld16_wait(lane_base + c, v);
           if (t < p.T) {
 #pragma unroll
             for (int j = 0; j < 16; j += 4)

@@ -19,7 +19,7 @@ STATUS_NAMES = {
 EK_BF16, EK_F32, EK_F8_E4M3, EK_I8, EK_I32, EK_F16, EK_U8, EK_I64 = range(8)
 EK_SCORE_SOFTMAX, EK_SCORE_SIGMOID = 0, 1
 EK_QUANT_BF16, EK_QUANT_FP8_BLOCK128, EK_QUANT_INT8_BLOCK128 = 0, 1, 2
-EK_TILE_LAYOUT_VERSION = 3   # include/ek_b200.h
+EK_TILE_LAYOUT_VERSION = 4   # include/ek_b200.h
 EK_EP_MAX_RANKS = 16
 
 
@@ -39,7 +39,8 @@ class Config(C.Structure):
                 ("topk_group", C.c_int32), ("norm_topk_prob", C.c_int32), ("routed_scaling", C.c_float),
                 ("n_shared_experts", C.c_int32), ("bf16_combine", C.c_int32), ("quant", C.c_int32),
                 ("max_tokens", C.c_int32), ("max_layers", C.c_int32), ("device", C.c_int32),
-                ("ep_rank", C.c_int32), ("ep_size", C.c_int32), ("model_name", C.c_char * 64)]
+                ("ep_rank", C.c_int32), ("ep_size", C.c_int32), ("replica_slots", C.c_int32),
+                ("model_name", C.c_char * 64)]
 
 
 class RouteDebug(C.Structure):
@@ -94,6 +95,7 @@ SIGNATURES = {
     "ek_ep_route": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "ek_ep_ffn": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "ek_ep_combine": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
+    "ek_ep_set_owners": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p]),
     "ek_ep_partial": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "ek_ep_finish": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "ek_bucket_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,

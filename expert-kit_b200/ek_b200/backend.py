@@ -47,11 +47,13 @@ class BackendConfig:
     ep_rank: int = 0
     ep_size: int = 1
     model_name: str = "model"
+    replica_slots: int = 0
 
     def to_c(self) -> L.Config:
         c = L.Config()
         for f in ("hidden", "intermediate", "n_experts", "top_k", "scoring", "n_group", "topk_group",
-                  "n_shared_experts", "quant", "max_tokens", "max_layers", "device", "ep_rank", "ep_size"):
+                  "n_shared_experts", "quant", "max_tokens", "max_layers", "device", "ep_rank", "ep_size",
+                  "replica_slots"):
             setattr(c, f, int(getattr(self, f)))
         c.norm_topk_prob = int(bool(self.norm_topk_prob))
         c.bf16_combine = int(bool(self.bf16_combine))
@@ -66,6 +68,13 @@ _TORCH_TO_EK = {
 }
 if hasattr(torch, "float8_e4m3fn"):
     _TORCH_TO_EK[torch.float8_e4m3fn] = L.EK_F8_E4M3
+
+
+def _tensors_ready(tensors):
+    """Registration reads device tensors on the library's own stream, which does not wait for
+    torch's: whatever produced them on torch's current stream must have finished first."""
+    for dev in {t.device for t in tensors if t is not None and t.is_cuda}:
+        torch.cuda.current_stream(dev).synchronize()
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -119,6 +128,7 @@ class Backend:
         """ExpertDB::insert(ExpertBackend::build(...)).  `tensors` maps the names the weight
         server uses to contiguous tensors (CPU or CUDA)."""
         keep = []
+        _tensors_ready(tensors.values())
         views = (L.TensorView * len(tensors))()
         for i, (name, t) in enumerate(tensors.items()):
             t = t.contiguous()
@@ -186,6 +196,7 @@ class Backend:
             raise EKError(3, "router weight must be bf16 or fp32")
         if bias is not None:
             bias = bias.to(torch.float32).contiguous()
+        _tensors_ready((weight, bias))
         self._check(self._lib.ek_router_register(self._h, layer, _ptr(weight), _TORCH_TO_EK[weight.dtype],
                                                  _ptr(bias)))
 
@@ -267,6 +278,15 @@ class Backend:
         assert x_all.dtype == torch.bfloat16 and x_all.is_contiguous() and partial.is_contiguous()
         self._check(self._lib.ek_ep_partial(self._h, layer, _ptr(x_all), x_all.shape[0], t0, T_local, _ptr(partial)))
 
+    def set_owners(self, layer: int, owners: Optional[torch.Tensor]):
+        """Names the rank that serves each expert in the following passes on `layer` (int32 [n_experts],
+        the same table on every rank); None returns to the window rule."""
+        if owners is None:
+            self._check(self._lib.ek_ep_set_owners(self._h, layer, None))
+            return
+        o = owners.to(torch.int32).contiguous().cpu()
+        self._check(self._lib.ek_ep_set_owners(self._h, layer, _ptr(o)))
+
     def ep_finish(self, layer: int, reduced: torch.Tensor, y: torch.Tensor):
         assert reduced.dtype == torch.float32 and reduced.is_contiguous() and y.is_contiguous()
         self._check(self._lib.ek_ep_finish(self._h, layer, _ptr(reduced), reduced.shape[0], _ptr(y)))
@@ -275,15 +295,20 @@ class Backend:
         assert returned.is_contiguous() and y.is_contiguous()
         self._check(self._lib.ek_ep_combine(self._h, layer, _ptr(returned), T, _ptr(y)))
 
-    def route_from_logits(self, logits: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    def route_from_logits_device(self, logits: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        """`route_from_logits` with the results left on the logits' device."""
+        return self.route_from_logits(logits, bias, out_device=logits.device)
+
+    def route_from_logits(self, logits: torch.Tensor, bias: Optional[torch.Tensor] = None, out_device="cpu"):
         logits = logits.to(torch.float32).contiguous()
         T = logits.shape[0]
         E, k = self.cfg.n_experts, self.cfg.top_k
         if bias is not None:
             bias = bias.to(torch.float32).contiguous()
-        art = dict(ids=torch.empty(T, k, dtype=torch.int32), weights=torch.empty(T, k, dtype=torch.float32),
-                   counts=torch.empty(E, dtype=torch.int32), offsets=torch.empty(E + 1, dtype=torch.int32),
-                   perm=torch.empty(T * k, dtype=torch.int32))
+        d = out_device
+        art = dict(ids=torch.empty(T, k, dtype=torch.int32, device=d), weights=torch.empty(T, k, dtype=torch.float32, device=d),
+                   counts=torch.empty(E, dtype=torch.int32, device=d), offsets=torch.empty(E + 1, dtype=torch.int32, device=d),
+                   perm=torch.empty(T * k, dtype=torch.int32, device=d))
         self._check(self._lib.ek_route_from_logits(self._h, _ptr(logits), T, _ptr(bias), _ptr(art["ids"]),
                                                    _ptr(art["weights"]), _ptr(art["counts"]),
                                                    _ptr(art["offsets"]), _ptr(art["perm"])))

@@ -38,6 +38,22 @@ def plan_exchange(counts_all: torch.Tensor, rank: int, world: int):
     return send_splits, recv_splits, counts_src
 
 
+def choose_owners(holders: List[List[int]], step: int, counts: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One serving rank per expert for a pass.  `holders[e]` lists the ranks that hold expert e (home
+    rank first).  Deterministic in `step`, so every rank computes the same table without talking:
+    an expert with several holders rotates over them from pass to pass -- the stand-in for the
+    reference's uniform random pick.  With `counts` (rows per expert of the previous pass) only
+    experts above the mean load leave their home rank."""
+    owners = torch.empty(len(holders), dtype=torch.int32)
+    mean = float(counts.float().mean()) if counts is not None else 0.0
+    for e, h in enumerate(holders):
+        if len(h) > 1 and (counts is None or float(counts[e]) > mean):
+            owners[e] = h[(step + e) % len(h)]
+        else:
+            owners[e] = h[0]
+    return owners
+
+
 class BackendStages:
     """The three device stages of one rank, served by the CUDA backend."""
 
@@ -60,6 +76,9 @@ class BackendStages:
 
     def finish(self, layer: int, reduced: torch.Tensor, y: torch.Tensor):
         self.be.ep_finish(layer, reduced, y)
+
+    def set_owners(self, layer: int, owners: Optional[torch.Tensor]):
+        self.be.set_owners(layer, owners)
 
     # --- the same scheme over peer memory (no collectives) ---
     def peer_setup(self, group, tokens_per_rank: int):
@@ -149,6 +168,7 @@ class ExpertParallelMoE:
         self.last_counts_all = None
         self._peer_ok = None                # auto mode: None = not tried yet
         self.last_mode = None               # scheme the last forward used
+        self._owners_set = {}               # layers that currently follow an owner table
 
     def _buf(self, name: str, rows: int, like: torch.Tensor) -> torch.Tensor:
         b = self._bufs.get(name)
@@ -157,17 +177,28 @@ class ExpertParallelMoE:
             self._bufs[name] = b
         return b
 
-    def forward(self, layer: int, x: torch.Tensor, equal_batches: bool = True) -> torch.Tensor:
+    def forward(self, layer: int, x: torch.Tensor, equal_batches: bool = True,
+                owners: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: this rank's tokens [T,H].  `equal_batches`: every rank passes the same T (required by
-        the "gather" scheme; with "auto" unequal batches use the all-to-all scheme)."""
+        the "gather" scheme; with "auto" unequal batches use the all-to-all scheme).
+        `owners`: int32 [n_experts], the rank that serves each expert in THIS pass -- the same table on
+        every rank, naming only ranks that hold the expert (its home rank or one with a replica).  The
+        reference picks one holder per request at random (controller/registry.rs:49-72); here the
+        caller decides, e.g. `choose_owners`.  Only the schemes in which every rank routes the
+        gathered batch ("gather", "peer") can follow a table."""
         mode = self.mode
         if mode == "auto":
-            small = equal_batches and x.shape[0] * self.world <= self.gather_max_tokens
+            small = equal_batches and (x.shape[0] * self.world <= self.gather_max_tokens or owners is not None)
             if small and x.is_cuda and hasattr(self.stages, "peer_setup") and self._peer_ok is not False:
                 mode = "peer" if self._try_peer(x.shape[0]) else "gather"
             else:
                 mode = "gather" if small else "a2a"
         self.last_mode = mode
+        if owners is not None or self._owners_set.get(layer):
+            if mode == "a2a":
+                raise ValueError("an owner table needs the gather or peer scheme")
+            self.stages.set_owners(layer, owners)
+            self._owners_set[layer] = owners is not None
         if mode == "gather":
             return self._forward_gather(layer, x)
         if mode == "peer":

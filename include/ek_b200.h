@@ -14,7 +14,9 @@
  *     pointer attributes and stages host buffers through its own pinned/device workspace.
  *   - Weights are copied (and re-tiled) at registration; the caller's bytes may be freed as
  *     soon as the call returns (the reference aliases them instead:
- *     ek-computation/src/backend/torch/mod.rs:119-130).
+ *     ek-computation/src/backend/torch/mod.rs:119-130).  Device-resident weights are read on
+ *     the library's own load stream, which waits for no other stream: the work that produced
+ *     them must be complete when the registration call is made.
  *   - All workspace is sized from `max_tokens` at create time; forward calls allocate nothing.
  *   - A backend may be used from many host threads; forward calls on one backend share one
  *     workspace and run one after the other on the backend's stream, except that worker-level
@@ -95,6 +97,8 @@ typedef struct ek_config {
   int32_t ep_rank;           /* expert-parallel rank of this process */
   int32_t ep_size;           /* number of expert-parallel ranks; experts e with
                                 e / (n_experts/ep_size) == ep_rank are local */
+  int32_t replica_slots;     /* extra expert slots per layer for experts OUTSIDE this rank's window
+                                (replicas of hot experts); 0 = none */
   char model_name[64];       /* prefix of expert ids: "<model_name>/l<layer>-e<expert>" */
 } ek_config_t;
 
@@ -138,7 +142,7 @@ int32_t ek_expert_register_safetensors(ek_backend_t* be, const char* id,
  * EK_TILE_LAYOUT_VERSION; anything else is refused (EK_UNSUPPORTED / EK_INVALID_INPUT) and the
  * caller falls back to the bundle.  *needed receives the blob size; EK_INVALID_INPUT when `cap`
  * is too small. */
-#define EK_TILE_LAYOUT_VERSION 3
+#define EK_TILE_LAYOUT_VERSION 4
 int32_t ek_expert_export_tiles(ek_backend_t* be, const char* id, void* blob, size_t cap, size_t* needed);
 int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* blob, size_t blob_len);
 
@@ -330,6 +334,17 @@ int32_t ek_ep_combine(ek_backend_t* be, int32_t layer, const void* returned_rows
 int32_t ek_ep_partial(ek_backend_t* be, int32_t layer, const void* x_all_dev, int32_t T_all, int32_t t0,
                       int32_t T_local, float* partial_dev);
 int32_t ek_ep_finish(ek_backend_t* be, int32_t layer, const float* reduced_dev, int32_t T_local, void* y_dev);
+
+/* Replicated experts.  The reference may hold an expert on several workers and sends each request
+ * for it to one of them, chosen at random (ExpertRegistryImpl::select_random,
+ * ek-computation/src/controller/registry.rs:49-72; the histogram that tells which experts are hot is
+ * ek_expert_counts).  Here a rank created with `replica_slots` > 0 may register experts outside its
+ * window (ek_expert_register / ek_expert_register_tiles take any expert index then; ek_expert_evict
+ * frees the slot), and ek_ep_set_owners names, for the following passes on `layer`, the ONE rank that
+ * serves each expert: owners[n_experts] (host), every rank passing the same table; a rank must hold
+ * what the table gives it (EK_EXPERT_NOT_FOUND otherwise).  NULL returns to the window rule.  Applies
+ * to the schemes in which every rank routes the gathered batch (ek_ep_partial, ek_ep_peer_partial). */
+int32_t ek_ep_set_owners(ek_backend_t* be, int32_t layer, const int32_t* owners /* [n_experts] or NULL */);
 
 /* ---- allocation-free bucketing ------------------------------------------------------------
  * No counterpart in the reference.  Some callers are not allowed to allocate device memory (a

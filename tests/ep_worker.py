@@ -25,12 +25,22 @@ from ek_b200.ep import ExpertParallelMoE, plan_exchange  # noqa: E402
 class OracleStages:
     """CPU stand-in with the interface of ek_b200.ep.BackendStages; holds only this rank's experts."""
 
-    def __init__(self, cfg, layer, rank, world):
+    def __init__(self, cfg, layer, rank, world, replicas=()):
         self.cfg, self.layer = cfg, layer
         self.n_experts, self.top_k, self.hidden = cfg.n_experts, cfg.top_k, cfg.hidden
         self.el = cfg.n_experts // world
         self.lo = rank * self.el
+        self.rank = rank
         self.local = {self.lo + i: layer["experts"][self.lo + i] for i in range(self.el)}
+        for e in replicas:                      # experts of other ranks this rank also holds
+            self.local[e] = layer["experts"][e]
+        self.owners = None
+
+    def set_owners(self, layer_idx, owners):
+        if owners is not None:
+            for e in range(self.n_experts):
+                assert int(owners[e]) != self.rank or e in self.local, f"expert {e} assigned to a rank that does not hold it"
+        self.owners = owners
 
     def route(self, layer_idx, x, send_rows, counts):
         _, ids, w = O.route(self.cfg, x, self.layer["wg"], self.layer["bias"])
@@ -56,7 +66,9 @@ class OracleStages:
         cfg = self.cfg
         _, ids, w = O.route(cfg, x_all, self.layer["wg"], self.layer["bias"])
         partial.zero_()
-        for e in range(self.lo, self.lo + self.el):
+        mine = (range(self.lo, self.lo + self.el) if self.owners is None
+                else [e for e in range(self.n_experts) if int(self.owners[e]) == self.rank])
+        for e in mine:
             tok, slot = (ids == e).nonzero(as_tuple=True)
             if tok.numel():
                 out = O.expert_ffn(x_all[tok], *self.local[e].bf16()).float()
@@ -101,6 +113,12 @@ def main():
     timeout_case = scheme == "peer_timeout"
     if timeout_case:
         scheme = "peer"
+    # replicated experts: rank 1 also holds expert 0 and rank 0 the last expert; the serving rank of
+    # each changes from pass to pass
+    replica_case = scheme.endswith("_replica")
+    if replica_case:
+        scheme = scheme[:-len("_replica")]
+    replicas = ([cfg.n_experts - 1] if rank == 0 else [0] if rank == 1 else []) if replica_case else []
     if scheme in ("gather", "peer"):        # equal batches
         T_global -= T_global % world
         x = x[:T_global]
@@ -110,7 +128,7 @@ def main():
         bounds = [T_global * r // world + (1 if 0 < r < world else 0) for r in range(world + 1)]
     lo, hi = bounds[rank], bounds[rank + 1]
     if mode == "cpu":
-        stages = OracleStages(cfg, layer, rank, world)
+        stages = OracleStages(cfg, layer, rank, world, replicas)
         xl = x[lo:hi].contiguous()
         be = None
     else:
@@ -119,10 +137,10 @@ def main():
         from ek_b200.backend import expert_tensors
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=T_global, device=torch.cuda.current_device(),
-                                               ep_rank=rank, ep_size=world))
+                                               ep_rank=rank, ep_size=world, replica_slots=len(replicas)))
         be.register_router(0, layer["wg"], layer["bias"])
         el = cfg.n_experts // world
-        for e in range(rank * el, (rank + 1) * el):
+        for e in list(range(rank * el, (rank + 1) * el)) + replicas:
             w = layer["experts"][e]
             be.register_expert(be.expert_id(0, e), expert_tensors(0, e, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
         w = layer["shared"]
@@ -132,7 +150,24 @@ def main():
         stages = ek_b200.BackendStages(be)
         xl = x[lo:hi].contiguous().cuda()
     moe = ExpertParallelMoE(stages, mode=scheme)
-    for _ in range(3):                      # several times: buffers, staging areas and step parities are reused
+    if replica_case:
+        from ek_b200.ep import choose_owners
+        el = cfg.n_experts // world
+        holders = [[e // el] for e in range(cfg.n_experts)]
+        holders[0].append(1)
+        holders[cfg.n_experts - 1].append(0)
+        served = set()
+        for step in range(4):               # the table differs from pass to pass; the result must not
+            owners = choose_owners(holders, step)
+            served.add((int(owners[0]), int(owners[cfg.n_experts - 1])))
+            y = moe.forward(0, xl, owners=owners)
+            if be is not None:
+                be.sync()
+            d = (y.cpu().float() - ref["y"][lo:hi].float()).abs()
+            assert (d.max() / ref["y"][lo:hi].float().abs().max()).item() <= 2e-2, f"step {step}: wrong with owners {owners.tolist()}"
+        assert len(served) > 1, "the replicated experts never changed hands"
+        y = moe.forward(0, xl, owners=None)  # and back to the window rule
+    for _ in range(0 if replica_case else 3):   # several times: buffers, staging areas and step parities are reused
         y = moe.forward(0, xl)
     if be is not None:
         be.sync()

@@ -41,15 +41,33 @@ def test_expert_parallel_over_gloo_matches_single_process_oracle(world, scheme):
     assert r.stdout.count("OK") == world
 
 
+def test_replicated_experts_follow_the_owner_table_over_gloo():
+    """Two experts are held by two ranks each; the per-pass owner table moves them between their
+    holders and the layer output stays the single-process oracle's."""
+    r = _launch(2, "cpu", 29640, "gather_replica")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == 2
+
+
+def test_choose_owners_is_the_same_on_every_rank_and_rotates():
+    from ek_b200.ep import choose_owners
+    holders = [[0], [0, 1], [1], [1, 0]]
+    a, b = choose_owners(holders, 0), choose_owners(holders, 1)
+    assert a.tolist() != b.tolist() and a[0] == 0 and a[2] == 1
+    assert all(int(a[e]) in holders[e] and int(b[e]) in holders[e] for e in range(4))
+    cold = choose_owners(holders, 0, counts=torch.tensor([5, 1, 5, 9]))
+    assert int(cold[1]) == 0                 # below the mean load: stays at home
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("scheme", ["a2a", "gather", "peer"])
+@pytest.mark.parametrize("scheme", ["a2a", "gather", "peer", "gather_replica", "peer_replica"])
 def test_expert_parallel_over_nccl_matches_oracle(scheme):
     """"peer": dispatch and combine by the library's own kernels over peer memory (NCCL only sets
     the process group up and exchanges the IPC handles)."""
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
-    r = _launch(2, "gpu", 29650 + {"a2a": 0, "gather": 1, "peer": 2}[scheme], scheme)
+    r = _launch(2, "gpu", 29650 + {"a2a": 0, "gather": 1, "peer": 2, "gather_replica": 3, "peer_replica": 4}[scheme], scheme)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == 2
 

@@ -175,11 +175,12 @@ def test_cfg2_decode_batches_zipf(cfg2_full, T):
     assert int(be.expert_counts(0).sum()) == T * cfg.top_k
 
 
-@pytest.mark.parametrize("T", [1, 32, 256])
+@pytest.mark.parametrize("T", [1, 32, 80, 256])
 def test_cfg3_shape_fp8_reduced_expert_count(T):
     """DeepSeek-V3 layer dimensions (H=7168, I=2048, k=8, fp8 block-scaled, shared expert,
     group-limited sigmoid routing) with 16 routed experts so that the CPU oracle finishes in
-    seconds."""
+    seconds.  The batch sizes reach every chunk-size variant of the grouped GEMM: 16 / 40 / 128 rows
+    per expert on average select the 32-, 64- and 128-row kernels."""
     cfg, layer, x = _cfg_case(3, T, n_experts=16)
     ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
     be = _backend(cfg, layer, 256)
@@ -429,3 +430,45 @@ def test_moe_block_module_matches_the_golden_blocks():
                 assert out[1].shape == (t["x"].shape[0], cfg.n_experts)
         finally:
             be.close()
+
+
+def test_vllm_signature_modules_match_the_golden_blocks():
+    """`B200GrpcExpert.forward(hidden_states, router_logits)` (vLLM's FusedMoE slot) and
+    `B200ExpertKitMoE.forward(hidden_states)` (DeepseekV2MoE slot) against the blocks recorded from
+    the reference's Python modules.  No vLLM import is involved."""
+    import types
+    import ek_b200
+    # Qwen3: softmax scoring, no groups, routed output is the block output
+    t, cfg, layer = _golden_case("qwen3_tiny")
+    be = _backend(cfg, layer, 32, model_name="qwen3")
+    try:
+        m = ek_b200.B200GrpcExpert(cfg.n_experts, cfg.top_k, cfg.hidden, cfg.intermediate, "model.layers.0.mlp.experts",
+                                   backend=be, renormalize=True, scoring_func="softmax")
+        assert m.layer_idx == 0
+        y = m(t["x"].cuda(), t["router_logits"].cuda())
+        assert y.shape == t["x"].shape and y.is_cuda
+        _close(y.cpu(), t["y_remote"], "vLLM expert-mode module, qwen3 golden")
+        with pytest.raises(ek_b200.EKError):
+            ek_b200.B200GrpcExpert(cfg.n_experts, cfg.top_k + 1, cfg.hidden, cfg.intermediate, "p", backend=be)
+    finally:
+        be.close()
+    # DeepSeek-V3: sigmoid + correction bias + group-limited top-k; expert mode returns the routed part,
+    # moe mode the whole block (routed + shared)
+    t, cfg, layer = _golden_case("dsv3_tiny")
+    be = _backend(cfg, layer, 32, model_name="dsv3")
+    try:
+        logits = O.router_logits_sigmoid(t["x"], layer["wg"])
+        m = ek_b200.B200GrpcExpert(cfg.n_experts, cfg.top_k, cfg.hidden, cfg.intermediate, "model.layers.0.mlp.experts",
+                                   backend=be, renormalize=True, use_grouped_topk=cfg.n_group > 1,
+                                   num_expert_group=cfg.n_group, topk_group=cfg.topk_group, scoring_func="sigmoid",
+                                   e_score_correction_bias=layer["bias"].cuda())
+        routed = m(t["x"].cuda(), logits.cuda())
+        _close(routed.cpu(), t["routed_remote"], "vLLM expert-mode module, dsv3 golden (routed part)")
+        hf = types.SimpleNamespace(hidden_size=cfg.hidden, n_routed_experts=cfg.n_experts, num_experts_per_tok=cfg.top_k,
+                                   norm_topk_prob=True, n_shared_experts=1, routed_scaling_factor=cfg.routed_scaling)
+        moe = ek_b200.B200ExpertKitMoE(hf, None, "model.layers.0.mlp", backend=be)
+        y = moe(t["x"].cuda())
+        moe.check()
+        _close(y.cpu(), t["y_remote"], "vLLM moe-mode module, dsv3 golden (routed + shared)")
+    finally:
+        be.close()

@@ -366,3 +366,72 @@ def test_many_layers_registered_back_to_back():
         y = be.moe_forward_fused(i, x.cuda()).cpu()
         Hh.assert_outputs_close(y, ref["y"], f"layer {i}")
     be.close()
+
+
+def test_replica_slots_and_owner_table_two_ranks_emulated_on_one_gpu():
+    """Replicated experts without a second GPU: two backends (ep_rank 0 and 1 of 2) on one device,
+    each holding its window plus one replica of the other's expert.  Every pass both route the whole
+    batch and serve what the owner table gives them; the summed partials, finished per token slice,
+    must equal the single-process oracle whichever holder serves the replicated experts."""
+    import ek_b200
+    from ek_b200.backend import expert_tensors
+    from oracle import configs as OC
+    from oracle import ek_oracle as O
+    cfg = OC.config(1)
+    cfg.quant = "fp8"
+    layer = OC.make_layer(cfg, 515)
+    T, E = 48, cfg.n_experts
+    x = OC.make_inputs(cfg, T, 516)
+    ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
+    el = E // 2
+    replica = {0: E - 1, 1: 0}
+    backs = []
+    try:
+        for rank in (0, 1):
+            be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=T, ep_rank=rank, ep_size=2, replica_slots=1))
+            be.register_router(0, layer["wg"], layer["bias"])
+            for e in list(range(rank * el, (rank + 1) * el)) + [replica[rank]]:
+                w = layer["experts"][e]
+                be.register_expert(be.expert_id(0, e), expert_tensors(0, e, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
+            w = layer["shared"]
+            be.register_expert(be.shared_id(0), expert_tensors(0, None, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s,
+                                                               shared=True))
+            assert be.loaded() == el + 2
+            backs.append(be)
+        with pytest.raises(ek_b200.EKError) as err:     # the single replica slot is taken
+            w = layer["experts"][3]
+            backs[1].register_expert(backs[1].expert_id(0, 3), expert_tensors(0, 3, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
+        assert err.value.status_name == "EK_NO_MEMORY"
+        xc = x.cuda()
+        home = torch.tensor([e // el for e in range(E)], dtype=torch.int32)
+        tables = [None, home.clone(), home.clone(), home.clone()]
+        tables[2][0] = 1                                 # expert 0 served by its replica on rank 1
+        tables[3][0], tables[3][E - 1] = 1, 0            # both replicated experts away from home
+        for owners in tables:
+            total = torch.zeros(T, cfg.hidden, dtype=torch.float32, device="cuda")
+            for rank, be in enumerate(backs):
+                be.set_owners(0, owners)
+                part = torch.empty(T, cfg.hidden, dtype=torch.float32, device="cuda")
+                be.ep_partial(0, xc, rank * (T // 2), T // 2, part)
+                be.sync()
+                total += part
+            y = torch.empty(T, cfg.hidden, dtype=torch.bfloat16, device="cuda")
+            for rank, be in enumerate(backs):
+                sl = slice(rank * (T // 2), (rank + 1) * (T // 2))
+                be.ep_finish(0, total[sl].contiguous(), y[sl])
+                be.sync()
+            mr, ma = Hh.output_errors(y, ref["y"])
+            Hh.record(f"owner table {None if owners is None else owners.tolist()}", max_rel=mr, mean_abs=ma)
+            assert mr <= Hh.MAX_REL and ma <= Hh.MEAN_ABS
+        bad = home.clone()
+        bad[1] = 1                                       # rank 1 holds no copy of expert 1
+        with pytest.raises(ek_b200.EKError) as err:
+            backs[1].set_owners(0, bad)
+        assert err.value.status_name == "EK_EXPERT_NOT_FOUND"
+        backs[1].evict(backs[1].expert_id(0, 0))        # the replica slot is free again
+        w = layer["experts"][3]
+        backs[1].register_expert(backs[1].expert_id(0, 3), expert_tensors(0, 3, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
+        assert backs[1].has(backs[1].expert_id(0, 3)) and not backs[1].has(backs[1].expert_id(0, 0))
+    finally:
+        for be in backs:
+            be.close()
