@@ -50,9 +50,9 @@ SEED = 3000
 # profiler-sized case (dram__bytes_read.sum + dram__bytes_write.sum per launch / active slots).  Keyed by
 # (kernel, tile layout version): a library whose layout differs from the captured one reports null.
 NCU_TRAFFIC = {
-    ("ffn_tc_kernel<fp8, gate/up + SwiGLU>", 3): {
-        "bytes_per_active_slot": 976.71e6 / 33,
-        "source": "profiles/ffn_tc_fp8_cfg3_32experts_T32.md (33 slots, T=32: 973.30 MB read + 3.41 MB written)"},
+    ("ffn_tc_kernel<fp8, gate/up + SwiGLU>", 4): {
+        "bytes_per_active_slot": 977.48e6 / 33,
+        "source": "profiles/ffn_tc_fp8_cfg3_32experts_T32.md (33 slots, T=32: 973.32 MB read + 4.16 MB written)"},
 }
 
 
@@ -650,11 +650,14 @@ def main_single(args, local: int):
         step(i)
     sync()
     sampler = ClockSampler(local)
-    n_cond = condition(step, 1.0, sync)
+    n_cond = 0 if args.quick else condition(step, 1.0, sync)
     l0 = be.kernel_launches()
-    blocks, t0, t1 = timed_blocks(step, args.steps, sync)
+    if args.quick:
+        blocks, t0, t1 = timed_blocks(step, args.steps, sync, min_seconds=0.0, min_blocks=1, max_blocks=1)
+    else:
+        blocks, t0, t1 = timed_blocks(step, args.steps, sync)
     launches = (be.kernel_launches() - l0) // len(blocks)
-    stage = stage_profile(be, step, sync)            # back to back with the timed blocks
+    stage = stage_profile(be, step, sync, 4 if args.quick else 48)   # back to back with the timed blocks
     t2 = time.perf_counter()
     clocks = sampler.window(t0, t1)
     clocks_stage = sampler.window(t1, t2)
@@ -685,10 +688,10 @@ def main_single(args, local: int):
     def e2e_step(i):
         be._check(fused(be._h, 0, xh[i % 4].data_ptr(), T, yh.data_ptr(), None))
 
-    for i in range(3):
+    for i in range(1 if args.quick else 3):
         e2e_step(i)
     e2e_blocks, tot = [], 0.0
-    while len(e2e_blocks) < 3 or (tot < 0.3 and len(e2e_blocks) < 200):
+    while len(e2e_blocks) < (1 if args.quick else 3) or (not args.quick and tot < 0.3 and len(e2e_blocks) < 200):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for i in range(e2e_steps):
@@ -906,6 +909,9 @@ def main():
     ap.add_argument("--sweep", default="", help="comma-separated extra token counts reported under 'sweep'")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the timed batch")
+    ap.add_argument("--quick", action="store_true",
+                    help="N = 1, for profiler captures: W warm-up passes, ONE block of K steps, a short stage profile; no "
+                         "conditioning, no end-to-end loop, no check, no extras, no CPU baseline (not a benchmark number)")
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="N = 1: leave out the default sweep and the cfg2 / INT8 rows under 'extra'")
     ap.add_argument("--stream", type=int, default=0,
@@ -924,6 +930,9 @@ def main():
                     help="routed experts (default: the configuration's own count; smaller values give profiler-sized cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.quick:
+        args.no_check = args.no_cpu_baseline = True
+        args.extras = False
     if args.impl == "reference":
         return run_reference(args)
 
