@@ -111,6 +111,8 @@ struct ek_backend {
   ChunkDesc* chunks = nullptr;
   int32_t* n_chunks = nullptr;
   DevStatus* status = nullptr;
+  uint32_t* front_ticket = nullptr;    // last-CTA ticket of the fused small-batch front kernel
+  int front_small = 1;                 // use that kernel when the batch qualifies
   float* sk_buf = nullptr;             // partial accumulators of K-split work items
   uint32_t* sk_flags = nullptr;
   int split_k = 1;
@@ -485,6 +487,7 @@ int check_status(ek_backend* be) {
   cudaMemsetAsync(be->status, 0, sizeof(DevStatus), be->stream);
   // a pass that gave up may have left split-item flags raised
   cudaMemsetAsync(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t), be->stream);
+  cudaMemsetAsync(be->front_ticket, 0, sizeof(uint32_t), be->stream);
   cudaStreamSynchronize(be->stream);
   switch (st.code) {
     case DEV_TIMEOUT:
@@ -519,58 +522,25 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   cudaStream_t s = be->stream;
   mark(be, 0);
   const int32_t* ids = given_ids_dev;
-  if (fused) {
-    RouteParams rp;
-    rp.x = x;
-    rp.wg = L.router_w;
-    rp.wg_f32 = L.router_f32;
-    rp.bias = L.router_bias;
-    rp.logits = be->logits;
-    rp.ids = be->ids;
-    rp.weights = be->weights;
-    rp.counts = be->counts;
-    rp.T = T; rp.H = c.hidden; rp.E = c.n_experts; rp.k = k;
-    rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
-    rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling;
-    rp.bf16_weights = c.bf16_combine;
-    rp.partial = nullptr;
-    rp.n_partials = 0;
-    bool tc_done = false;
-    if (L.router_tc) {
-      RouterTcParams tp;
-      if (encode_2d(be, &tp.x_map, x, (uint64_t)c.hidden, (uint64_t)T, 128)) {
-        tp.w_map = L.router_map;
-        tp.partial = be->partial;
-        tp.zero_counts = be->counts;
-        tp.status = be->status;
-        tp.T = T; tp.H = c.hidden; tp.E = c.n_experts;
-        tp.n_atoms = (c.hidden + 63) / 64;
-        router_tc_plan(T, c.hidden, be->n_sm, &tp.n_splits, &tp.atoms_per_split);
-        tp.tmem_cols = 32;
-        while (tp.tmem_cols < c.n_experts) tp.tmem_cols *= 2;
-        be->launches += launch_router_tc(tp, s);
-        rp.partial = be->partial;
-        rp.n_partials = tp.n_splits;
-        tc_done = true;
-      }
-    }
-    if (!tc_done) be->launches += launch_router_logits(rp, s);
-    if (debug_sync_failed(be, "router logits")) return EK_CUDA;
-    be->launches += launch_route_select(rp, s, tc_done);
-    if (debug_sync_failed(be, "route select")) return EK_CUDA;
-    ids = be->ids;
-  } else {
-    // caller-supplied ids may be invalid: rows that no expert claims must read as "absent"
-    cudaMemsetAsync(be->inv, 0xFF, sizeof(int32_t) * Tk, s);
-    be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
-  }
-  mark(be, 1);
+  RouteParams rp;
+  rp.x = x;
+  rp.wg = L.router_w;
+  rp.wg_f32 = L.router_f32;
+  rp.bias = L.router_bias;
+  rp.logits = be->logits;
+  rp.ids = be->ids;
+  rp.weights = be->weights;
+  rp.counts = be->counts;
+  rp.T = T; rp.H = c.hidden; rp.E = c.n_experts; rp.k = k;
+  rp.scoring = c.scoring; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
+  rp.norm = c.norm_topk_prob; rp.scaling = c.routed_scaling;
+  rp.bf16_weights = c.bf16_combine;
+  rp.partial = nullptr;
+  rp.n_partials = 0;
   PermuteParams pp;
-  pp.ids = ids; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
+  pp.ids = fused ? be->ids : given_ids_dev; pp.counts = be->counts; pp.offsets = be->offsets; pp.perm = be->perm; pp.inv = be->inv;
   pp.T = T; pp.k = k; pp.E = c.n_experts; pp.e_lo = be->e_lo; pp.e_hi = be->e_hi;
   pp.owners = L.has_owners ? L.owners : nullptr; pp.rank = c.ep_rank;
-  be->launches += launch_permute(pp, s);
-  if (debug_sync_failed(be, "permute")) return EK_CUDA;
   // expected rows per local expert: Tk / n_experts whatever the sharding
   const int nmax = pick_nmax((int)((int64_t)Tk * be->n_local / c.n_experts), be->n_local);
   WorklistParams wp;
@@ -583,11 +553,72 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   wp.max_chunks = be->max_chunks;
   wp.status = be->status;
   wp.counts_copy = L.last_counts;   // the layer's activation metric, read back by ek_expert_counts
-  be->launches += launch_worklist(wp, s);
-  if (debug_sync_failed(be, "worklist")) return EK_CUDA;
-  be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T,
-                                f16_rows(be), s);
-  if (debug_sync_failed(be, "gather")) return EK_CUDA;
+  // small batches: everything in front of the GEMMs in one launch
+  const bool front = fused && be->front_small && L.router_bf16 && front_small_supported(T, c.n_experts, k, c.hidden);
+  bool gathered = false;
+  if (front) {
+    FrontParams fp;
+    fp.route = rp;
+    fp.route.wg = L.router_bf16;
+    fp.route.wg_f32 = 0;
+    fp.route.partial = nullptr;
+    fp.route.n_partials = 0;
+    fp.slice = front_small_slice(c.hidden);
+    fp.permute = pp;
+    fp.worklist = wp;
+    fp.partial = be->partial;
+    fp.ticket = be->front_ticket;
+    fp.xp = be->xp;
+    fp.gather_rows = Tk + sh_T <= 24 ? 1 : 0;
+    fp.shared_t0 = opt.sh_t0; fp.shared_T = sh_T;
+    fp.to_f16 = f16_rows(be) ? 1 : 0;
+    be->launches += launch_front_small(fp, s);
+    if (debug_sync_failed(be, "front (router + bucketing)")) return EK_CUDA;
+    gathered = fp.gather_rows != 0;
+    ids = be->ids;
+    mark(be, 1);
+  } else {
+    if (fused) {
+      bool tc_done = false;
+      if (L.router_tc) {
+        RouterTcParams tp;
+        if (encode_2d(be, &tp.x_map, x, (uint64_t)c.hidden, (uint64_t)T, 128)) {
+          tp.w_map = L.router_map;
+          tp.partial = be->partial;
+          tp.zero_counts = be->counts;
+          tp.status = be->status;
+          tp.T = T; tp.H = c.hidden; tp.E = c.n_experts;
+          tp.n_atoms = (c.hidden + 63) / 64;
+          router_tc_plan(T, c.hidden, be->n_sm, &tp.n_splits, &tp.atoms_per_split);
+          tp.tmem_cols = 32;
+          while (tp.tmem_cols < c.n_experts) tp.tmem_cols *= 2;
+          be->launches += launch_router_tc(tp, s);
+          rp.partial = be->partial;
+          rp.n_partials = tp.n_splits;
+          tc_done = true;
+        }
+      }
+      if (!tc_done) be->launches += launch_router_logits(rp, s);
+      if (debug_sync_failed(be, "router logits")) return EK_CUDA;
+      be->launches += launch_route_select(rp, s, tc_done);
+      if (debug_sync_failed(be, "route select")) return EK_CUDA;
+      ids = be->ids;
+    } else {
+      // caller-supplied ids may be invalid: rows that no expert claims must read as "absent"
+      cudaMemsetAsync(be->inv, 0xFF, sizeof(int32_t) * Tk, s);
+      be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
+    }
+    mark(be, 1);
+    be->launches += launch_permute(pp, s);
+    if (debug_sync_failed(be, "permute")) return EK_CUDA;
+    be->launches += launch_worklist(wp, s);
+    if (debug_sync_failed(be, "worklist")) return EK_CUDA;
+  }
+  if (!gathered) {
+    be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T,
+                                  f16_rows(be), s);
+    if (debug_sync_failed(be, "gather")) return EK_CUDA;
+  }
   L.have_counts = true;
   mark(be, 2);
   run_ffn(be, L, nmax, 0);
@@ -764,6 +795,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
   CKC(cudaMalloc(&be->ep_counters, EK_EP_MAX_RANKS * sizeof(uint32_t)));
   CKC(cudaMemset(be->ep_counters, 0, EK_EP_MAX_RANKS * sizeof(uint32_t)));
+  CKC(cudaMalloc(&be->front_ticket, sizeof(uint32_t)));
+  CKC(cudaMemset(be->front_ticket, 0, sizeof(uint32_t)));
   CKC(cudaMalloc(&be->sk_buf, ffn_tc_scratch_floats(be->n_sm) * sizeof(float)));
   CKC(cudaMalloc(&be->sk_flags, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
   CKC(cudaMemset(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
@@ -790,6 +823,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   if (impl && std::string(impl) == "simt") be->ffn_impl = 1;
   const char* prec = getenv("EK_B200_PRECISE_DEQUANT");
   if (prec && prec[0] == '1') be->precise = 1;
+  const char* fs = getenv("EK_B200_FRONT_SMALL");
+  if (fs && fs[0] == '0') be->front_small = 0;
   const char* sk = getenv("EK_B200_SPLIT_K");
   if (sk && sk[0] == '0') be->split_k = 0;
   *out = be;
@@ -813,7 +848,7 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaFree(be->tk_dev);
   cudaFree(be->logits); cudaFree(be->weights); cudaFree(be->bias_scratch); cudaFree(be->partial); cudaFree(be->flag_dev); cudaFree(be->ids); cudaFree(be->counts);
   cudaFree(be->offsets); cudaFree(be->perm); cudaFree(be->inv); cudaFree(be->chunks);
-  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->sk_buf); cudaFree(be->sk_flags); cudaFree(be->ep_counters); cudaFree(be->maps);
+  cudaFree(be->n_chunks); cudaFree(be->status); cudaFree(be->sk_buf); cudaFree(be->sk_flags); cudaFree(be->front_ticket); cudaFree(be->ep_counters); cudaFree(be->maps);
   cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_segs); cudaFree(be->segs); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }

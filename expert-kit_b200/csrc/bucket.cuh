@@ -1,0 +1,107 @@
+// Device routines shared by the bucketing kernels (permute.cu) and the fused front kernel for small
+// batches (front_small.cu).
+#pragma once
+#include "ek_internal.h"
+
+namespace ek {
+
+// eight bf16 -> eight f16 (round to nearest, saturating at +-65504)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(v & 0xFFFF0000u)), "f"(__uint_as_float(v << 16)));
+  return r;
+}
+__device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
+  v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y); v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
+  return v;
+}
+
+// Chunk descriptors: every expert this rank serves has its row range cut into pieces of `chunk_rows`,
+// followed by the virtual shared experts (all T tokens each).  One CTA of 1024 threads.
+__device__ __forceinline__ void build_worklist(const WorklistParams& p) {
+  __shared__ int s_scan[1024];
+  __shared__ int s_total;
+  const int tid = threadIdx.x;
+  const int n_local = p.e_hi - p.e_lo;
+  if (p.counts_copy)
+    for (int e = tid; e < p.E; e += 1024) p.counts_copy[e] = __ldcg(&p.counts[e]);
+  // experts this rank serves: its window (slot = e - e_lo), or, with an owner table, every expert
+  // the table gives to this rank (slot from the layer's slot table: own experts and replicas)
+  const int first = p.owners ? 0 : p.e_lo, last = p.owners ? p.E : p.e_hi;
+  int running = 0;
+  for (int e0 = first; e0 < last; e0 += 1024) {
+    const int e = e0 + tid;
+    int cnt = 0, nch = 0, slot = -1;
+    if (e < last && (!p.owners || p.owners[e] == p.rank)) {
+      cnt = __ldcg(&p.counts[e]);   // the histogram is built with atomics: read it at L2
+      slot = p.slot_of ? p.slot_of[e] : e - p.e_lo;
+      nch = (cnt + p.chunk_rows - 1) / p.chunk_rows;
+      if (cnt > 0 && (slot < 0 || !p.registered[slot])) {
+        if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
+          p.status->where = 2;
+          p.status->aux0 = e;
+        }
+        nch = 0;
+      }
+    }
+    s_scan[tid] = nch;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {
+      int v = tid >= o ? s_scan[tid - o] : 0;
+      __syncthreads();
+      s_scan[tid] += v;
+      __syncthreads();
+    }
+    int first_chunk = running + s_scan[tid] - nch;
+    if (tid == 1023) s_total = s_scan[tid];
+    if (nch > 0) {
+      const int off = p.offsets[e];
+      for (int c = 0; c < nch; ++c) {
+        if (first_chunk + c >= p.max_chunks) break;
+        ChunkDesc d;
+        d.slot = slot;
+        d.in_row = off + c * p.chunk_rows;
+        d.out_row = d.in_row;
+        d.n_rows = min(p.chunk_rows, cnt - c * p.chunk_rows) | (nch > 1 ? kChunkMulti : 0);
+        p.chunks[first_chunk + c] = d;
+      }
+    }
+    __syncthreads();
+    running += s_total;
+    __syncthreads();
+  }
+  // shared virtual experts
+  const int per_shared = (p.T + p.chunk_rows - 1) / p.chunk_rows;
+  for (int i = tid; i < p.n_shared * per_shared; i += 1024) {
+    const int j = i / per_shared, c = i % per_shared;
+    if (running + i >= p.max_chunks) break;
+    ChunkDesc d;
+    d.slot = n_local + j;
+    d.in_row = p.Tk + c * p.chunk_rows;
+    d.out_row = p.Tk + j * p.T + c * p.chunk_rows;
+    d.n_rows = min(p.chunk_rows, p.T - c * p.chunk_rows) | (per_shared > 1 ? kChunkMulti : 0);
+    p.chunks[running + i] = d;
+    if (c == 0 && !p.registered[d.slot]) {
+      if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
+        p.status->where = 3;
+        p.status->aux0 = -1 - j;
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int total = running + p.n_shared * per_shared;
+    if (total > p.max_chunks) {
+      if (atomicCAS(&p.status->code, DEV_OK, DEV_BOUNDS) == DEV_OK) {
+        p.status->where = 4;
+        p.status->aux0 = total;
+      }
+      total = p.max_chunks;
+    }
+    // a missing expert cancels the GEMMs altogether
+    *p.n_chunks = (*reinterpret_cast<volatile int32_t*>(&p.status->code) == DEV_OK) ? total : 0;
+  }
+}
+
+}  // namespace ek

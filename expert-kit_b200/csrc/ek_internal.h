@@ -172,6 +172,25 @@ struct WorklistParams {
 };
 int launch_worklist(const WorklistParams& p, cudaStream_t s);
 
+// Router + bucketing + work list (+ gather of a handful of rows) in one launch for small batches
+// (front_small.cu).  `route.wg` must be the bf16 router weight; `route.partial` is unused, the
+// kernel keeps its K-slice partial logits in `partial` ([slices][T][E]).
+struct FrontParams {
+  RouteParams route;
+  PermuteParams permute;
+  WorklistParams worklist;
+  float* partial;
+  uint32_t* ticket;          // zero between launches
+  __nv_bfloat16* xp;         // gathered rows (when gather_rows)
+  int32_t gather_rows;       // 1: also gather; rows [0,Tk) routed, [Tk, Tk+shared_T) tokens from shared_t0
+  int32_t shared_t0, shared_T;
+  int32_t to_f16;
+  int32_t slice;             // K elements per CTA of the logits phase: front_small_slice(H)
+};
+bool front_small_supported(int T, int E, int k, int H);
+int front_small_slice(int H);
+int launch_front_small(const FrontParams& p, cudaStream_t s);
+
 // rows [0,Tk): xp[r] = x[perm[r]/k]; rows [Tk, Tk+T) = x (only when with_shared)
 // `n_routed` (device) = number of permuted rows that exist on this rank (offsets[E]).
 // The shared expert's rows are tokens [shared_t0, shared_t0 + shared_T) of x (shared_T = 0: none).

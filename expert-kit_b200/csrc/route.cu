@@ -4,6 +4,7 @@
 // Replaces the frontend routing of expertkit_torch/models/qwen3_moe.py:161-169 and of the
 // DeepSeek-V3 router called at expertkit_torch/models/deepseek_v3/model.py:142.
 #include "ek_internal.h"
+#include "route_select.cuh"
 
 namespace ek {
 
@@ -98,19 +99,6 @@ __global__ void __launch_bounds__(256) router_logits_kernel(RouteParams p) {
 constexpr int kMaxExperts = 1024;
 constexpr int kSelWarps = 4;
 
-// (value, index) argmax with the canonical tie rule: larger value first, then lower index.
-__device__ __forceinline__ void warp_argmax(float& v, int& idx) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, v, o);
-    int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (ov > v || (ov == v && oi < idx)) {
-      v = ov;
-      idx = oi;
-    }
-  }
-}
-
 // One warp per token.
 __global__ void __launch_bounds__(kSelWarps * 32) route_select_kernel(RouteParams p) {
   pdl_wait();
@@ -121,129 +109,7 @@ __global__ void __launch_bounds__(kSelWarps * 32) route_select_kernel(RouteParam
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kSelWarps + warp;
   if (t >= p.T) return;
-  float* sc = s_score[warp];
-  float* ch = s_choice[warp];
-  float* lg = p.logits + (size_t)t * p.E;
-  const int E = p.E;
-  if (p.partial) {
-    // add the split-K partial sums in split order; the softmax path works on bf16 logits like the
-    // reference's bf16 linear layer.  Four experts per lane and four splits per round: 16
-    // independent loads in flight instead of one dependent chain per expert.
-    for (int e0 = lane; e0 < E; e0 += 128) {
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int k0 = 0; k0 < p.n_partials; k0 += 4) {
-        float tmp[4][4];
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int e = e0 + 32 * j;
-            tmp[a][j] = (k0 + a < p.n_partials && e < E) ? p.partial[((size_t)(k0 + a) * p.T + t) * E + e] : 0.f;
-          }
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-          if (k0 + a < p.n_partials) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] += tmp[a][j];
-          }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int e = e0 + 32 * j;
-        if (e < E) lg[e] = p.scoring == EK_SCORE_SOFTMAX ? __bfloat162float(__float2bfloat16_rn(v[j])) : v[j];
-      }
-    }
-    __syncwarp();
-  }
-
-  if (p.scoring == EK_SCORE_SOFTMAX) {
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, lg[e]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-      float ex = expf(lg[e] - m);
-      sc[e] = ex;
-      sum += ex;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    for (int e = lane; e < E; e += 32) {
-      float pr = sc[e] / sum;
-      sc[e] = pr;
-      ch[e] = pr;
-    }
-  } else {
-    for (int e = lane; e < E; e += 32) {
-      float s = 1.f / (1.f + expf(-lg[e]));
-      sc[e] = s;
-      ch[e] = p.bias ? s + p.bias[e] : s;
-    }
-  }
-  __syncwarp();
-
-  if (p.n_group > 1) {
-    const int per = E / p.n_group;
-    float* gs = s_group[warp];
-    for (int g = lane; g < p.n_group; g += 32) {
-      float a = -INFINITY, b = -INFINITY;  // two largest
-      for (int j = 0; j < per; ++j) {
-        float v = ch[g * per + j];
-        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
-      }
-      gs[g] = a + b;
-    }
-    __syncwarp();
-    // keep the best topk_group groups (descending score, ties towards the lower group)
-    unsigned long long keep = 0ull;
-    for (int it = 0; it < p.topk_group; ++it) {
-      float bv = -INFINITY;
-      int bi = 0x7fffffff;
-      for (int g = lane; g < p.n_group; g += 32) {
-        if ((keep >> g) & 1ull) continue;
-        float v = gs[g];
-        if (v > bv || (v == bv && g < bi)) { bv = v; bi = g; }
-      }
-      warp_argmax(bv, bi);
-      keep |= 1ull << bi;
-    }
-    for (int e = lane; e < E; e += 32)
-      if (!((keep >> (e / per)) & 1ull)) ch[e] = 0.0f;
-    __syncwarp();
-  }
-
-  // top-k, canonical order
-  unsigned taken = 0u;  // bit j: element lane + 32*j already selected
-  float wsel = 0.f;     // lane i < k keeps the weight of the i-th pick
-  int isel = -1;
-  for (int it = 0; it < p.k; ++it) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int j = 0, e = lane; e < E; ++j, e += 32) {
-      if ((taken >> j) & 1u) continue;
-      float v = ch[e];
-      if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
-    }
-    warp_argmax(bv, bi);
-    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-    if (lane == it) {
-      isel = bi;
-      wsel = sc[bi];
-    }
-  }
-  // renormalise: sequential sum in slot order (lane 0 .. k-1)
-  float denom = 0.f;
-  for (int i = 0; i < p.k; ++i) denom += __shfl_sync(0xffffffffu, wsel, i);
-  if (lane < p.k) {
-    float w = wsel;
-    if (p.norm) w = (p.scoring == EK_SCORE_SOFTMAX) ? w / denom : w / (denom + 1e-20f);
-    if (p.scoring != EK_SCORE_SOFTMAX) w *= p.scaling;
-    if (p.bf16_weights) w = __bfloat162float(__float2bfloat16_rn(w));
-    p.ids[(size_t)t * p.k + lane] = isel;
-    p.weights[(size_t)t * p.k + lane] = w;
-    atomicAdd(&p.counts[isel], 1);
-  }
+  select_token(p, t, lane, s_score[warp], s_choice[warp], s_group[warp]);
 }
 
 __global__ void histogram_kernel(const int32_t* ids, int32_t n, int32_t E, int32_t* counts,
