@@ -50,7 +50,7 @@ SEED = 3000
 # profiler-sized case (dram__bytes_read.sum + dram__bytes_write.sum per launch / active slots).  Keyed by
 # (kernel, tile layout version): a library whose layout differs from the captured one reports null.
 NCU_TRAFFIC = {
-    ("ffn_tc_kernel<fp8, gate/up + SwiGLU>", 4): {
+    ("ffn_tc_kernel<fp8, gate/up + SwiGLU>", 5): {
         "bytes_per_active_slot": 977.48e6 / 33,
         "source": "profiles/ffn_tc_fp8_cfg3_32experts_T32.md (33 slots, T=32: 973.32 MB read + 4.16 MB written)"},
 }
@@ -629,6 +629,9 @@ def main_single(args, local: int):
     if args.extras and not sweep:
         sweep = [1, 32, 1024, 4096] if args.config == "cfg3" else [1, 16, 64]
     dev = torch.device("cuda", local)
+    # the continuous-batching stream: 2000 steps when asked for, a 300-step sample in the default run
+    if args.stream == 0 and args.extras and args.config == "cfg3" and n_exp == S.n_experts:
+        args.stream = 300
     T_max = max([T] + sweep + ([2400] if args.stream > 0 else []))
     be, dirs = synth.build_backend(S, T_max, SEED, dev, n_experts=n_exp)
     u = dirs[0]
@@ -915,7 +918,7 @@ def main():
     ap.add_argument("--no-extras", dest="extras", action="store_false",
                     help="N = 1: leave out the default sweep and the cfg2 / INT8 rows under 'extra'")
     ap.add_argument("--stream", type=int, default=0,
-                    help="also run a continuous-batching stream of this many steps (decode ~Poisson(96) tokens, a "
+                    help="also run a continuous-batching stream of this many steps (the default run takes a 300-step sample; 2000 = the full configuration) (decode ~Poisson(96) tokens, a "
                          "512-2048 token prefill chunk every 10th step, Zipf(1.2) expert load rotated every 200 steps, "
                          "every expert >= 1 row) through the controller-level entry point; reported under 'stream'")
     ap.add_argument("--worker-threads", type=int, default=0,

@@ -21,7 +21,7 @@ OUT_DIR = os.path.join(HERE, "lib", VARIANT) if VARIANT else os.path.join(HERE, 
 LIB = os.path.join(OUT_DIR, "libek_b200.so")
 EXTRA = os.environ.get("EK_B200_EXTRA_FLAGS", "").split()
 SOURCES = ["backend.cu", "route.cu", "permute.cu", "front_small.cu", "combine.cu", "layout.cu", "ffn_simt.cu", "ffn_tc.cu", "router_tc.cu", "ep_peer.cu"]
-HEADERS = ["ek_internal.h", "ptx.cuh", "route_select.cuh", "bucket.cuh", "safetensors.hpp", os.path.join("..", "..", "include", "ek_b200.h")]
+HEADERS = ["ek_internal.h", "ptx.cuh", "route_select.cuh", "bucket.cuh", "peer_sync.cuh", "safetensors.hpp", os.path.join("..", "..", "include", "ek_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "--expt-relaxed-constexpr"]
 

@@ -111,8 +111,9 @@ struct ek_backend {
   ChunkDesc* chunks = nullptr;
   int32_t* n_chunks = nullptr;
   DevStatus* status = nullptr;
-  uint32_t* front_ticket = nullptr;    // last-CTA ticket of the fused small-batch front kernel
+  uint32_t* front_ticket = nullptr;    // last-CTA tickets: [0] fused small-batch front kernel, [1] expert-parallel signal
   int front_small = 1;                 // use that kernel when the batch qualifies
+  int bucket_gather = 1;               // bucketing + work list + gather in one launch when T*k <= 4096
   float* sk_buf = nullptr;             // partial accumulators of K-split work items
   uint32_t* sk_flags = nullptr;
   int split_k = 1;
@@ -487,7 +488,7 @@ int check_status(ek_backend* be) {
   cudaMemsetAsync(be->status, 0, sizeof(DevStatus), be->stream);
   // a pass that gave up may have left split-item flags raised
   cudaMemsetAsync(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t), be->stream);
-  cudaMemsetAsync(be->front_ticket, 0, sizeof(uint32_t), be->stream);
+  cudaMemsetAsync(be->front_ticket, 0, 2 * sizeof(uint32_t), be->stream);
   cudaStreamSynchronize(be->stream);
   switch (st.code) {
     case DEV_TIMEOUT:
@@ -510,6 +511,8 @@ struct LayerOpts {
   int sh_t0 = 0;
   int sh_T = -1;            // -1: all T tokens
   float* partial = nullptr; // [T,H] fp32 instead of y
+  PeerWait wait;            // expert parallel: x is complete once every rank's flag has reached a step number
+  const PeerSignal* signal = nullptr;   // expert parallel: publish the step number once `partial` is complete
 };
 
 int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, const int32_t* given_ids_dev,
@@ -556,7 +559,14 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   // small batches: everything in front of the GEMMs in one launch
   const bool front = fused && be->front_small && L.router_bf16 && front_small_supported(T, c.n_experts, k, c.hidden);
   bool gathered = false;
+  // a pending wait for the peers' tokens: taken along by the tensor-core router, else a launch of its own
+  bool wait_pending = opt.wait.flags != nullptr;
+  auto wait_now = [&]() {
+    if (wait_pending) be->launches += launch_ep_wait(opt.wait.flags, opt.wait.world, opt.wait.step_no, be->status, opt.wait.where, s);
+    wait_pending = false;
+  };
   if (front) {
+    wait_now();
     FrontParams fp;
     fp.route = rp;
     fp.route.wg = L.router_bf16;
@@ -592,27 +602,43 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
           router_tc_plan(T, c.hidden, be->n_sm, &tp.n_splits, &tp.atoms_per_split);
           tp.tmem_cols = 32;
           while (tp.tmem_cols < c.n_experts) tp.tmem_cols *= 2;
+          if (wait_pending) tp.wait = opt.wait;
+          wait_pending = false;
           be->launches += launch_router_tc(tp, s);
           rp.partial = be->partial;
           rp.n_partials = tp.n_splits;
           tc_done = true;
         }
       }
+      wait_now();
       if (!tc_done) be->launches += launch_router_logits(rp, s);
       if (debug_sync_failed(be, "router logits")) return EK_CUDA;
       be->launches += launch_route_select(rp, s, tc_done);
       if (debug_sync_failed(be, "route select")) return EK_CUDA;
       ids = be->ids;
     } else {
+      wait_now();
       // caller-supplied ids may be invalid: rows that no expert claims must read as "absent"
       cudaMemsetAsync(be->inv, 0xFF, sizeof(int32_t) * Tk, s);
       be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
     }
     mark(be, 1);
-    be->launches += launch_permute(pp, s);
-    if (debug_sync_failed(be, "permute")) return EK_CUDA;
-    be->launches += launch_worklist(wp, s);
-    if (debug_sync_failed(be, "worklist")) return EK_CUDA;
+    if (be->bucket_gather && bucket_gather_supported(Tk, c.n_experts)) {
+      BucketGatherParams bg;
+      bg.permute = pp;
+      bg.worklist = wp;
+      bg.x = x; bg.xp = be->xp; bg.H = c.hidden;
+      bg.shared_t0 = opt.sh_t0; bg.shared_T = sh_T;
+      bg.to_f16 = f16_rows(be) ? 1 : 0;
+      be->launches += launch_bucket_gather(bg, be->n_sm, s);
+      if (debug_sync_failed(be, "bucketing + gather")) return EK_CUDA;
+      gathered = true;
+    } else {
+      be->launches += launch_permute(pp, s);
+      if (debug_sync_failed(be, "permute")) return EK_CUDA;
+      be->launches += launch_worklist(wp, s);
+      if (debug_sync_failed(be, "worklist")) return EK_CUDA;
+    }
   }
   if (!gathered) {
     be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T,
@@ -633,7 +659,7 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
     cp.T = T; cp.k = k; cp.H = c.hidden; cp.n_shared = 0; cp.Tk = Tk;
     cp.bf16_products = c.bf16_combine;
     cp.shared = nullptr;
-    be->launches += launch_combine_partial(cp, opt.partial, s);
+    be->launches += launch_combine_partial(cp, opt.partial, opt.signal, s);
   } else if (fused) {
     CombineParams cp;
     cp.obuf = be->obuf; cp.inv = be->inv; cp.weights = be->weights; cp.y = y;
@@ -795,8 +821,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
   CKC(cudaMalloc(&be->ep_counters, EK_EP_MAX_RANKS * sizeof(uint32_t)));
   CKC(cudaMemset(be->ep_counters, 0, EK_EP_MAX_RANKS * sizeof(uint32_t)));
-  CKC(cudaMalloc(&be->front_ticket, sizeof(uint32_t)));
-  CKC(cudaMemset(be->front_ticket, 0, sizeof(uint32_t)));
+  CKC(cudaMalloc(&be->front_ticket, 2 * sizeof(uint32_t)));
+  CKC(cudaMemset(be->front_ticket, 0, 2 * sizeof(uint32_t)));
   CKC(cudaMalloc(&be->sk_buf, ffn_tc_scratch_floats(be->n_sm) * sizeof(float)));
   CKC(cudaMalloc(&be->sk_flags, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
   CKC(cudaMemset(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
@@ -825,6 +851,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   if (prec && prec[0] == '1') be->precise = 1;
   const char* fs = getenv("EK_B200_FRONT_SMALL");
   if (fs && fs[0] == '0') be->front_small = 0;
+  const char* bgs = getenv("EK_B200_BUCKET_GATHER");
+  if (bgs && bgs[0] == '0') be->bucket_gather = 0;
   const char* sk = getenv("EK_B200_SPLIT_K");
   if (sk && sk[0] == '0') be->split_k = 0;
   *out = be;
@@ -1046,6 +1074,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
       rp.row0 = v * c.intermediate; rp.n_rows = c.intermediate;
       rp.col0 = 0; rp.n_cols = c.hidden;
       rp.esz = esz;
+      rp.xor_mask = c.quant == EK_QUANT_INT8_BLOCK128 ? 0x80808080u : 0u;
       rp.dst = gu0 + (size_t)m * kTileBytes;
       rp.rt_stride = (int64_t)d.kt_gu * 2 * kTileBytes;
       rp.kt_stride = 2 * kTileBytes;
@@ -1067,6 +1096,7 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     rp.row0 = 0; rp.n_rows = c.hidden;
     rp.col0 = v * c.intermediate; rp.n_cols = c.intermediate;
     rp.esz = esz;
+    rp.xor_mask = c.quant == EK_QUANT_INT8_BLOCK128 ? 0x80808080u : 0u;
     rp.dst = dn0;
     rp.rt_stride = 0; rp.kt_stride = 0;
     rp.rt_pairs = 1;                       // row tiles 2j, 2j+1 adjacent per K tile; an odd tail is zero-filled
@@ -2145,17 +2175,23 @@ int32_t ek_ep_peer_partial(ek_backend_t* be, int32_t layer, int32_t T, uint32_t 
   const size_t Ta = (size_t)T * c.ep_size;
   const size_t par = (size_t)(step & 1u) * Ta * H;
   uint32_t* my_flags = reinterpret_cast<uint32_t*>(pt.flags[c.ep_rank]);
-  be->launches += launch_ep_wait(my_flags, c.ep_size, step + 1, be->status, 500, be->stream);
   LayerOpts opt;
   opt.sh_t0 = c.ep_rank * T;
   opt.sh_T = T;
   opt.partial = reinterpret_cast<float*>(pt.partial[c.ep_rank]) + par;
+  // the wait for the peers' tokens rides on the first kernel of the pass, the signal that the partial
+  // sums are complete on the last one
+  opt.wait.flags = my_flags; opt.wait.world = c.ep_size; opt.wait.step_no = step + 1; opt.wait.where = 500;
+  PeerSignal sig;
+  for (int r = 0; r < EK_EP_MAX_RANKS; ++r) sig.flags.p[r] = r < c.ep_size ? pt.flags[r] : nullptr;
+  sig.world = c.ep_size; sig.slot = EK_EP_MAX_RANKS + c.ep_rank; sig.step_no = step + 1;
+  sig.ticket = be->front_ticket + 1;
+  opt.signal = &sig;
   be->ep_rows = (int)Ta * c.top_k;
   be->ep_T = T;
   rc = run_layer(be, li->second, reinterpret_cast<const __nv_bfloat16*>(pt.xall[c.ep_rank]) + par, (int)Ta, c.top_k, nullptr,
                  nullptr, nullptr, opt);
   if (rc != EK_OK) return rc;
-  be->launches += launch_ep_signal(pt.flags, c.ep_size, EK_EP_MAX_RANKS + c.ep_rank, step + 1, be->stream);
   CK(cudaGetLastError());
   return EK_OK;
 }

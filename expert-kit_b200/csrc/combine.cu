@@ -6,6 +6,7 @@
 // unpermute: out[t,s,:] = row of (t,s) -- NaiveExecutor's scatter + two-level stack
 // (ek-computation/src/controller/executor.rs:203-251).
 #include "ek_internal.h"
+#include "peer_sync.cuh"
 
 namespace ek {
 
@@ -127,7 +128,8 @@ __global__ void __launch_bounds__(128) unpermute_kernel(const __nv_bfloat16* __r
 }
 
 template <int BATCH>
-__global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, float* __restrict__ partial) {
+__global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, float* __restrict__ partial,
+                                                              const __grid_constant__ PeerSignal sig) {
   pdl_wait();
   pdl_trigger();
   __shared__ int s_row[kMaxK];
@@ -147,6 +149,7 @@ __global__ void __launch_bounds__(256) combine_partial_kernel(CombineParams p, f
     d[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     d[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
+  if (sig.world > 0) cta_signal_when_last(sig, gridDim.x * gridDim.y);
 }
 
 __global__ void __launch_bounds__(256) combine_finish_kernel(const float* __restrict__ reduced,
@@ -215,10 +218,11 @@ static int h_slices(int T, int H) {
   return parts < 1 ? 1 : parts;
 }
 
-int launch_combine_partial(const CombineParams& p, float* partial, cudaStream_t s) {
+int launch_combine_partial(const CombineParams& p, float* partial, const PeerSignal* sig, cudaStream_t s) {
+  const PeerSignal g = sig ? *sig : PeerSignal();
   if (p.T > 0) {
-    if (p.T < 1024) launch_pdl(combine_partial_kernel<8>, dim3(p.T, h_slices(p.T, p.H)), dim3(256), 0, s, p, partial);
-    else launch_pdl(combine_partial_kernel<2>, dim3(p.T, 1), dim3(256), 0, s, p, partial);
+    if (p.T < 1024) launch_pdl(combine_partial_kernel<8>, dim3(p.T, h_slices(p.T, p.H)), dim3(256), 0, s, p, partial, g);
+    else launch_pdl(combine_partial_kernel<2>, dim3(p.T, 1), dim3(256), 0, s, p, partial, g);
   }
   return p.T > 0 ? 1 : 0;
 }

@@ -117,6 +117,24 @@ struct RouteParams {
 };
 int launch_router_logits(const RouteParams& p, cudaStream_t s);
 
+// Expert-parallel step flags handed to a kernel instead of a launch of their own (peer_sync.cuh).
+struct PeerPtrs {
+  void* p[EK_EP_MAX_RANKS];
+};
+struct PeerWait {            // wait until every rank's flag word has reached step_no
+  const uint32_t* flags = nullptr;   // this rank's own flag words, one per rank; null: no wait
+  int32_t world = 0;
+  uint32_t step_no = 0;
+  int32_t where = 0;         // recorded in the device status on a timeout
+};
+struct PeerSignal {          // publish step_no into word `slot` of every rank's flags
+  PeerPtrs flags;
+  int32_t world = 0;         // 0: no signal
+  int32_t slot = 0;
+  uint32_t step_no = 0;
+  uint32_t* ticket = nullptr;   // zeroed counter that finds the last CTA
+};
+
 // Tensor-core router (router_tc.cu): split-K partial logits, summed by route_select.
 struct RouterTcParams {
   CUtensorMap x_map;        // activations [T,H] bf16, box {64, 128}, 128-byte swizzle
@@ -128,6 +146,7 @@ struct RouterTcParams {
   int32_t n_atoms;          // ceil(H / 64)
   int32_t n_splits, atoms_per_split;
   int32_t tmem_cols;        // power of two >= max(32, E)
+  PeerWait wait;            // expert parallel: x is written by the peers; wait for them first
 };
 bool router_tc_supported(int E, int H);
 void router_tc_plan(int T, int H, int n_sm, int* n_splits, int* atoms_per_split);
@@ -171,6 +190,21 @@ struct WorklistParams {
   DevStatus* status;
 };
 int launch_worklist(const WorklistParams& p, cudaStream_t s);
+
+// Offsets, permutation, work list and row gather in ONE launch for T*k <= 4096 and E <= 256
+// (permute.cu): every CTA repeats the cheap bucketing in shared memory, CTA 0 writes its results and
+// the work list, the others gather the rows.
+struct BucketGatherParams {
+  PermuteParams permute;
+  WorklistParams worklist;
+  const __nv_bfloat16* x;     // [T, H]
+  __nv_bfloat16* xp;          // out: permuted rows, then the shared expert's rows
+  int32_t H;
+  int32_t shared_t0, shared_T;
+  int32_t to_f16;
+};
+bool bucket_gather_supported(int Tk, int E);
+int launch_bucket_gather(const BucketGatherParams& p, int n_sm, cudaStream_t s);
 
 // Router + bucketing + work list (+ gather of a handful of rows) in one launch for small batches
 // (front_small.cu).  `route.wg` must be the bf16 router weight; `route.partial` is unused, the
@@ -247,7 +281,8 @@ int launch_combine(const CombineParams& p, cudaStream_t s);
 // Expert-parallel partial sums: partial[t,:] = sum over the slots whose expert is local of
 // w[t,k] * out[t,k,:] in fp32 (no shared expert, no rounding); and the finish after the
 // cross-rank sum: y[i,:] = bf16(reduced[i,:]) + shared rows.
-int launch_combine_partial(const CombineParams& p, float* partial, cudaStream_t s);
+// `sig` (may be null): the CTA that finishes last tells every rank that the partial sums are complete.
+int launch_combine_partial(const CombineParams& p, float* partial, const PeerSignal* sig, cudaStream_t s);
 int launch_combine_finish(const float* reduced, const __nv_bfloat16* shared, int32_t n_shared, int32_t T,
                           int32_t H, __nv_bfloat16* y, cudaStream_t s);
 // out[t,s,:] = obuf[inv[t*k+s]]
@@ -261,7 +296,6 @@ struct RowSegment {
 int launch_ep_push(const __nv_bfloat16* x, int32_t T, int32_t H, void* const* xall, void* const* flags, int32_t world,
                    int32_t rank, uint32_t step_no, size_t dst_elem_off, uint32_t* counters, cudaStream_t s);
 int launch_ep_wait(const uint32_t* flags, int32_t world, uint32_t step_no, DevStatus* st, int32_t where, cudaStream_t s);
-int launch_ep_signal(void* const* flags, int32_t world, int32_t slot, uint32_t step_no, cudaStream_t s);
 int launch_ep_pull_finish(void* const* partial, size_t src_elem_off, int32_t world, const uint32_t* my_flags,
                           uint32_t step_no, const __nv_bfloat16* shared, int32_t n_shared, int32_t T, int32_t H,
                           __nv_bfloat16* y, DevStatus* st, cudaStream_t s);
@@ -281,6 +315,7 @@ struct RetileParams {
   int64_t rt_stride;      // bytes between consecutive row tiles
   int64_t kt_stride;      // bytes between consecutive K tiles
   int32_t n_rt, n_kt;     // tiles to write (padding tiles are zero-filled)
+  uint32_t xor_mask = 0;  // applied to every 32-bit word written: 0x80808080 turns int8 codes into offset binary
 };
 int launch_retile(const RetileParams& p, cudaStream_t s);
 struct ScaleRetileParams {

@@ -12,35 +12,13 @@
 // words (release at system scope after the data) and polled locally (acquire at system scope).
 // Plain loads and stores only: no TMA on peer memory, no multimem.  Every wait is bounded.
 #include "ek_internal.h"
+#include "peer_sync.cuh"
 
 namespace ek {
 
 namespace {
 
 constexpr int kMaxRanks = EK_EP_MAX_RANKS;
-constexpr uint32_t kPollLimit = 1u << 20;   // polls with a ~100 ns back-off: about a second
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// Waits until flag >= want; false after the poll limit.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want) {
-  for (uint32_t i = 0; i < kPollLimit; ++i) {
-    if (ld_acquire_sys(flag) >= want) return true;
-    if (i > 64) __nanosleep(100);
-  }
-  return false;
-}
-
-struct PeerPtrs {
-  void* p[kMaxRanks];
-};
 
 // grid (world, slices): CTA (dst, s) copies its share of this rank's rows into rank dst's buffer;
 // the last CTA of a destination publishes the step number there.
@@ -71,31 +49,12 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const __nv_bfloat16* __res
   }
 }
 
-// One warp: lane r waits for rank r's step number in this rank's own flag words.
-__global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int32_t world, uint32_t step_no, DevStatus* st,
-                               int32_t where) {
+// One warp: lane r waits for rank r's step number in this rank's own flag words (for passes whose
+// first kernel cannot take the wait along).
+__global__ void ep_wait_kernel(PeerWait w, DevStatus* st) {
   pdl_wait();
   pdl_trigger();
-  const int r = threadIdx.x;
-  if (r < world && !wait_flag(flags + r, step_no)) {
-    if (atomicCAS(&st->code, DEV_OK, DEV_TIMEOUT) == DEV_OK) {
-      st->where = where;
-      st->aux0 = r;
-      st->aux1 = (int)step_no;
-    }
-  }
-}
-
-// Tells every rank that this rank's partial sums of the step are complete (they were written by the
-// kernels before this one on the stream).
-__global__ void ep_signal_kernel(PeerPtrs flags, int32_t world, int32_t slot, uint32_t step_no) {
-  pdl_wait();
-  pdl_trigger();
-  const int r = threadIdx.x;
-  if (r < world) {
-    __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(flags.p[r]) + slot, step_no);
-  }
+  warp_wait_ranks(w, st, threadIdx.x);
 }
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -198,12 +157,9 @@ int launch_ep_push(const __nv_bfloat16* x, int32_t T, int32_t H, void* const* xa
 }
 
 int launch_ep_wait(const uint32_t* flags, int32_t world, uint32_t step_no, DevStatus* st, int32_t where, cudaStream_t s) {
-  launch_pdl(ep_wait_kernel, dim3(1), dim3(32), 0, s, flags, world, step_no, st, where);
-  return 1;
-}
-
-int launch_ep_signal(void* const* flags, int32_t world, int32_t slot, uint32_t step_no, cudaStream_t s) {
-  launch_pdl(ep_signal_kernel, dim3(1), dim3(32), 0, s, ptrs_of(flags, world), world, slot, step_no);
+  PeerWait w;
+  w.flags = flags; w.world = world; w.step_no = step_no; w.where = where;
+  launch_pdl(ep_wait_kernel, dim3(1), dim3(32), 0, s, w, st);
   return 1;
 }
 

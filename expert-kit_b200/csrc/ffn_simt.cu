@@ -35,7 +35,7 @@ __device__ __forceinline__ void decode16(const uint4& raw, float scale, float* o
         q.__x = b[i];
         v = static_cast<float>(q);
       } else {
-        v = static_cast<float>(static_cast<int8_t>(b[i]));
+        v = static_cast<float>(static_cast<int>(b[i]) - 128);   // tiles keep int8 codes in offset binary
       }
       out[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v, scale)));
     }

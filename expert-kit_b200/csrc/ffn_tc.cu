@@ -197,12 +197,11 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<unsigned short>(two_bytes)));
   return r;
 }
-// four int8 -> four f16, exact: 0x6400 | (b ^ 0x80) is the f16 value 1024 + (b + 128); subtract 1152
+// four int8 codes in offset binary (u = b ^ 0x80 = b + 128, as the tiles keep them) -> four f16, exact:
+// 0x6400 | u is the f16 value 1024 + u; subtract 1152
 __device__ __forceinline__ void s8x4_to_f16(uint32_t w, uint32_t* out) {
-  const uint32_t lo = __byte_perm(w, 0x64646464u, 0x4140) ^ 0x00800080u;
-  const uint32_t hi = __byte_perm(w, 0x64646464u, 0x4342) ^ 0x00800080u;
-  out[0] = sub_f16x2(lo, 0x64806480u);
-  out[1] = sub_f16x2(hi, 0x64806480u);
+  out[0] = sub_f16x2(__byte_perm(w, 0x64646464u, 0x4140), 0x64806480u);
+  out[1] = sub_f16x2(__byte_perm(w, 0x64646464u, 0x4342), 0x64806480u);
 }
 __device__ __forceinline__ float2 f16x2_to_float2(uint32_t v) {
   return __half22float2(*reinterpret_cast<const __half2*>(&v));
@@ -220,10 +219,10 @@ __device__ __forceinline__ void cvt_word(uint32_t w, float scale, uint32_t s_hi,
       out[0] = pack_bf16(__fmul_rn(a.x, scale), __fmul_rn(a.y, scale));
       out[1] = pack_bf16(__fmul_rn(b.x, scale), __fmul_rn(b.y, scale));
     } else {
-      const float f0 = static_cast<float>(static_cast<int>(static_cast<int8_t>(w & 0xff)));
-      const float f1 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 8) & 0xff)));
-      const float f2 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 16) & 0xff)));
-      const float f3 = static_cast<float>(static_cast<int>(static_cast<int8_t>((w >> 24) & 0xff)));
+      const float f0 = static_cast<float>(static_cast<int>(w & 0xff) - 128);           // offset binary
+      const float f1 = static_cast<float>(static_cast<int>((w >> 8) & 0xff) - 128);
+      const float f2 = static_cast<float>(static_cast<int>((w >> 16) & 0xff) - 128);
+      const float f3 = static_cast<float>(static_cast<int>(w >> 24) - 128);
       out[0] = pack_bf16(__fmul_rn(f0, scale), __fmul_rn(f1, scale));
       out[1] = pack_bf16(__fmul_rn(f2, scale), __fmul_rn(f3, scale));
     }

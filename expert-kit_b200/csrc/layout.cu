@@ -1,5 +1,6 @@
 // Registration-time layout kernels: re-tile row-major expert weights into the 16 KiB tiles
-// the GEMM kernels stream, re-order the block scales to match, and the stand-alone block
+// the GEMM kernels stream (int8 codes are kept in offset binary, b ^ 0x80, which saves the GEMM's
+// converters an instruction per weight pair), re-order the block scales to match, and the stand-alone block
 // dequantisation (w8a16_activate, ek-computation/src/ffn/expert_torch.rs:24-53).
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -36,6 +37,7 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileParams p) {
         v = *reinterpret_cast<uint4*>(tmp);
       }
     }
+    v.x ^= p.xor_mask; v.y ^= p.xor_mask; v.z ^= p.xor_mask; v.w ^= p.xor_mask;   // padding zeros become code 0 too
     *reinterpret_cast<uint4*>(tile + (size_t)(j * kTileRows + r) * 16) = v;
   }
 }

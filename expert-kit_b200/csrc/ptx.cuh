@@ -101,6 +101,10 @@ __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// all state spaces: orders generic-proxy accesses (global memory included) with later TMA accesses
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 
 // ---- tcgen05: tensor memory --------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

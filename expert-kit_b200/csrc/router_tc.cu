@@ -8,6 +8,7 @@
 // router weights that are exactly representable in bf16 (products of bf16 values are exact in
 // fp32, so only the summation order differs from an fp32 evaluation).
 #include "ek_internal.h"
+#include "peer_sync.cuh"
 #include "ptx.cuh"
 
 namespace ek {
@@ -56,8 +57,18 @@ __global__ void __launch_bounds__(192, 1) router_tc_kernel(const __grid_constant
   const int a_hi = min(a_lo + p.atoms_per_split, p.n_atoms);
   const int n_it = a_hi - a_lo;
 
+  if (p.wait.flags) {
+    // the activations are stored by the peers: every rank's step number first (one warp, a lane per
+    // rank), then the TMA reads (async proxy) are ordered behind the acquiring loads (generic proxy)
+    if (warp == 4) {
+      if (!warp_wait_ranks(p.wait, p.status, lane) && lane == 0) *abortp = 1;
+      fence_proxy_async_all();
+    }
+    __syncthreads();
+  }
+  const bool go = *abortp == 0;
   if (warp == 4) {
-    if (lane == 0) {
+    if (lane == 0 && go) {
       for (int i = 0; i < n_it; ++i) {
         const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
         if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp)) break;
@@ -76,7 +87,7 @@ __global__ void __launch_bounds__(192, 1) router_tc_kernel(const __grid_constant
         }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    if (lane == 0 && go) {
       const uint32_t idesc = umma_idesc_bf16(p.E);
       bool ok = true;
       for (int i = 0; i < n_it; ++i) {
@@ -96,7 +107,7 @@ __global__ void __launch_bounds__(192, 1) router_tc_kernel(const __grid_constant
     }
   } else {
     // epilogue: thread = token row, 16 experts per tcgen05.ld
-    if (n_it > 0) {
+    if (n_it > 0 && go) {
       if (mbar_wait(smem_u32(&bar_acc), 0, abortp)) {
         tc_fence_after();
         const int t = m0 + warp * 32 + lane;

@@ -19,7 +19,7 @@ STATUS_NAMES = {
 EK_BF16, EK_F32, EK_F8_E4M3, EK_I8, EK_I32, EK_F16, EK_U8, EK_I64 = range(8)
 EK_SCORE_SOFTMAX, EK_SCORE_SIGMOID = 0, 1
 EK_QUANT_BF16, EK_QUANT_FP8_BLOCK128, EK_QUANT_INT8_BLOCK128 = 0, 1, 2
-EK_TILE_LAYOUT_VERSION = 4   # include/ek_b200.h
+EK_TILE_LAYOUT_VERSION = 5   # include/ek_b200.h
 EK_EP_MAX_RANKS = 16
 
 

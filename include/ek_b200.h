@@ -135,14 +135,14 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id,
 int32_t ek_expert_register_safetensors(ek_backend_t* be, const char* id,
                                        const void* blob, size_t blob_len);
 
-/* The expert as this library keeps it in HBM (16 KiB tiles, re-encoded FP8 bytes, re-ordered
- * scales), for a cache next to the raw bundle in the weight server's file cache
+/* The expert as this library keeps it in HBM (16 KiB tiles, int8 codes in offset binary, re-ordered
+ * scales and the per-expert powers of two), for a cache next to the raw bundle in the weight server's file cache
  * (ek-db/src/safetensor/mod.rs:144-171): a restart registers the blob with plain copies and skips
  * decoding and re-tiling.  The blob is only valid for the same quant/hidden/intermediate and for
  * EK_TILE_LAYOUT_VERSION; anything else is refused (EK_UNSUPPORTED / EK_INVALID_INPUT) and the
  * caller falls back to the bundle.  *needed receives the blob size; EK_INVALID_INPUT when `cap`
  * is too small. */
-#define EK_TILE_LAYOUT_VERSION 4
+#define EK_TILE_LAYOUT_VERSION 5
 int32_t ek_expert_export_tiles(ek_backend_t* be, const char* id, void* blob, size_t cap, size_t* needed);
 int32_t ek_expert_register_tiles(ek_backend_t* be, const char* id, const void* blob, size_t blob_len);
 
@@ -281,11 +281,14 @@ int64_t ek_kernel_launches(const ek_backend_t* be);
  * `calls` = requests served so far, `batches` = grouped passes that served them. */
 int32_t ek_worker_batch_stats(ek_backend_t* be, int64_t* calls, int64_t* batches);
 
-/* FP8 block scales inside the grouped GEMM.  0 (default): the scale is split into two bf16
- * terms and applied with packed bf16 arithmetic (16 significant bits of the scale, one final
- * rounding; equals the reference formula except within 2^-17 of a rounding boundary).  1: applied
- * in fp32 with one rounding, bit-exact w8a16_activate (ek-computation/src/ffn/expert_torch.rs:24-53)
- * at roughly a third of the weight-streaming rate.  ek_w8a16_activate itself is always exact. */
+/* FP8 / INT8 block scales inside the grouped GEMM.  0 (default): the weight codes are converted
+ * exactly to f16 and both MMA operands are f16 (the activations of these GEMMs are kept in f16 from
+ * the row gather on); the block scale, times a per-expert power of two that the epilogue takes out
+ * again, is applied to the activation tile (chunks of <= 64 rows) or to the weight operand (128-row
+ * chunks) with one rounding to 11 bits per element, where the reference's bf16(w * s) rounds to 8.
+ * 1: bf16 operands with A = bf16_rne(float(w) * s), bit-exact w8a16_activate
+ * (ek-computation/src/ffn/expert_torch.rs:24-53), at roughly a third of the weight-streaming rate.
+ * ek_w8a16_activate itself is always exact. */
 int32_t ek_set_precise_dequant(ek_backend_t* be, int32_t on);
 
 /* Test hook: 0 = tensor-core kernels (default), 1 = the CUDA-core evaluation of the same
