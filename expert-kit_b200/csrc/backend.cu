@@ -113,7 +113,6 @@ struct ek_backend {
   DevStatus* status = nullptr;
   uint32_t* front_ticket = nullptr;    // last-CTA tickets: [0] fused small-batch front kernel, [1] expert-parallel signal
   int front_small = 1;                 // use that kernel when the batch qualifies
-  int bucket_gather = 1;               // bucketing + work list + gather in one launch when T*k <= 4096
   float* sk_buf = nullptr;             // partial accumulators of K-split work items
   uint32_t* sk_flags = nullptr;
   int split_k = 1;
@@ -426,8 +425,13 @@ bool f16_rows(const ek_backend* be) {
 }
 
 int pick_nmax(int rows, int n_segments) {
+  // EK_B200_NMAX=32|64|128 forces the chunk size (measurement only)
+  static const int forced = getenv("EK_B200_NMAX") ? atoi(getenv("EK_B200_NMAX")) : 0;
+  if (forced == 32 || forced == 64 || forced == 128) return forced;
   const int avg = n_segments > 0 ? (rows + n_segments - 1) / n_segments : rows;
-  return avg <= 20 ? 32 : avg <= 48 ? 64 : 128;
+  // measured on the DeepSeek-V3-shape layer (Zipf-skewed load): 32-row chunks win up to 24 rows per
+  // expert on average, 128-row chunks from 32 on; the 64-row variant only in between
+  return avg <= 24 ? 32 : avg < 32 ? 64 : 128;
 }
 
 // Event i of the current pass; the last one closes the pass.
@@ -623,22 +627,10 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
       be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
     }
     mark(be, 1);
-    if (be->bucket_gather && bucket_gather_supported(Tk, c.n_experts)) {
-      BucketGatherParams bg;
-      bg.permute = pp;
-      bg.worklist = wp;
-      bg.x = x; bg.xp = be->xp; bg.H = c.hidden;
-      bg.shared_t0 = opt.sh_t0; bg.shared_T = sh_T;
-      bg.to_f16 = f16_rows(be) ? 1 : 0;
-      be->launches += launch_bucket_gather(bg, be->n_sm, s);
-      if (debug_sync_failed(be, "bucketing + gather")) return EK_CUDA;
-      gathered = true;
-    } else {
-      be->launches += launch_permute(pp, s);
-      if (debug_sync_failed(be, "permute")) return EK_CUDA;
-      be->launches += launch_worklist(wp, s);
-      if (debug_sync_failed(be, "worklist")) return EK_CUDA;
-    }
+    be->launches += launch_permute(pp, s);
+    if (debug_sync_failed(be, "permute")) return EK_CUDA;
+    be->launches += launch_worklist(wp, s);
+    if (debug_sync_failed(be, "worklist")) return EK_CUDA;
   }
   if (!gathered) {
     be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T,
@@ -851,8 +843,6 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   if (prec && prec[0] == '1') be->precise = 1;
   const char* fs = getenv("EK_B200_FRONT_SMALL");
   if (fs && fs[0] == '0') be->front_small = 0;
-  const char* bgs = getenv("EK_B200_BUCKET_GATHER");
-  if (bgs && bgs[0] == '0') be->bucket_gather = 0;
   const char* sk = getenv("EK_B200_SPLIT_K");
   if (sk && sk[0] == '0') be->split_k = 0;
   *out = be;

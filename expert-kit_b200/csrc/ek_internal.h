@@ -191,21 +191,6 @@ struct WorklistParams {
 };
 int launch_worklist(const WorklistParams& p, cudaStream_t s);
 
-// Offsets, permutation, work list and row gather in ONE launch for T*k <= 4096 and E <= 256
-// (permute.cu): every CTA repeats the cheap bucketing in shared memory, CTA 0 writes its results and
-// the work list, the others gather the rows.
-struct BucketGatherParams {
-  PermuteParams permute;
-  WorklistParams worklist;
-  const __nv_bfloat16* x;     // [T, H]
-  __nv_bfloat16* xp;          // out: permuted rows, then the shared expert's rows
-  int32_t H;
-  int32_t shared_t0, shared_T;
-  int32_t to_f16;
-};
-bool bucket_gather_supported(int Tk, int E);
-int launch_bucket_gather(const BucketGatherParams& p, int n_sm, cudaStream_t s);
-
 // Router + bucketing + work list (+ gather of a handful of rows) in one launch for small batches
 // (front_small.cu).  `route.wg` must be the bf16 router weight; `route.partial` is unused, the
 // kernel keeps its K-slice partial logits in `partial` ([slices][T][E]).

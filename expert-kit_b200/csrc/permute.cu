@@ -1,7 +1,6 @@
 // Bucketing: exclusive scan of the per-expert histogram, stable ranking of the flattened
 // [T*k] assignments by expert (ascending token order inside an expert), the inverse map, the
-// chunk work list for the grouped GEMMs and the row gather -- as separate kernels for any size and
-// as one launch (bucket_gather_kernel) up to 4096 assignments.
+// chunk work list for the grouped GEMMs and the row gather.
 //
 // Semantics follow NaiveExecutor::break_down_to_egress / assemble_seq_tensors
 // (ek-computation/src/controller/executor.rs:283-299,112-133): a stable counting sort.
@@ -126,127 +125,6 @@ __global__ void __launch_bounds__(128) gather_kernel(const __nv_bfloat16* __rest
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = F16 ? bf16x8_to_f16x8(s[v]) : s[v];
 }
 
-// Bucketing and gather in one launch.  Every CTA computes the permutation of all T*k assignments
-// in shared memory (a stable counting sort: per-warp histograms over contiguous segments, a prefix
-// over (expert, warp), then ranks inside a warp's round from match_any): that is a few microseconds
-// and saves a grid-wide hand-over.  CTA 0 writes offsets / perm / inv and builds the work list; CTAs
-// 1.. copy the rows, one warp per row.
-constexpr int kBgMaxTk = 4096, kBgMaxE = 256, kBgWarps = 32;
-
-__global__ void __launch_bounds__(1024) bucket_gather_kernel(const __grid_constant__ BucketGatherParams p) {
-  extern __shared__ int bg_smem[];
-  int* s_ids = bg_smem;                       // [kBgMaxTk]
-  int* s_perm = s_ids + kBgMaxTk;             // [kBgMaxTk]
-  int* s_wh = s_perm + kBgMaxTk;              // [kBgWarps][kBgMaxE] histogram, then running base
-  int* s_off = s_wh + kBgWarps * kBgMaxE;     // [kBgMaxE + 1]
-  int* s_loc = s_off + kBgMaxE + 1;           // [kBgMaxE] expert served by this rank?
-  const PermuteParams& pp = p.permute;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int E = pp.E, Tk = pp.T * pp.k;
-  pdl_wait();
-  pdl_trigger();
-  for (int i = tid; i < kBgWarps * kBgMaxE; i += 1024) s_wh[i] = 0;
-  for (int i = tid; i < Tk; i += 1024) s_ids[i] = pp.ids[i];
-  if (tid < E) s_loc[tid] = pp.owners ? pp.owners[tid] == pp.rank : (tid >= pp.e_lo && tid < pp.e_hi);
-  __syncthreads();
-  // per-warp histograms over contiguous segments of the assignment list
-  const int seg = (Tk + kBgWarps - 1) / kBgWarps;
-  const int i_lo = warp * seg, i_hi = min(Tk, i_lo + seg);
-  for (int i = i_lo + lane; i < i_hi; i += 32) {
-    const int e = s_ids[i];
-    if (e >= 0 && e < E && s_loc[e]) atomicAdd(&s_wh[warp * kBgMaxE + e], 1);
-  }
-  __syncthreads();
-  // exclusive scan over the experts (warp 0, eight experts per lane) of the totals
-  if (warp == 0) {
-    int v[8], sum = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = lane * 8 + j;
-      int c = 0;
-      if (e < E)
-        for (int w = 0; w < kBgWarps; ++w) c += s_wh[w * kBgMaxE + e];
-      v[j] = c;
-      sum += c;
-    }
-    int inc = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int u = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += u;
-    }
-    int run = inc - sum;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = lane * 8 + j;
-      if (e < E) s_off[e] = run;
-      run += v[j];
-    }
-    if (lane == 31) s_off[E] = inc;
-  }
-  __syncthreads();
-  // base position of (warp, expert): rows of an expert are in ascending assignment order
-  if (tid < E) {
-    int run = s_off[tid];
-    for (int w = 0; w < kBgWarps; ++w) {
-      const int c = s_wh[w * kBgMaxE + tid];
-      s_wh[w * kBgMaxE + tid] = run;
-      run += c;
-    }
-  }
-  __syncthreads();
-  for (int i0 = i_lo; i0 < i_hi; i0 += 32) {
-    const int i = i0 + lane;
-    const int e = i < i_hi ? s_ids[i] : -1;
-    const bool local = e >= 0 && e < E && s_loc[e];
-    const unsigned m = __match_any_sync(0xffffffffu, local ? e : -1);
-    const int rank = __popc(m & ((1u << lane) - 1u));
-    int pos = -1;
-    if (local) {
-      pos = s_wh[warp * kBgMaxE + e] + rank;
-      s_perm[pos] = i;
-    }
-    __syncwarp();
-    if (local && rank == 0) s_wh[warp * kBgMaxE + e] += __popc(m);
-    __syncwarp();
-    if (blockIdx.x == 0 && i < i_hi) pp.inv[i] = pos;
-  }
-  __syncthreads();
-  const int n_routed = s_off[E];
-  if (blockIdx.x == 0) {
-    for (int e = tid; e <= E; e += 1024) pp.offsets[e] = s_off[e];
-    for (int r = tid; r < n_routed; r += 1024) pp.perm[r] = s_perm[r];
-    __syncthreads();
-    build_worklist(p.worklist);
-    if (gridDim.x > 1) return;
-  }
-  // gather: one warp per row, CTAs 1.. (all of them when the grid is a single CTA)
-  const int n_gather = gridDim.x > 1 ? (int)gridDim.x - 1 : 1;
-  const int me = gridDim.x > 1 ? (int)blockIdx.x - 1 : 0;
-  const int rows = Tk + p.shared_T;
-  const int nv = p.H / 8;
-  for (int row = me * kBgWarps + warp; row < rows; row += n_gather * kBgWarps) {
-    int src;
-    if (row < Tk) {
-      if (row >= n_routed) continue;            // rows of experts served elsewhere are not materialised
-      src = s_perm[row] / pp.k;
-    } else {
-      src = p.shared_t0 + row - Tk;
-    }
-    const uint4* sv = reinterpret_cast<const uint4*>(p.x + (size_t)src * p.H);
-    uint4* dv = reinterpret_cast<uint4*>(p.xp + (size_t)row * p.H);
-    for (int v0 = lane; v0 < nv; v0 += 128) {
-      uint4 t[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (v0 + 32 * j < nv) t[j] = sv[v0 + 32 * j];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (v0 + 32 * j < nv) dv[v0 + 32 * j] = p.to_f16 ? bf16x8_to_f16x8(t[j]) : t[j];
-    }
-  }
-}
-
 __global__ void __launch_bounds__(128) rows_to_f16_kernel(__nv_bfloat16* rows, int32_t H) {
   uint4* d = reinterpret_cast<uint4*>(rows + (size_t)blockIdx.x * H);
   for (int v = threadIdx.x; v < H / 8; v += blockDim.x) d[v] = bf16x8_to_f16x8(d[v]);
@@ -273,18 +151,6 @@ int launch_gather(const __nv_bfloat16* x, const int32_t* perm, const int32_t* n_
     else launch_pdl(gather_kernel<false>, dim3(rows), dim3(128), 0, s, x, perm, n_routed, xp, T, k, H, shared_t0);
   }
   return rows > 0 ? 1 : 0;
-}
-
-bool bucket_gather_supported(int Tk, int E) { return Tk >= 1 && Tk <= kBgMaxTk && E >= 1 && E <= kBgMaxE; }
-
-int launch_bucket_gather(const BucketGatherParams& p, int n_sm, cudaStream_t s) {
-  const int rows = p.permute.T * p.permute.k + p.shared_T;
-  int gather_ctas = (rows + kBgWarps - 1) / kBgWarps;
-  if (gather_ctas > n_sm - 1) gather_ctas = n_sm - 1;
-  const size_t smem = sizeof(int) * (2 * kBgMaxTk + kBgWarps * kBgMaxE + 2 * kBgMaxE + 1);
-  cudaFuncSetAttribute(bucket_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(bucket_gather_kernel, dim3(1 + gather_ctas), dim3(1024), smem, s, p);
-  return 1;
 }
 
 int launch_rows_to_f16(__nv_bfloat16* rows, int64_t n_rows, int32_t H, cudaStream_t s) {

@@ -30,28 +30,28 @@ __device__ __forceinline__ void select_token(const RouteParams& p, int t, int la
   const int E = p.E;
   if (p.partial) {
     // add the split-K partial sums in split order; the softmax path works on bf16 logits like the
-    // reference's bf16 linear layer.  Four experts per lane and four splits per round: 16
-    // independent loads in flight instead of one dependent chain per expert.
-    for (int e0 = lane; e0 < E; e0 += 128) {
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int k0 = 0; k0 < p.n_partials; k0 += 4) {
-        float tmp[4][4];
+    // reference's bf16 linear layer.  Eight experts per lane and eight splits per round: 64
+    // independent loads in flight (the loads are what this step costs: a round trip to L2 each round).
+    for (int e0 = lane; e0 < E; e0 += 256) {
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k0 = 0; k0 < p.n_partials; k0 += 8) {
+        float tmp[8][8];
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int a = 0; a < 8; ++a)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < 8; ++j) {
             const int e = e0 + 32 * j;
             tmp[a][j] = (k0 + a < p.n_partials && e < E) ? __ldcg(&p.partial[((size_t)(k0 + a) * p.T + t) * E + e]) : 0.f;
           }
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int a = 0; a < 8; ++a)
           if (k0 + a < p.n_partials) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] += tmp[a][j];
+            for (int j = 0; j < 8; ++j) v[j] += tmp[a][j];
           }
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         const int e = e0 + 32 * j;
         if (e < E) lg[e] = p.scoring == EK_SCORE_SOFTMAX ? __bfloat162float(__float2bfloat16_rn(v[j])) : v[j];
       }
