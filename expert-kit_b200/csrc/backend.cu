@@ -425,9 +425,6 @@ bool f16_rows(const ek_backend* be) {
 }
 
 int pick_nmax(int rows, int n_segments) {
-  // EK_B200_NMAX=32|64|128 forces the chunk size (measurement only)
-  static const int forced = getenv("EK_B200_NMAX") ? atoi(getenv("EK_B200_NMAX")) : 0;
-  if (forced == 32 || forced == 64 || forced == 128) return forced;
   const int avg = n_segments > 0 ? (rows + n_segments - 1) / n_segments : rows;
   // measured on the DeepSeek-V3-shape layer (Zipf-skewed load): 32-row chunks win up to 24 rows per
   // expert on average, 128-row chunks from 32 on; the 64-row variant only in between
@@ -837,10 +834,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
     fail(be, EK_CUDA, "device synchronisation failed after workspace set-up");
     return cleanup_fail(EK_CUDA);
   }
-  const char* impl = getenv("EK_B200_FFN_IMPL");
-  if (impl && std::string(impl) == "simt") be->ffn_impl = 1;
-  const char* prec = getenv("EK_B200_PRECISE_DEQUANT");
-  if (prec && prec[0] == '1') be->precise = 1;
+  // measurement switches (they take single kernels out of the pass to time what each is worth; the
+  // results are the same either way): EK_B200_FRONT_SMALL=0, EK_B200_SPLIT_K=0
   const char* fs = getenv("EK_B200_FRONT_SMALL");
   if (fs && fs[0] == '0') be->front_small = 0;
   const char* sk = getenv("EK_B200_SPLIT_K");
@@ -1333,7 +1328,7 @@ int32_t ek_router_register(ek_backend_t* be, int32_t layer, const void* weight, 
   // tensor-core router: needs the weight in bf16 without loss
   if (L->router_bf16_owned) cudaFree(L->router_bf16);
   L->router_bf16 = nullptr; L->router_bf16_owned = false; L->router_tc = false;
-  if (router_tc_supported(be->cfg.n_experts, be->cfg.hidden) && !getenv("EK_B200_SIMT_ROUTER")) {
+  if (router_tc_supported(be->cfg.n_experts, be->cfg.hidden)) {
     if (dt == EK_BF16) {
       L->router_bf16 = reinterpret_cast<__nv_bfloat16*>(L->router_w);
     } else {

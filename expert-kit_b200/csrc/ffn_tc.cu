@@ -104,9 +104,13 @@ struct Cfg {
   static constexpr int NW = NCH * WPC;
   static constexpr bool SCALE_B = MODE == kModeScaleB2;
   static constexpr bool F16 = MODE == kModeScaleB2 || MODE == kModeScaleAH;   // both MMA operands f16, h written as f16
-  // tensor memory: two accumulators of NMAX columns, the rest is a ring of A staging slots (an
-  // even number, shared by the two chains): 6 slots for the decode variants, 4 at NMAX = 128
-  static constexpr int A_BASE = 2 * NMAX;
+  // tensor memory: two accumulators of NMAX columns (one per chain) - twice that in the 32-row
+  // variant, where consecutive work items alternate between two accumulator sets so that the
+  // epilogue of an item can be put off behind the first conversions of the next one - and the rest
+  // is a ring of A staging slots (an even number, shared by the two chains): 6 slots for the decode
+  // variants, 4 at NMAX = 128
+  static constexpr int ACC_BUFS = NMAX <= 32 ? 2 : 1;
+  static constexpr int A_BASE = ACC_BUFS * 2 * NMAX;
   static constexpr int A_SLOTS_RAW = ((kTmemCols - A_BASE) / kASlotCols) & ~1;
   static constexpr int A_SLOTS = A_SLOTS_RAW > kMaxASlots ? kMaxASlots : A_SLOTS_RAW;
   static constexpr int A_PER = A_SLOTS / 2;                       // slots per chain
@@ -285,14 +289,153 @@ __device__ __forceinline__ void tmem_ld_pair_wait(uint32_t ta, uint32_t tb, uint
   else tmem_ld8x2_wait(ta, tb, a, b);
 }
 
+// A finished work item whose epilogue is still to run.
+struct Pending {
+  ChunkDesc cd;
+  int rt, N, item, kt0, kt1, n_follow;
+  float out_pow;
+  uint32_t n;            // index of the item in this CTA's sequence
+};
+
+// The epilogue of a finished work item: tensor memory -> (partial sums of split items) -> SwiGLU or
+// plain rounding -> global memory.  In the variants with two accumulator sets it runs behind the
+// warp's first conversion step of the NEXT item (or behind the last item): the converters - the unit
+// that sets the pace of this kernel - then do not sit out the latency of the item's last MMAs, and
+// the MMA chains go straight on into the other accumulator set.  Not inlined: the converters' K loop
+// stays small.
+template <int QUANT, bool GATEUP, int NMAX, int MODE>
+__device__ __noinline__ bool run_epilogue(const FfnParams& p, const Pending& e, uint32_t tmem, uint64_t* bar_accfull,
+                                          uint64_t* bar_accempty, volatile int* abortp) {
+  using C = Cfg<QUANT, GATEUP, NMAX, MODE>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = warp & 3;
+  const int r = q * 32 + lane;
+  const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+    const uint32_t ab = C::ACC_BUFS == 2 ? (e.n & 1u) : 0u;
+    const uint32_t ause = C::ACC_BUFS == 2 ? (e.n >> 1) : e.n;
+    if (!mbar_wait(smem_u32(&bar_accfull[ab]), ause & 1u, abortp)) {
+      report(p.status, DEV_TIMEOUT, 302, e.item, 0);
+      return false;
+    }
+    const ChunkDesc& cd = e.cd;
+    const int rt = e.rt, N = e.N;
+    const float out_pow = e.out_pow;
+    const uint32_t acc_base = lane_base + ab * (2 * NMAX);
+    tc_fence_after();
+    // a split item: parts that do not start at K step 0 leave their accumulators in the scratch
+    // buffer; the part that does adds them, in part order, before the epilogue proper
+    const bool part_write = e.kt0 > 0;
+    const int n_follow = e.n_follow;
+    float* const sk_mine = p.sk_buf + (size_t)blockIdx.x * (2 * NMAX * 128);
+    if (n_follow > 0) {
+      int got = 1;
+      if (lane == 0) {
+        for (int j = 1; j <= n_follow && got; ++j) {
+          const uint32_t* f = p.sk_flags + ((size_t)blockIdx.x + j) * 32 + warp;
+          got = 0;
+          for (uint32_t poll = 0; poll < (1u << 21); ++poll) {
+            if (ld_acquire_gpu(f) != 0u) { got = 1; break; }
+            if (poll > 64) __nanosleep(100);
+            if ((poll & 1023u) == 1023u && *abortp) break;
+          }
+        }
+      }
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0) {
+          report(p.status, DEV_TIMEOUT, 304, e.item, e.kt1);
+          *abortp = 1;
+        }
+        return false;
+      }
+    }
+    // gate/up: this thread owns intermediate feature rt*128 + r (gate in accumulator 0, up in 1);
+    // down: hidden features (2*rt)*128 + r (accumulator 0) and (2*rt+1)*128 + r (accumulator 1)
+    const int feat = (GATEUP ? rt : 2 * rt) * kTileRows + r;
+    // Row pointers advance by a constant stride; full column blocks take a branch-free path.
+    const size_t ostride = GATEUP ? (size_t)p.d.Ip : (size_t)p.d.H;
+    __nv_bfloat16* obase = (GATEUP ? p.hbuf : p.obuf) + (size_t)cd.out_row * ostride + feat;
+    const bool f0 = GATEUP || feat < p.d.H, f1 = !GATEUP && feat + kTileRows < p.d.H;
+    auto emit = [&](__nv_bfloat16* o, float gv, float uv) {
+      if (C::F16) {
+        gv *= out_pow;
+        uv *= out_pow;
+      }
+      if (GATEUP) {
+        const float h = uv * __fdividef(gv, 1.f + __expf(-gv));
+        if (C::F16) {   // the down GEMM of these modes takes f16 activations
+          const __half hh = __float2half_rn(fminf(fmaxf(h, -65504.f), 65504.f));
+          *reinterpret_cast<__half*>(o) = hh;
+        } else {
+          *o = __float2bfloat16_rn(h);
+        }
+      } else {
+        if (f0) *o = __float2bfloat16_rn(gv);
+        if (f1) o[kTileRows] = __float2bfloat16_rn(uv);
+      }
+    };
+    auto columns = [&](auto wtag) {
+      constexpr int W = decltype(wtag)::value;
+      for (int cb = warp >> 2; cb < N / W; cb += kConvWarps / 4) {
+        const int c0 = cb * W;
+        if (c0 >= cd.n_rows) break;
+        uint32_t g[W], uu[W];
+        tmem_ld_pair_wait<W>(acc_base + c0, acc_base + NMAX + c0, g, uu);
+        if (part_write) {
+          float* d = sk_mine + (size_t)c0 * 128 + r;
+#pragma unroll
+          for (int i = 0; i < W; ++i)
+            if (c0 + i < cd.n_rows) {
+              d[(size_t)i * 128] = __uint_as_float(g[i]);
+              d[(size_t)(NMAX + i) * 128] = __uint_as_float(uu[i]);
+            }
+          continue;
+        }
+        for (int j = 1; j <= n_follow; ++j) {
+          const float* sp = p.sk_buf + ((size_t)blockIdx.x + j) * (2 * NMAX * 128) + (size_t)c0 * 128 + r;
+#pragma unroll
+          for (int i = 0; i < W; ++i)
+            if (c0 + i < cd.n_rows) {
+              g[i] = __float_as_uint(__uint_as_float(g[i]) + __ldcg(sp + (size_t)i * 128));
+              uu[i] = __float_as_uint(__uint_as_float(uu[i]) + __ldcg(sp + (size_t)(NMAX + i) * 128));
+            }
+        }
+        __nv_bfloat16* o = obase + (size_t)c0 * ostride;
+        if (c0 + W <= cd.n_rows) {
+#pragma unroll
+          for (int i = 0; i < W; ++i, o += ostride) emit(o, __uint_as_float(g[i]), __uint_as_float(uu[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < W; ++i, o += ostride)
+            if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(uu[i]));
+        }
+      }
+    };
+    if (NMAX >= 64 && N >= 64) columns(std::integral_constant<int, 32>());   // 32 columns per tensor-memory round trip
+    else columns(std::integral_constant<int, 8>());
+    if (part_write) {
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) st_release_gpu(p.sk_flags + (size_t)blockIdx.x * 32 + warp, 1u);
+    } else if (n_follow > 0) {
+      __syncwarp();
+      if (lane == 0)
+        for (int j = 1; j <= n_follow; ++j) p.sk_flags[((size_t)blockIdx.x + j) * 32 + warp] = 0u;   // consumed
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&bar_accempty[ab]));
+    return true;
+}
+
 template <int QUANT, bool GATEUP, int NMAX, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_constant__ FfnParams p) {
   using C = Cfg<QUANT, GATEUP, NMAX, MODE>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_wfull[8], bar_wempty[8], bar_xfull[8], bar_ready[8], bar_done[kMmaWarps][8];
-  __shared__ __align__(8) uint64_t bar_accfull, bar_accempty, bar_drain[kMmaWarps];
+  __shared__ __align__(8) uint64_t bar_accfull[2], bar_accempty[2], bar_drain[kMmaWarps];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
+  __shared__ Pending s_pend[kConvWarps];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -311,8 +454,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       mbar_init(smem_u32(&bar_ready[i]), C::SCALE_B ? kGroupWarps : kGroupWarps + 1);
       for (int c = 0; c < kMmaWarps; ++c) mbar_init(smem_u32(&bar_done[c][i]), 1);   // chain c's MMAs of the step are complete
     }
-    mbar_init(smem_u32(&bar_accfull), kMmaWarps);
-    mbar_init(smem_u32(&bar_accempty), kConvWarps);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bar_accfull[i]), kMmaWarps);     // both chains' MMAs of a work item are complete
+      mbar_init(smem_u32(&bar_accempty[i]), kConvWarps);   // every converter warp has read the item's accumulators
+    }
     for (int i = 0; i < kMmaWarps; ++i) mbar_init(smem_u32(&bar_drain[i]), 1);
     mbar_init_fence();
   }
@@ -410,7 +555,6 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       const uint32_t chain = warp - kFirstMmaWarp;
       uint32_t it = 0, units_done = 0, s = 0, ph = 0, ai = 0;
       bool ok = true;
-      const uint32_t d_tmem = tmem + chain * NMAX;
       // descriptor of stage 0's activation tile (this chain's copy); stages are a constant number of
       // 16-byte units apart
       const uint64_t b_base =
@@ -422,7 +566,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         const int N = pick_n(cd.n_rows & kChunkRowsMask, NMAX);
         const uint32_t idesc = idesc_for(N, C::F16);
         const uint32_t atom_step = (uint32_t)(N * 128) >> 4;   // descriptor units between 64-element K atoms
-        if (!mbar_wait(smem_u32(&bar_accempty), (units_done & 1u) ^ 1u, abortp)) {
+        // accumulator set of this item and how often it has been used before
+        const uint32_t ab = C::ACC_BUFS == 2 ? (units_done & 1u) : 0u;
+        const uint32_t ause = C::ACC_BUFS == 2 ? (units_done >> 1) : units_done;
+        const uint32_t d_tmem = tmem + ab * (2 * NMAX) + chain * NMAX;
+        if (!mbar_wait(smem_u32(&bar_accempty[ab]), (ause & 1u) ^ 1u, abortp)) {
           report(p.status, DEV_TIMEOUT, 200, u.item, 0);
           ok = false;
           break;
@@ -449,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           else umma_ts_x4(d_tmem, a_tmem, bd, idesc, kt > u.kt0 ? 1u : 0u);
           tc_commit(smem_u32(&bar_done[chain][cs]));
         }
-        if (ok) tc_commit(smem_u32(&bar_accfull));
+        if (ok) tc_commit(smem_u32(&bar_accfull[ab]));
         ++units_done;
       }
       // drain: every MMA issued by this thread has completed before tensor memory is freed
@@ -468,6 +616,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
     const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
     uint32_t it_base = 0, units_done = 0;
     bool ok = true;
+    // this warp's copy of the finished item that still waits for its epilogue (see run_epilogue)
+    Pending* const pend = &s_pend[warp];
+    bool has_pend = false;
     Sched sched(total, KT, p.split_k);
     Unit u;
     while (ok && sched.next(u)) {
@@ -584,122 +735,41 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
           mbar_arrive(smem_u32(&bar_ready[s]));
           if (!C::SCALE_B) mbar_arrive(smem_u32(&bar_wempty[s]));
         }
+        // this warp's first step of the item is on its way: now the epilogue of the item before it
+        if (C::ACC_BUFS == 2 && has_pend) {
+          has_pend = false;
+          if (!run_epilogue<QUANT, GATEUP, NMAX, MODE>(p, *pend, tmem, bar_accfull, bar_accempty, abortp)) {
+            ok = false;
+            break;
+          }
+        }
       }
       it_base += (uint32_t)(u.kt1 - u.kt0);
       if (!ok) break;
-      // ---- epilogue ----
-      if (!mbar_wait(smem_u32(&bar_accfull), units_done & 1u, abortp)) {
-        report(p.status, DEV_TIMEOUT, 302, u.item, 0);
+      // the unit had no step for this group: the item before it is still waiting for its epilogue
+      if (has_pend) {
+        has_pend = false;
+        if (!run_epilogue<QUANT, GATEUP, NMAX, MODE>(p, *pend, tmem, bar_accfull, bar_accempty, abortp)) { ok = false; break; }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        Pending cur;
+        cur.cd = cd; cur.rt = rt; cur.N = N; cur.item = u.item; cur.kt0 = u.kt0; cur.kt1 = u.kt1;
+        cur.n_follow = (u.kt0 == 0 && u.kt1 < KT) ? sched.followers(u) : 0;
+        cur.out_pow = out_pow;
+        cur.n = units_done;
+        *pend = cur;
+      }
+      __syncwarp();
+      if (C::ACC_BUFS == 2) {
+        has_pend = true;       // read the accumulators behind the first step of the next item
+      } else if (!run_epilogue<QUANT, GATEUP, NMAX, MODE>(p, *pend, tmem, bar_accfull, bar_accempty, abortp)) {
         ok = false;
         break;
       }
-      tc_fence_after();
-      // a split item: parts that do not start at K step 0 leave their accumulators in the scratch
-      // buffer; the part that does adds them, in part order, before the epilogue proper
-      const bool part_write = u.kt0 > 0;
-      const int n_follow = (u.kt0 == 0 && u.kt1 < KT) ? sched.followers(u) : 0;
-      float* const sk_mine = p.sk_buf + (size_t)blockIdx.x * (2 * NMAX * 128);
-      if (n_follow > 0) {
-        int got = 1;
-        if (lane == 0) {
-          for (int j = 1; j <= n_follow && got; ++j) {
-            const uint32_t* f = p.sk_flags + ((size_t)blockIdx.x + j) * 32 + warp;
-            got = 0;
-            for (uint32_t poll = 0; poll < (1u << 21); ++poll) {
-              if (ld_acquire_gpu(f) != 0u) { got = 1; break; }
-              if (poll > 64) __nanosleep(100);
-              if ((poll & 1023u) == 1023u && *abortp) break;
-            }
-          }
-        }
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) {
-          if (lane == 0) {
-            report(p.status, DEV_TIMEOUT, 304, u.item, u.kt1);
-            *abortp = 1;
-          }
-          ok = false;
-          break;
-        }
-      }
-      // gate/up: this thread owns intermediate feature rt*128 + r (gate in accumulator 0, up in 1);
-      // down: hidden features (2*rt)*128 + r (accumulator 0) and (2*rt+1)*128 + r (accumulator 1)
-      const int feat = (GATEUP ? rt : 2 * rt) * kTileRows + r;
-      // Row pointers advance by a constant stride; full column blocks take a branch-free path.
-      const size_t ostride = GATEUP ? (size_t)p.d.Ip : (size_t)p.d.H;
-      __nv_bfloat16* obase = (GATEUP ? p.hbuf : p.obuf) + (size_t)cd.out_row * ostride + feat;
-      const bool f0 = GATEUP || feat < p.d.H, f1 = !GATEUP && feat + kTileRows < p.d.H;
-      auto emit = [&](__nv_bfloat16* o, float gv, float uv) {
-        if (C::F16) {
-          gv *= out_pow;
-          uv *= out_pow;
-        }
-        if (GATEUP) {
-          const float h = uv * __fdividef(gv, 1.f + __expf(-gv));
-          if (C::F16) {   // the down GEMM of these modes takes f16 activations
-            const __half hh = __float2half_rn(fminf(fmaxf(h, -65504.f), 65504.f));
-            *reinterpret_cast<__half*>(o) = hh;
-          } else {
-            *o = __float2bfloat16_rn(h);
-          }
-        } else {
-          if (f0) *o = __float2bfloat16_rn(gv);
-          if (f1) o[kTileRows] = __float2bfloat16_rn(uv);
-        }
-      };
-      auto columns = [&](auto wtag) {
-        constexpr int W = decltype(wtag)::value;
-        for (int cb = warp >> 2; cb < N / W; cb += kConvWarps / 4) {
-          const int c0 = cb * W;
-          if (c0 >= cd.n_rows) break;
-          uint32_t g[W], uu[W];
-          tmem_ld_pair_wait<W>(lane_base + c0, lane_base + NMAX + c0, g, uu);
-          if (part_write) {
-            float* d = sk_mine + (size_t)c0 * 128 + r;
-#pragma unroll
-            for (int i = 0; i < W; ++i)
-              if (c0 + i < cd.n_rows) {
-                d[(size_t)i * 128] = __uint_as_float(g[i]);
-                d[(size_t)(NMAX + i) * 128] = __uint_as_float(uu[i]);
-              }
-            continue;
-          }
-          for (int j = 1; j <= n_follow; ++j) {
-            const float* sp = p.sk_buf + ((size_t)blockIdx.x + j) * (2 * NMAX * 128) + (size_t)c0 * 128 + r;
-#pragma unroll
-            for (int i = 0; i < W; ++i)
-              if (c0 + i < cd.n_rows) {
-                g[i] = __float_as_uint(__uint_as_float(g[i]) + __ldcg(sp + (size_t)i * 128));
-                uu[i] = __float_as_uint(__uint_as_float(uu[i]) + __ldcg(sp + (size_t)(NMAX + i) * 128));
-              }
-          }
-          __nv_bfloat16* o = obase + (size_t)c0 * ostride;
-          if (c0 + W <= cd.n_rows) {
-#pragma unroll
-            for (int i = 0; i < W; ++i, o += ostride) emit(o, __uint_as_float(g[i]), __uint_as_float(uu[i]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < W; ++i, o += ostride)
-              if (c0 + i < cd.n_rows) emit(o, __uint_as_float(g[i]), __uint_as_float(uu[i]));
-          }
-        }
-      };
-      if (NMAX >= 64 && N >= 64) columns(std::integral_constant<int, 32>());   // 32 columns per tensor-memory round trip
-      else columns(std::integral_constant<int, 8>());
-      if (part_write) {
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_release_gpu(p.sk_flags + (size_t)blockIdx.x * 32 + warp, 1u);
-      } else if (n_follow > 0) {
-        __syncwarp();
-        if (lane == 0)
-          for (int j = 1; j <= n_follow; ++j) p.sk_flags[((size_t)blockIdx.x + j) * 32 + warp] = 0u;   // consumed
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_accempty));
       ++units_done;
     }
+    if (ok && has_pend) run_epilogue<QUANT, GATEUP, NMAX, MODE>(p, *pend, tmem, bar_accfull, bar_accempty, abortp);
   }
 
   tc_fence_before();
