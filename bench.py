@@ -798,7 +798,37 @@ def run_extras(args, dev, sync_unused):
         torch.cuda.empty_cache()
     except Exception as ex:   # noqa: BLE001
         out["int8_dsv3_shape_64_experts"] = {"error": repr(ex)}
+    try:
+        out["registration_fp8_host_tensors"] = registration_run(dev)
+    except Exception as ex:   # noqa: BLE001
+        out["registration_fp8_host_tensors"] = {"error": repr(ex)}
     return out
+
+
+def registration_run(dev, n_exp: int = 64):
+    """Loader throughput: `n_exp` DeepSeek-V3-shape fp8 experts (44 MB each) registered from pageable
+    host memory by 1, 8 and 64 threads at once - the reference loads 64 experts concurrently
+    (ek-computation/src/worker/state.rs:178-197)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from ek_b200 import synth, Backend
+    S = synth.DSV3
+    be = Backend(S.backend_config(256, dev.index, 0, 1, 1, n_exp))
+    host = [{k_: v.cpu() for k_, v in synth.make_expert(S, dev, SEED + 7, 0, e).items()} for e in range(8)]
+    nbytes = sum(v.numel() * v.element_size() for v in host[0].values())
+    res = {}
+    for nthr in (1, 8, 64):
+        for e in range(n_exp):
+            be.evict(be.expert_id(0, e))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(nthr) as ex:
+            list(ex.map(lambda e: be.register_expert(be.expert_id(0, e), host[e % 8]), range(n_exp)))
+        dt = time.perf_counter() - t0
+        res[str(nthr)] = {"experts_per_s": n_exp / dt, "GB_per_s": n_exp * nbytes / dt / 1e9}
+    be.close()
+    del be
+    torch.cuda.empty_cache()
+    return {"experts": n_exp, "bytes_per_expert": nbytes, "source": "pageable host tensors", "threads": res}
 
 
 def worker_path(args, S, be, dev, T, u):

@@ -77,6 +77,24 @@ struct ExpertReq {
   std::atomic<bool> done{false};   // set (release) by whoever served the request, after rc
 };
 
+// One of a few independent loader lanes: registrations from several threads run side by side, each
+// with its own stream, device staging and pinned bounce buffer (the reference loads up to 64 experts
+// concurrently, ek-computation/src/worker/state.rs:178-197).
+struct LoadLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev = nullptr;
+  void* stage[3] = {nullptr, nullptr, nullptr};
+  size_t stage_cap[3] = {0, 0, 0};
+  float* stage_scale[3] = {nullptr, nullptr, nullptr};
+  size_t stage_scale_cap[3] = {0, 0, 0};
+  void* stage_cvt = nullptr;
+  size_t stage_cvt_cap = 0;
+  uint8_t* bounce = nullptr;           // pinned host memory: pageable sources are copied here by the calling thread
+  size_t bounce_cap = 0;
+  bool busy = false;
+};
+constexpr int kLoadLanes = 8;
+
 struct ek_backend {
   ek_config_t cfg;
   Dims d;
@@ -148,7 +166,11 @@ struct ek_backend {
   std::condition_variable pend_cv;            // signalled after every grouped pass
   int last_batch = 1;                         // requests served by the previous pass
   int64_t batched_calls = 0, batched_launches = 0;   // worker-level calls served / grouped launches used (under fwd_mu)
-  std::mutex load_mu;                         // loads share the staging buffers
+  std::mutex load_mu;                         // loads other than ek_expert_register share one set of staging buffers
+  LoadLane lanes[kLoadLanes];                 // ek_expert_register: one lane per registration in flight
+  std::mutex lane_mu;
+  std::condition_variable lane_cv;
+  std::set<std::string> lane_ids;             // ids being registered right now (one registration per id at a time)
   mutable std::mutex err_mu;
   mutable std::string err;
   std::atomic<int64_t> launches{0};
@@ -332,6 +354,55 @@ int grow(ek_backend* be, void** buf, size_t* cap, size_t need) {
   *buf = nullptr;
   *cap = 0;
   CK(cudaMalloc(buf, need));
+  *cap = need;
+  return EK_OK;
+}
+
+// Takes a free loader lane for `id`; waits while all lanes are busy or the same id is being registered.
+struct LaneGuard {
+  ek_backend* be;
+  LoadLane* lane = nullptr;
+  std::string id;
+  LaneGuard(ek_backend* b, const std::string& i) : be(b), id(i) {
+    std::unique_lock<std::mutex> lk(be->lane_mu);
+    for (;;) {
+      if (!be->lane_ids.count(id))
+        for (auto& l : be->lanes)
+          if (!l.busy) { lane = &l; break; }
+      if (lane) break;
+      be->lane_cv.wait(lk);
+    }
+    lane->busy = true;
+    be->lane_ids.insert(id);
+  }
+  ~LaneGuard() {
+    {
+      std::lock_guard<std::mutex> lk(be->lane_mu);
+      lane->busy = false;
+      be->lane_ids.erase(id);
+    }
+    be->lane_cv.notify_all();
+  }
+  int ready() {   // stream, event (created on first use)
+    if (!lane->stream) CK(cudaStreamCreateWithFlags(&lane->stream, cudaStreamNonBlocking));
+    if (!lane->ev) CK(cudaEventCreateWithFlags(&lane->ev, cudaEventDisableTiming));
+    return EK_OK;
+  }
+  // a host source goes through the pinned bounce buffer at byte offset *off (advanced)
+  int upload(void* dst, const void* src, size_t bytes, size_t* off) {
+    memcpy(lane->bounce + *off, src, bytes);
+    CK(cudaMemcpyAsync(dst, lane->bounce + *off, bytes, cudaMemcpyHostToDevice, lane->stream));
+    *off += (bytes + 255) & ~(size_t)255;
+    return EK_OK;
+  }
+};
+
+int grow_pinned(uint8_t** buf, size_t* cap, size_t need) {
+  if (*cap >= need) return EK_OK;
+  if (*buf) cudaFreeHost(*buf);
+  *buf = nullptr;
+  *cap = 0;
+  if (cudaMallocHost(reinterpret_cast<void**>(buf), need) != cudaSuccess) return EK_NO_MEMORY;
   *cap = need;
   return EK_OK;
 }
@@ -865,6 +936,13 @@ void ek_backend_destroy(ek_backend_t* be) {
   cudaFreeHost(be->h_status); cudaFreeHost(be->h_chunks); cudaFreeHost(be->h_segs); cudaFree(be->segs); cudaFreeHost(be->h_x); cudaFreeHost(be->h_y);
   cudaFreeHost(be->h_tk);
   for (int i = 0; i < 3; ++i) { cudaFree(be->stage[i]); cudaFree(be->stage_scale[i]); }
+  for (auto& l : be->lanes) {
+    if (l.stream) { cudaStreamSynchronize(l.stream); cudaStreamDestroy(l.stream); }
+    if (l.ev) cudaEventDestroy(l.ev);
+    for (int i = 0; i < 3; ++i) { cudaFree(l.stage[i]); cudaFree(l.stage_scale[i]); }
+    cudaFree(l.stage_cvt);
+    if (l.bounce) cudaFreeHost(l.bounce);
+  }
   cudaFree(be->stage_cvt);
   for (auto& pass : be->ev)
     for (auto& e : pass) if (e) cudaEventDestroy(e);
@@ -985,7 +1063,9 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
     }
   }
 
-  std::lock_guard<std::mutex> lg(be->load_mu);
+  LaneGuard lg(be, id);
+  LoadLane* const lane = lg.lane;
+  if (int rc = lg.ready()) return rc;
   Layer* L = nullptr;
   int slot_routed = -1;
   {
@@ -1006,28 +1086,39 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
         return fail(be, EK_NO_MEMORY, "all %d replica slots of layer %d are taken", c.replica_slots, layer);
     }
   }
-  cudaStream_t ls = be->load_stream;
+  cudaStream_t ls = lane->stream;
   // the slot may still be read by forwards queued before an eviction
-  CK(cudaEventRecord(be->fwd_done, be->stream));
-  CK(cudaStreamWaitEvent(ls, be->fwd_done, 0));
+  CK(cudaEventRecord(lane->ev, be->stream));
+  CK(cudaStreamWaitEvent(ls, lane->ev, 0));
 
   const int esz = elem_bytes(c.quant);
+  // host sources: the calling thread copies them into the lane's pinned buffer (threads do that side
+  // by side), the DMA and the re-tiling kernels follow on the lane's stream
+  size_t host_bytes = 0, host_off = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (!is_device_ptr(w[i]->data))
+      host_bytes += (((size_t)want[i][0] * want[i][1] * (w[i]->dtype == EK_F16 ? 2 : esz)) + 255) & ~(size_t)255;
+    if (c.quant != EK_QUANT_BF16 && !is_device_ptr(sc[i]->data))
+      host_bytes += (((size_t)sc[i]->shape[0] * sc[i]->shape[1] * 4) + 255) & ~(size_t)255;
+  }
+  if (host_bytes && grow_pinned(&lane->bounce, &lane->bounce_cap, host_bytes) != EK_OK)
+    return fail(be, EK_NO_MEMORY, "no pinned host memory for the loader (%zu bytes)", host_bytes);
   const void* src[3];
   for (int i = 0; i < 3; ++i) {
     const size_t elems = (size_t)want[i][0] * want[i][1];
     const size_t in_bytes = elems * (w[i]->dtype == EK_F16 ? 2 : esz);
     const void* p = w[i]->data;
     if (!is_device_ptr(p)) {
-      int rc = grow(be, &be->stage[i], &be->stage_cap[i], in_bytes);
+      int rc = grow(be, &lane->stage[i], &lane->stage_cap[i], in_bytes);
       if (rc != EK_OK) return rc;
-      CK(cudaMemcpyAsync(be->stage[i], p, in_bytes, cudaMemcpyHostToDevice, ls));
-      p = be->stage[i];
+      rc = lg.upload(lane->stage[i], p, in_bytes, &host_off);
+      if (rc != EK_OK) return rc;
+      p = lane->stage[i];
     }
     if (w[i]->dtype == EK_F16) {
-      // one staging buffer for converted copies: serialise by syncing between matrices
-      int rc = grow(be, &be->stage_cvt, &be->stage_cvt_cap, elems * 2 * 3);
+      int rc = grow(be, &lane->stage_cvt, &lane->stage_cvt_cap, elems * 2 * 3);
       if (rc != EK_OK) return rc;
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(be->stage_cvt) + (size_t)i * elems;
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(lane->stage_cvt) + (size_t)i * elems;
       be->launches += launch_f16_to_bf16(p, dst, (int64_t)elems, ls);
       p = dst;
     }
@@ -1039,10 +1130,11 @@ int32_t ek_expert_register(ek_backend_t* be, const char* id, const ek_tensor_vie
       const size_t bytes = (size_t)sc[i]->shape[0] * sc[i]->shape[1] * 4;
       const void* p = sc[i]->data;
       if (!is_device_ptr(p)) {
-        int rc = grow(be, (void**)&be->stage_scale[i], &be->stage_scale_cap[i], bytes);
+        int rc = grow(be, (void**)&lane->stage_scale[i], &lane->stage_scale_cap[i], bytes);
         if (rc != EK_OK) return rc;
-        CK(cudaMemcpyAsync(be->stage_scale[i], p, bytes, cudaMemcpyHostToDevice, ls));
-        p = be->stage_scale[i];
+        rc = lg.upload(lane->stage_scale[i], p, bytes, &host_off);
+        if (rc != EK_OK) return rc;
+        p = lane->stage_scale[i];
       }
       ssrc[i] = reinterpret_cast<const float*>(p);
     }

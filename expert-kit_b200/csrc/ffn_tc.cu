@@ -762,7 +762,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       }
       __syncwarp();
       if (C::ACC_BUFS == 2) {
-        has_pend = true;       // read the accumulators behind the first step of the next item
+        has_pend = true;       // read the accumulators behind the first step of the next item (two or three steps measured the same)
       } else if (!run_epilogue<QUANT, GATEUP, NMAX, MODE>(p, *pend, tmem, bar_accfull, bar_accempty, abortp)) {
         ok = false;
         break;
@@ -793,7 +793,7 @@ template <int QUANT, int MODE_DECODE, int MODE_PREFILL>
 int launch_quant(const FfnParams& p, int nmax, int which, cudaStream_t s) {
   if (nmax <= 32)
     return which == 0 ? launch_one<QUANT, true, 32, MODE_DECODE>(p, s) : launch_one<QUANT, false, 32, MODE_DECODE>(p, s);
-  if (nmax <= 64)
+  if (nmax <= 64)   // (scale-on-A measured no faster than scale-on-B at this chunk size)
     return which == 0 ? launch_one<QUANT, true, 64, MODE_DECODE>(p, s) : launch_one<QUANT, false, 64, MODE_DECODE>(p, s);
   return which == 0 ? launch_one<QUANT, true, 128, MODE_PREFILL>(p, s) : launch_one<QUANT, false, 128, MODE_PREFILL>(p, s);
 }
