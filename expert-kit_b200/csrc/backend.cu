@@ -129,7 +129,7 @@ struct ek_backend {
   ChunkDesc* chunks = nullptr;
   int32_t* n_chunks = nullptr;
   DevStatus* status = nullptr;
-  uint32_t* front_ticket = nullptr;    // last-CTA tickets: [0] fused small-batch front kernel, [1] expert-parallel signal
+  uint32_t* front_ticket = nullptr;    // last-CTA tickets: [0] fused small-batch front kernel, [1] expert-parallel signal, [2] permute + work list
   int front_small = 1;                 // use that kernel when the batch qualifies
   float* sk_buf = nullptr;             // partial accumulators of K-split work items
   uint32_t* sk_flags = nullptr;
@@ -560,7 +560,7 @@ int check_status(ek_backend* be) {
   cudaMemsetAsync(be->status, 0, sizeof(DevStatus), be->stream);
   // a pass that gave up may have left split-item flags raised
   cudaMemsetAsync(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t), be->stream);
-  cudaMemsetAsync(be->front_ticket, 0, 2 * sizeof(uint32_t), be->stream);
+  cudaMemsetAsync(be->front_ticket, 0, 4 * sizeof(uint32_t), be->stream);
   cudaStreamSynchronize(be->stream);
   switch (st.code) {
     case DEV_TIMEOUT:
@@ -695,10 +695,8 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
       be->launches += launch_histogram(ids, Tk, c.n_experts, be->counts, be->status, s);
     }
     mark(be, 1);
-    be->launches += launch_permute(pp, s);
-    if (debug_sync_failed(be, "permute")) return EK_CUDA;
-    be->launches += launch_worklist(wp, s);
-    if (debug_sync_failed(be, "worklist")) return EK_CUDA;
+    be->launches += launch_permute_worklist(pp, wp, be->front_ticket + 2, s);
+    if (debug_sync_failed(be, "permute + work list")) return EK_CUDA;
   }
   if (!gathered) {
     be->launches += launch_gather(x, be->perm, be->offsets + c.n_experts, be->xp, T, k, c.hidden, opt.sh_t0, sh_T,
@@ -881,8 +879,8 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
   CKC(cudaMemset(be->status, 0, sizeof(DevStatus)));
   CKC(cudaMalloc(&be->ep_counters, EK_EP_MAX_RANKS * sizeof(uint32_t)));
   CKC(cudaMemset(be->ep_counters, 0, EK_EP_MAX_RANKS * sizeof(uint32_t)));
-  CKC(cudaMalloc(&be->front_ticket, 2 * sizeof(uint32_t)));
-  CKC(cudaMemset(be->front_ticket, 0, 2 * sizeof(uint32_t)));
+  CKC(cudaMalloc(&be->front_ticket, 4 * sizeof(uint32_t)));
+  CKC(cudaMemset(be->front_ticket, 0, 4 * sizeof(uint32_t)));
   CKC(cudaMalloc(&be->sk_buf, ffn_tc_scratch_floats(be->n_sm) * sizeof(float)));
   CKC(cudaMalloc(&be->sk_flags, (size_t)be->n_sm * 32 * sizeof(uint32_t)));
   CKC(cudaMemset(be->sk_flags, 0, (size_t)be->n_sm * 32 * sizeof(uint32_t)));

@@ -17,19 +17,20 @@ __device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
 }
 
 // Chunk descriptors: every expert this rank serves has its row range cut into pieces of `chunk_rows`,
-// followed by the virtual shared experts (all T tokens each).  One CTA of 1024 threads.
+// followed by the virtual shared experts (all T tokens each).  One CTA of NT threads.
+template <int NT>
 __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
-  __shared__ int s_scan[1024];
+  __shared__ int s_scan[NT];
   __shared__ int s_total;
   const int tid = threadIdx.x;
   const int n_local = p.e_hi - p.e_lo;
   if (p.counts_copy)
-    for (int e = tid; e < p.E; e += 1024) p.counts_copy[e] = __ldcg(&p.counts[e]);
+    for (int e = tid; e < p.E; e += NT) p.counts_copy[e] = __ldcg(&p.counts[e]);
   // experts this rank serves: its window (slot = e - e_lo), or, with an owner table, every expert
   // the table gives to this rank (slot from the layer's slot table: own experts and replicas)
   const int first = p.owners ? 0 : p.e_lo, last = p.owners ? p.E : p.e_hi;
   int running = 0;
-  for (int e0 = first; e0 < last; e0 += 1024) {
+  for (int e0 = first; e0 < last; e0 += NT) {
     const int e = e0 + tid;
     int cnt = 0, nch = 0, slot = -1;
     if (e < last && (!p.owners || p.owners[e] == p.rank)) {
@@ -46,16 +47,16 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
     }
     s_scan[tid] = nch;
     __syncthreads();
-    for (int o = 1; o < 1024; o <<= 1) {
+    for (int o = 1; o < NT; o <<= 1) {
       int v = tid >= o ? s_scan[tid - o] : 0;
       __syncthreads();
       s_scan[tid] += v;
       __syncthreads();
     }
     int first_chunk = running + s_scan[tid] - nch;
-    if (tid == 1023) s_total = s_scan[tid];
+    if (tid == NT - 1) s_total = s_scan[tid];
     if (nch > 0) {
-      const int off = p.offsets[e];
+      const int off = __ldcg(&p.offsets[e]);   // may have been written by another CTA of this kernel
       for (int c = 0; c < nch; ++c) {
         if (first_chunk + c >= p.max_chunks) break;
         ChunkDesc d;
@@ -72,7 +73,7 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
   }
   // shared virtual experts
   const int per_shared = (p.T + p.chunk_rows - 1) / p.chunk_rows;
-  for (int i = tid; i < p.n_shared * per_shared; i += 1024) {
+  for (int i = tid; i < p.n_shared * per_shared; i += NT) {
     const int j = i / per_shared, c = i % per_shared;
     if (running + i >= p.max_chunks) break;
     ChunkDesc d;

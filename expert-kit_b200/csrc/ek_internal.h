@@ -189,7 +189,14 @@ struct WorklistParams {
   int32_t max_chunks;
   DevStatus* status;
 };
-int launch_worklist(const WorklistParams& p, cudaStream_t s);
+// permutation and work list in one launch (the CTA that finishes last builds the list); `ticket`: a zeroed counter
+struct PermuteWorklistParams {
+  PermuteParams permute;
+  WorklistParams worklist;
+  uint32_t* ticket = nullptr;
+  int32_t with_worklist = 0;
+};
+int launch_permute_worklist(const PermuteParams& p, const WorklistParams& w, uint32_t* ticket, cudaStream_t s);
 
 // Router + bucketing + work list (+ gather of a handful of rows) in one launch for small batches
 // (front_small.cu).  `route.wg` must be the bf16 router weight; `route.partial` is unused, the

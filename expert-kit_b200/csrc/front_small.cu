@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
   }
   __syncthreads();                                      // counts / offsets / perm are in global memory for this CTA
   // ---- chunk work list -----------------------------------------------------------------------------
-  build_worklist(p.worklist);
+  build_worklist<kThreads>(p.worklist);
   // ---- row gather (only when the host asked for it: a handful of rows) --------------------------------
   if (p.gather_rows) {
     __syncthreads();

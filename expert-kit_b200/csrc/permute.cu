@@ -17,11 +17,14 @@ namespace {
 
 // One CTA per expert: offsets[e] = sum of counts of local experts below e, then one ordered
 // pass over all assignments, ranking the matches with warp scans.
-__global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
+// With a work list to build (`with_worklist`), the CTA that finishes last does that too: one launch less.
+__global__ void __launch_bounds__(256) permute_kernel(const __grid_constant__ PermuteWorklistParams pw) {
+  const PermuteParams& p = pw.permute;
   pdl_wait();
   pdl_trigger();
   __shared__ int s_red[8];
   __shared__ int s_base;
+  __shared__ int s_last;
   const int e = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // experts this rank serves in this pass: its window, or whatever the owner table says
@@ -50,9 +53,8 @@ __global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
   int running = s_base;
   const int n = p.T * p.k;
   const bool empty = p.counts[e] == 0;
-  if (empty) return;
 
-  for (int base = 0; base < n; base += 1024) {
+  for (int base = 0; base < (empty ? 0 : n); base += 1024) {
     const int i0 = base + tid * 4;
     int id[4];
 #pragma unroll
@@ -92,13 +94,18 @@ __global__ void __launch_bounds__(256) permute_kernel(PermuteParams p) {
     }
     running += total;
   }
-}
-
-// Chunk work list of the grouped GEMMs (see build_worklist).
-__global__ void __launch_bounds__(1024) worklist_kernel(WorklistParams p) {
-  pdl_wait();
-  pdl_trigger();
-  build_worklist(p);
+  if (!pw.with_worklist) return;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned t = atomicAdd(pw.ticket, 1u);
+    s_last = t == gridDim.x - 1;
+    if (s_last) *pw.ticket = 0;              // launches on one stream do not overlap
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  build_worklist<256>(pw.worklist);
 }
 
 // xp[r,:] = x[perm[r] / k, :] for permuted rows, then (optionally) a straight copy of x for
@@ -133,12 +140,20 @@ __global__ void __launch_bounds__(128) rows_to_f16_kernel(__nv_bfloat16* rows, i
 }  // namespace
 
 int launch_permute(const PermuteParams& p, cudaStream_t s) {
-  if (p.E > 0) launch_pdl(permute_kernel, dim3(p.E), dim3(256), 0, s, p);
+  PermuteWorklistParams pw;
+  pw.permute = p;
+  pw.with_worklist = 0;
+  if (p.E > 0) launch_pdl(permute_kernel, dim3(p.E), dim3(256), 0, s, pw);
   return 1;
 }
 
-int launch_worklist(const WorklistParams& p, cudaStream_t s) {
-  launch_pdl(worklist_kernel, dim3(1), dim3(1024), 0, s, p);
+int launch_permute_worklist(const PermuteParams& p, const WorklistParams& w, uint32_t* ticket, cudaStream_t s) {
+  PermuteWorklistParams pw;
+  pw.permute = p;
+  pw.worklist = w;
+  pw.ticket = ticket;
+  pw.with_worklist = 1;
+  launch_pdl(permute_kernel, dim3(p.E), dim3(256), 0, s, pw);
   return 1;
 }
 
