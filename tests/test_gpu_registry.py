@@ -181,6 +181,38 @@ def test_concurrent_forwards_and_loads(small):
     assert be.loaded() == 8
 
 
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_registrations_from_many_threads_at_once(quant):
+    """The worker loads up to 64 experts concurrently (ek-computation/src/worker/state.rs:178-197):
+    registrations from 16 threads run side by side on the loader lanes, two threads register the same
+    id at once, and every expert then answers like the oracle."""
+    import ek_b200
+    cfg = O.MoEConfig(hidden=256, intermediate=128, n_experts=16, top_k=2, scoring=O.SCORE_SOFTMAX, quant=quant)
+    layer = OC.make_layer(cfg, 77)
+    be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=64))
+    errors = []
+
+    def load(e):
+        try:
+            for _ in range(3):     # host tensors (pageable): the path through the pinned bounce buffers
+                be.register_expert(be.expert_id(0, e), _tensors(0, e, layer["experts"][e]))
+        except Exception as ex:   # noqa: BLE001
+            errors.append(ex)
+
+    ths = [threading.Thread(target=load, args=(e % 16,)) for e in range(24)]   # experts 0..7 from two threads each
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    assert not errors, errors
+    assert be.loaded() == 16 and be.loading() == 0
+    x = OC.make_inputs(cfg, 12, 3)
+    for e in range(16):
+        y = be.expert_forward(be.expert_id(0, e), x)
+        Hh.assert_outputs_close(y, O.expert_ffn(x, *layer["experts"][e].bf16()), f"expert {e} after parallel registration")
+    be.close()
+
+
 def test_concurrent_worker_calls_share_grouped_launches(small):
     """Single-expert calls from many threads (one RPC per expert in the reference worker) are
     served in groups: same bits as the calls made one by one, fewer passes than calls."""
