@@ -20,7 +20,8 @@ __device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
 // followed by the virtual shared experts (all T tokens each).  One CTA of NT threads.
 template <int NT>
 __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
-  __shared__ int s_scan[NT];
+  static_assert(NT % 32 == 0 && NT <= 1024, "whole warps");
+  __shared__ int s_scan[64];
   __shared__ int s_total;
   const int tid = threadIdx.x;
   const int n_local = p.e_hi - p.e_lo;
@@ -45,16 +46,28 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
         nch = 0;
       }
     }
-    s_scan[tid] = nch;
-    __syncthreads();
-    for (int o = 1; o < NT; o <<= 1) {
-      int v = tid >= o ? s_scan[tid - o] : 0;
-      __syncthreads();
-      s_scan[tid] += v;
-      __syncthreads();
+    // inclusive scan of the chunk counts: shuffles inside a warp, then the warps' totals
+    int inc = nch;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, o);
+      if ((tid & 31) >= o) inc += v;
     }
-    int first_chunk = running + s_scan[tid] - nch;
-    if (tid == NT - 1) s_total = s_scan[tid];
+    if ((tid & 31) == 31) s_scan[tid >> 5] = inc;
+    __syncthreads();
+    if (tid < 32) {
+      int w = tid < NT / 32 ? s_scan[tid] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, w, o);
+        if (tid >= o) w += v;
+      }
+      s_scan[32 + tid] = w;                      // inclusive totals of warps 0..tid
+    }
+    __syncthreads();
+    const int before = (tid >> 5) > 0 ? s_scan[32 + (tid >> 5) - 1] : 0;
+    int first_chunk = running + before + inc - nch;
+    if (tid == NT - 1) s_total = before + inc;
     if (nch > 0) {
       const int off = __ldcg(&p.offsets[e]);   // may have been written by another CTA of this kernel
       for (int c = 0; c < nch; ++c) {

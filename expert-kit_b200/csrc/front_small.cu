@@ -122,11 +122,8 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
       r.logits[o] = r.scoring == EK_SCORE_SOFTMAX ? __bfloat162float(__float2bfloat16_rn(v)) : v;
     }
     __syncthreads();
-    RouteParams rr = r;
-    rr.partial = nullptr;                                // the logits are final
-    rr.n_partials = 0;
     float* sc = smem + (size_t)warp * (2 * kMaxE + 64);
-    if (warp < T) select_token(rr, warp, lane, sc, sc + kMaxE, sc + 2 * kMaxE);
+    if (warp < T) select_token(r, warp, lane, sc, sc + kMaxE, sc + 2 * kMaxE);   // r.partial is null: the logits are final
   }
   __syncthreads();
   // ---- offsets: exclusive scan of the counts of the experts this rank serves -------------------

@@ -119,19 +119,41 @@ __device__ __forceinline__ void select_token(const RouteParams& p, int t, int la
   unsigned taken = 0u;  // bit j: element lane + 32*j already selected
   float wsel = 0.f;     // lane i < k keeps the weight of the i-th pick
   int isel = -1;
-  for (int it = 0; it < p.k; ++it) {
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int j = 0, e = lane; e < E; ++j, e += 32) {
-      if ((taken >> j) & 1u) continue;
-      float v = ch[e];
-      if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+  if (E <= 256) {
+    // the lane's candidates stay in registers over the k rounds
+    float mine[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mine[j] = lane + 32 * j < E ? ch[lane + 32 * j] : -INFINITY;
+    for (int it = 0; it < p.k; ++it) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E && !((taken >> j) & 1u) && (mine[j] > bv || (mine[j] == bv && e < bi))) { bv = mine[j]; bi = e; }
+      }
+      warp_argmax(bv, bi);
+      if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+      if (lane == it) {
+        isel = bi;
+        wsel = sc[bi];
+      }
     }
-    warp_argmax(bv, bi);
-    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-    if (lane == it) {
-      isel = bi;
-      wsel = sc[bi];
+  } else {
+    for (int it = 0; it < p.k; ++it) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int j = 0, e = lane; e < E; ++j, e += 32) {
+        if ((taken >> j) & 1u) continue;
+        float v = ch[e];
+        if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+      }
+      warp_argmax(bv, bi);
+      if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+      if (lane == it) {
+        isel = bi;
+        wsel = sc[bi];
+      }
     }
   }
   // renormalise: sequential sum in slot order (lane 0 .. k-1)
