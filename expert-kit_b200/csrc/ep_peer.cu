@@ -88,10 +88,11 @@ __global__ void __launch_bounds__(256) ep_pull_finish_kernel(PeerPtrs partial, s
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int r0 = 0; r0 < world; r0 += 4) {
-      float4 a[4], b[4];
+    // the loads of eight ranks are in flight together: one NVLink round trip for a box of eight
+    for (int r0 = 0; r0 < world; r0 += 8) {
+      float4 a[8], b[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < 8; ++i) {
         if (r0 + i < world) {
           const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(partial.p[r0 + i]) +
                                                               src_elem_off + (size_t)t * H + (size_t)v * 8);
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(256) ep_pull_finish_kernel(PeerPtrs partial, s
         }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < 8; ++i) {
         if (r0 + i < world) {
           acc[0] += a[i].x; acc[1] += a[i].y; acc[2] += a[i].z; acc[3] += a[i].w;
           acc[4] += b[i].x; acc[5] += b[i].y; acc[6] += b[i].z; acc[7] += b[i].w;
