@@ -761,7 +761,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
         *pend = cur;
       }
       __syncwarp();
-      if (C::ACC_BUFS == 2) {
+      if (C::ACC_BUFS == 2) {   // with a single accumulator set the MMAs could not go on anyway: deferring measured slower
         has_pend = true;       // read the accumulators behind the first step of the next item (two or three steps measured the same)
       } else if (!run_epilogue<QUANT, GATEUP, NMAX, MODE>(p, *pend, tmem, bar_accfull, bar_accempty, abortp)) {
         ok = false;
