@@ -187,6 +187,13 @@ def shape_of(name: str):
     return {"cfg3": synth.DSV3, "cfg2": synth.QWEN3}[name]
 
 
+def compute_dtype(S) -> str:
+    """Operand type of the tensor-core contractions (fp32 accumulation): quantised weights are converted
+    exactly to f16 and meet f16 activations; bf16 weights meet bf16 activations.  Inputs and outputs
+    of the layer are bf16 either way."""
+    return "f16" if S.quant != 0 else "bf16"
+
+
 def metric_of(cfg_name: str) -> str:
     return {"cfg3": "MoE expert-layer tokens/s (DSV3 FP8-W/bf16-A)",
             "cfg2": "MoE expert-layer tokens/s (Qwen3-30B-A3B shape, bf16 W/A)"}[cfg_name]
@@ -604,7 +611,7 @@ def main_ep(args, rank: int, world: int, local: int):
     if rank == 0:
         line = {"metric": metric_of(args.config), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "vs_baseline": None, "dtype": compute_dtype(S), "data": "synthetic",
                 "config": workload_config(S, args.config, T, world, n_exp, NL),
                 "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
                 "layer_roofline": layer, "cpu_baseline": None, "check": check,
@@ -736,7 +743,7 @@ def main_single(args, local: int):
     fb = sampler.stop()
     line = {"metric": metric_of(args.config), "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": compute_dtype(S), "data": "synthetic",
             "config": workload_config(S, args.config, T, 1, n_exp),
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks or fb, "roofline": roof,
             "layer_roofline": layer, "cpu_baseline": base, "check": check,
