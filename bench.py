@@ -349,14 +349,14 @@ def cpu_baseline(S, T: int, n_exp: int, budget_s: float = 15.0, seed: int = 5, s
     counts, offsets, perm = O.bucket(ids, n_exp)
     t_route = time.perf_counter() - t0
     active = int((counts > 0).sum())
-    n_sample = 4
+    n_sample = 8
     experts = [[torch.randn(s, generator=g).mul_(0.02).to(torch.bfloat16) for s in ((I, H), (I, H), (H, I))]
                for _ in range(n_sample)]
     rows_per = max(1, round(T * K / max(active, 1)))
     xe = x[:rows_per] if rows_per <= T else x.repeat((rows_per + T - 1) // T, 1)[:rows_per]
     O.expert_ffn(xe, *experts[0])   # warm-up
     n_calls, t_ffn = 0, 0.0
-    while t_ffn < budget_s * 0.5 and n_calls < 64:
+    while t_ffn < budget_s * 0.5 and n_calls < 16384:    # about half the budget in the expert loop
         ws = experts[n_calls % n_sample]
         t0 = time.perf_counter()
         O.expert_ffn(xe, *ws)
