@@ -385,9 +385,9 @@ def cpu_baseline(S, T: int, n_exp: int, budget_s: float = 15.0, seed: int = 5, s
             xb = torch.randn(b, H, generator=g).to(torch.bfloat16)
             O.expert_ffn(xb, *experts[0])
             ts = []
-            for i in range(4):
+            while sum(ts) < 0.5 and len(ts) < 2048:          # half a second per batch size
                 t0 = time.perf_counter()
-                O.expert_ffn(xb, *experts[i % n_sample])
+                O.expert_ffn(xb, *experts[len(ts) % n_sample])
                 ts.append(time.perf_counter() - t0)
             m = statistics.mean(ts)
             rows[str(b)] = {"us_per_call": m * 1e6, "rows_per_s": b / m}
