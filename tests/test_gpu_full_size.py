@@ -36,7 +36,7 @@ def dsv3_full():
     be.close()
 
 
-@pytest.mark.parametrize("T,n_sample", [(32, 6), (256, 6), (4096, 5)])
+@pytest.mark.parametrize("T,n_sample", [(1, 1), (32, 6), (256, 6), (1024, 5), (4096, 5)])
 def test_cfg3_full_layer_256_experts(dsv3_full, T, n_sample):
     from ek_b200 import synth
     cfg, be, wg, fetch, dev = dsv3_full
