@@ -25,16 +25,20 @@ from ek_b200.ep import ExpertParallelMoE, plan_exchange  # noqa: E402
 class OracleStages:
     """CPU stand-in with the interface of ek_b200.ep.BackendStages; holds only this rank's experts."""
 
-    def __init__(self, cfg, layer, rank, world, replicas=()):
-        self.cfg, self.layer = cfg, layer
+    def __init__(self, cfg, layers, rank, world, replicas=()):
+        self.cfg, self.layers = cfg, layers
         self.n_experts, self.top_k, self.hidden = cfg.n_experts, cfg.top_k, cfg.hidden
         self.el = cfg.n_experts // world
         self.lo = rank * self.el
         self.rank = rank
-        self.local = {self.lo + i: layer["experts"][self.lo + i] for i in range(self.el)}
-        for e in replicas:                      # experts of other ranks this rank also holds
-            self.local[e] = layer["experts"][e]
+        self.held = list(range(self.lo, self.lo + self.el)) + list(replicas)   # replicas: experts of other ranks held too
         self.owners = None
+        self._use(0)
+
+    def _use(self, layer_idx):
+        """Every layer of a stack has weights of its own."""
+        self.layer = self.layers[layer_idx]
+        self.local = {e: self.layer["experts"][e] for e in self.held}
 
     def set_owners(self, layer_idx, owners):
         if owners is not None:
@@ -43,6 +47,7 @@ class OracleStages:
         self.owners = owners
 
     def route(self, layer_idx, x, send_rows, counts):
+        self._use(layer_idx)
         _, ids, w = O.route(self.cfg, x, self.layer["wg"], self.layer["bias"])
         c, off, perm = O.bucket(ids, self.n_experts)
         self.w, self.perm = w, perm
@@ -63,6 +68,7 @@ class OracleStages:
             self.shared_out = O.expert_ffn(x, *self.layer["shared"].bf16())
 
     def partial(self, layer_idx, x_all, t0, T_local, partial):
+        self._use(layer_idx)
         cfg = self.cfg
         _, ids, w = O.route(cfg, x_all, self.layer["wg"], self.layer["bias"])
         partial.zero_()
@@ -118,6 +124,12 @@ def main():
     replica_case = scheme.endswith("_replica")
     if replica_case:
         scheme = scheme[:-len("_replica")]
+    # a stack of layers, each with weights of its own, the output of one feeding the next (the shape
+    # of the full-model configuration: 58 such layers over the GPUs of a box)
+    stack_case = scheme.endswith("_stack")
+    if stack_case:
+        scheme = scheme[:-len("_stack")]
+    layers = [layer] + ([OC.make_layer(cfg, 777 + 100 * l) for l in (1, 2)] if stack_case else [])
     replicas = ([cfg.n_experts - 1] if rank == 0 else [0] if rank == 1 else []) if replica_case else []
     if scheme in ("gather", "peer"):        # equal batches
         T_global -= T_global % world
@@ -128,7 +140,7 @@ def main():
         bounds = [T_global * r // world + (1 if 0 < r < world else 0) for r in range(world + 1)]
     lo, hi = bounds[rank], bounds[rank + 1]
     if mode == "cpu":
-        stages = OracleStages(cfg, layer, rank, world, replicas)
+        stages = OracleStages(cfg, layers, rank, world, replicas)
         xl = x[lo:hi].contiguous()
         be = None
     else:
@@ -137,15 +149,17 @@ def main():
         from ek_b200.backend import expert_tensors
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         be = ek_b200.Backend(Hh.backend_config(cfg, max_tokens=T_global, device=torch.cuda.current_device(),
-                                               ep_rank=rank, ep_size=world, replica_slots=len(replicas)))
-        be.register_router(0, layer["wg"], layer["bias"])
+                                               ep_rank=rank, ep_size=world, replica_slots=len(replicas),
+                                               max_layers=len(layers)))
         el = cfg.n_experts // world
-        for e in list(range(rank * el, (rank + 1) * el)) + replicas:
-            w = layer["experts"][e]
-            be.register_expert(be.expert_id(0, e), expert_tensors(0, e, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
-        w = layer["shared"]
-        be.register_expert(be.shared_id(0), expert_tensors(0, None, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s,
-                                                           shared=True))
+        for li, lay in enumerate(layers):
+            be.register_router(li, lay["wg"], lay["bias"])
+            for e in list(range(rank * el, (rank + 1) * el)) + replicas:
+                w = lay["experts"][e]
+                be.register_expert(be.expert_id(li, e), expert_tensors(li, e, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s))
+            w = lay["shared"]
+            be.register_expert(be.shared_id(li), expert_tensors(li, None, w.up, w.gate, w.down, w.up_s, w.gate_s, w.down_s,
+                                                                shared=True))
         be.set_stream(torch.cuda.current_stream().cuda_stream)
         stages = ek_b200.BackendStages(be)
         xl = x[lo:hi].contiguous().cuda()
@@ -167,6 +181,38 @@ def main():
             assert (d.max() / ref["y"][lo:hi].float().abs().max()).item() <= 2e-2, f"step {step}: wrong with owners {owners.tolist()}"
         assert len(served) > 1, "the replicated experts never changed hands"
         y = moe.forward(0, xl, owners=None)  # and back to the window rule
+    if stack_case:
+        # Each layer is checked on the input the stack really gave it: the ranks' slices are gathered
+        # and the single-process oracle evaluates that layer on them (an error of layer l cannot hide
+        # behind, or be blamed on, a routing flip it causes in layer l + 1).  Twice over the stack:
+        # buffers and step parities are reused across layers and passes.
+        ok = True
+        for rnd in range(2):
+            xin = xl
+            for li, lay in enumerate(layers):
+                y = moe.forward(li, xin)
+                if be is not None:
+                    be.sync()
+                x_all = torch.empty(T_global, cfg.hidden, dtype=xin.dtype, device=xin.device)
+                dist.all_gather_into_tensor(x_all, xin.contiguous())
+                want = O.moe_layer(cfg, x_all.cpu(), lay["wg"], lay["bias"], lay["experts"], lay["shared"])["y"][lo:hi]
+                d = (y.cpu().float() - want.float()).abs()
+                max_rel = (d.max() / want.float().abs().max()).item()
+                # the outputs grow from layer to layer (the gain below overshoots): the mean-abs bound of
+                # unit-scale outputs, 1e-3 at mean|ref| <= 0.1, grows with them
+                mean_ref = want.float().abs().mean().item()
+                good = max_rel <= 2e-2 and d.mean().item() <= 1e-3 * max(1.0, mean_ref / 0.1)
+                ok = ok and good
+                print(f"rank {rank}/{world} round {rnd} layer {li} max-rel {max_rel:.3e} mean-abs {d.mean().item():.3e} "
+                      f"mean|ref| {mean_ref:.3f} {'good' if good else 'BAD'}", flush=True)
+                xin = (y * 16).to(xin.dtype)          # back to unit scale; a power of two, exact in bf16
+        print(f"rank {rank}/{world} stack of {len(layers)} layers {'OK' if ok else 'FAIL'}", flush=True)
+        if be is not None:
+            moe.close()
+            be.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if ok else 1)
     for _ in range(0 if replica_case else 3):   # several times: buffers, staging areas and step parities are reused
         y = moe.forward(0, xl)
     if be is not None:

@@ -49,6 +49,14 @@ def test_replicated_experts_follow_the_owner_table_over_gloo():
     assert r.stdout.count("OK") == 2
 
 
+def test_stack_of_layers_over_gloo():
+    """Three layers with weights of their own, each fed the previous one's output, every layer
+    checked against the single-process oracle on the input it really got."""
+    r = _launch(2, "cpu", 29645, "gather_stack")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == 2 and r.stdout.count("good") == 2 * 2 * 3
+
+
 def test_choose_owners_is_the_same_on_every_rank_and_rotates():
     from ek_b200.ep import choose_owners
     holders = [[0], [0, 1], [1], [1, 0]]
@@ -70,6 +78,19 @@ def test_expert_parallel_over_nccl_matches_oracle(scheme):
     r = _launch(2, "gpu", 29650 + {"a2a": 0, "gather": 1, "peer": 2, "gather_replica": 3, "peer_replica": 4}[scheme], scheme)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("OK") == 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("scheme", ["peer_stack", "gather_stack"])
+def test_stack_of_layers_over_nccl_matches_oracle(scheme):
+    """The shape of the full-model configuration in small: a stack of expert-parallel layers with
+    weights of their own on 2 GPUs, the output of a layer feeding the next, every layer checked."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    r = _launch(2, "gpu", 29660 + (scheme == "gather_stack"), scheme)
+    print("\n".join(ln for ln in r.stdout.splitlines() if " layer " in ln))      # the measured margins, for -rP
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("OK") == 2 and r.stdout.count("good") == 2 * 2 * 3
 
 
 @pytest.mark.gpu
