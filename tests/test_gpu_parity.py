@@ -142,6 +142,23 @@ def test_cfg1_full_layer(quant):
     be.close()
 
 
+@pytest.mark.parametrize("quant", ["bf16", "fp8"])
+def test_every_token_routes_to_the_same_experts(quant):
+    """Maximal skew through the fused call: 300 copies of one token (plus a few others) put 300 rows
+    on each of its experts - three chunks of 128 + 128 + 44 rows - and leave most experts empty."""
+    cfg, layer, x = _cfg_case(1, 8, quant=quant)
+    T = 300
+    x = torch.cat([x[:1].expand(T, -1), x[1:]]).contiguous()
+    ref = O.moe_layer(cfg, x, layer["wg"], layer["bias"], layer["experts"], layer["shared"])
+    assert int(ref["counts"].max()) >= T and int((ref["counts"] == 0).sum()) > 0
+    be = _backend(cfg, layer, x.shape[0])
+    y, art = be.moe_forward_fused(0, x, debug=True)
+    _check_routing(art, ref, False)
+    _close(y, ref["y"], f"maximal skew {quant}")
+    assert torch.equal(y[:T], y[:1].expand(T, -1)), "equal tokens must get equal outputs"
+    be.close()
+
+
 @pytest.fixture(scope="module")
 def cfg2_full():
     """Qwen3-30B-A3B layer at its full size: 128 experts, top-8, bf16 weights, Zipf(1.1) load."""
