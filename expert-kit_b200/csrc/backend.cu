@@ -134,6 +134,7 @@ struct ek_backend {
   float* sk_buf = nullptr;             // partial accumulators of K-split work items
   uint32_t* sk_flags = nullptr;
   int split_k = 1;
+  int weights_ahead = 1;
   DevStatus* h_status = nullptr;       // pinned
   ChunkDesc* h_chunks = nullptr;       // pinned, worker-level call
   int h_chunks_cap = 0;
@@ -483,6 +484,7 @@ FfnParams ffn_params(ek_backend* be, const Layer& L) {
   p.n_sm = be->n_sm;
   p.precise = be->precise;
   p.split_k = be->split_k;
+  p.weights_ahead = 0;
   p.sk_buf = be->sk_buf;
   p.sk_flags = be->sk_flags;
   return p;
@@ -539,10 +541,13 @@ int finish_timing(ek_backend* be) {
   return EK_OK;
 }
 
-// Runs gate/up + down over the work list already on the device.
-void run_ffn(ek_backend* be, const Layer& L, int nmax, int which, bool allow_split = true) {
+// Runs gate/up (which = 0) or down (1) over the work list already on the device.  `list_older`: the
+// kernel launched just before this one is not the one that wrote the work list (always true for down:
+// gate/up is in front of it).
+void run_ffn(ek_backend* be, const Layer& L, int nmax, int which, bool allow_split = true, bool list_older = false) {
   FfnParams p = ffn_params(be, L);
   if (!allow_split) p.split_k = 0;
+  p.weights_ahead = be->weights_ahead && (which == 1 || list_older);
   if (be->ffn_impl == 1) {
     p.chunk_rows = 16;
     be->launches += launch_ffn_simt(p, which, be->stream);
@@ -705,7 +710,7 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
   }
   L.have_counts = true;
   mark(be, 2);
-  run_ffn(be, L, nmax, 0);
+  run_ffn(be, L, nmax, 0, true, /*list_older=*/!gathered);   // a gather launch of its own sits between the work list and gate/up
   if (debug_sync_failed(be, "gate/up GEMM")) return EK_CUDA;
   mark(be, 3);
   run_ffn(be, L, nmax, 1);
@@ -904,11 +909,13 @@ int32_t ek_backend_create(const ek_config_t* cfg, ek_backend_t** out) {
     return cleanup_fail(EK_CUDA);
   }
   // measurement switches (they take single kernels out of the pass to time what each is worth; the
-  // results are the same either way): EK_B200_FRONT_SMALL=0, EK_B200_SPLIT_K=0
+  // results are the same either way): EK_B200_FRONT_SMALL=0, EK_B200_SPLIT_K=0, EK_B200_WEIGHTS_AHEAD=0
   const char* fs = getenv("EK_B200_FRONT_SMALL");
   if (fs && fs[0] == '0') be->front_small = 0;
   const char* sk = getenv("EK_B200_SPLIT_K");
   if (sk && sk[0] == '0') be->split_k = 0;
+  const char* wa = getenv("EK_B200_WEIGHTS_AHEAD");
+  if (wa && wa[0] == '0') be->weights_ahead = 0;
   *out = be;
   return EK_OK;
 }

@@ -246,6 +246,8 @@ struct FfnParams {
   int32_t n_sm;
   int32_t precise;           // quantised weights: bf16_rne(float(w) * scale) as the A operand (bit-exact reference dequantisation)
   int32_t split_k;           // cut the work items left over after the last full wave along K over all CTAs
+  int32_t weights_ahead;     // the weight producer does not wait for the kernel launched in front of this one: allowed
+                             // only if that kernel does not write the work list
   float* sk_buf;             // [n_sm][2][128][128] fp32 partial accumulators of split items
   uint32_t* sk_flags;        // [n_sm][32] one word per (CTA, warp): partial written; zero between launches
 };

@@ -137,6 +137,14 @@ __device__ __forceinline__ void report(DevStatus* st, int code, int where, int a
 struct Unit {
   int item, kt0, kt1;
 };
+__device__ __forceinline__ ChunkDesc load_chunk(const ChunkDesc* c) {   // from L2: see the weight producer
+  static_assert(sizeof(ChunkDesc) == 16, "one 16-byte load");
+  const int4 v = __ldcg(reinterpret_cast<const int4*>(c));
+  ChunkDesc d;
+  d.slot = v.x; d.in_row = v.y; d.out_row = v.z; d.n_rows = v.w;
+  return d;
+}
+
 struct Sched {
   int KT, n_full, tail_hi, next_item, g, L;
   __device__ __forceinline__ Sched(int total, int KT_, int split_k) {
@@ -470,10 +478,17 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  // barriers and tensor memory are this CTA's own; everything below reads what earlier kernels wrote
-  pdl_wait();
+  // barriers and tensor memory are this CTA's own; everything below reads what earlier kernels wrote.
+  // One thread may go ahead (`weights_ahead`): the weight producer, when the kernel launched in front
+  // of this one does not write the work list - gate/up in front of a down GEMM, the row gather in
+  // front of gate/up.  The list was then complete before that kernel began, and registered weights
+  // do not change during a pass: the stages fill with weight tiles while the last CTAs of the
+  // kernel in front are still at work.  The producer reads the work list past L1 (a line kept from an
+  // earlier pass must not be used).
+  const bool ahead = p.weights_ahead && warp == kConvWarps;
+  if (!ahead) pdl_wait();
   pdl_trigger();
-  const int n_chunks = *p.n_chunks;
+  const int n_chunks = __ldcg(p.n_chunks);
   const int n_rt = GATEUP ? p.d.it : p.d.hp;       // work items per chunk
   const int KT = GATEUP ? p.d.kt_gu : p.d.kt_dn;   // K tiles of the GEMM = pipeline stages per work item
   const int total = n_chunks * n_rt;
@@ -494,7 +509,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_tc_kernel(const __grid_consta
       Sched sched(total, KT, p.split_k);
       Unit u;
       while (ok && sched.next(u)) {
-        ChunkDesc cd = p.chunks[u.item / n_rt];
+        ChunkDesc cd = load_chunk(p.chunks + u.item / n_rt);
         // weights that the neighbouring items read again stay in L2; the rest is streamed through
         const bool reread = (cd.n_rows & kChunkMulti) != 0;
         cd.n_rows &= kChunkRowsMask;
