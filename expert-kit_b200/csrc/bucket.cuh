@@ -18,15 +18,18 @@ __device__ __forceinline__ uint4 bf16x8_to_f16x8(uint4 v) {
 
 // Chunk descriptors: every expert this rank serves has its row range cut into pieces of `chunk_rows`,
 // followed by the virtual shared experts (all T tokens each).  One CTA of NT threads.
+// `s_counts` / `s_offsets`: the histogram and the offsets in shared memory when the calling CTA made
+// them itself (the fused front kernel); null: read from global memory at L2.
 template <int NT>
-__device__ __forceinline__ void build_worklist(const WorklistParams& p) {
+__device__ __forceinline__ void build_worklist(const WorklistParams& p, const int* s_counts = nullptr,
+                                               const int* s_offsets = nullptr) {
   static_assert(NT % 32 == 0 && NT <= 1024, "whole warps");
   __shared__ int s_scan[64];
   __shared__ int s_total;
   const int tid = threadIdx.x;
   const int n_local = p.e_hi - p.e_lo;
   if (p.counts_copy)
-    for (int e = tid; e < p.E; e += NT) p.counts_copy[e] = __ldcg(&p.counts[e]);
+    for (int e = tid; e < p.E; e += NT) p.counts_copy[e] = s_counts ? s_counts[e] : __ldcg(&p.counts[e]);
   // experts this rank serves: its window (slot = e - e_lo), or, with an owner table, every expert
   // the table gives to this rank (slot from the layer's slot table: own experts and replicas)
   const int first = p.owners ? 0 : p.e_lo, last = p.owners ? p.E : p.e_hi;
@@ -35,7 +38,7 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
     const int e = e0 + tid;
     int cnt = 0, nch = 0, slot = -1;
     if (e < last && (!p.owners || p.owners[e] == p.rank)) {
-      cnt = __ldcg(&p.counts[e]);   // the histogram is built with atomics: read it at L2
+      cnt = s_counts ? s_counts[e] : __ldcg(&p.counts[e]);   // the histogram is built with atomics: read it at L2
       slot = p.slot_of ? p.slot_of[e] : e - p.e_lo;
       nch = (cnt + p.chunk_rows - 1) / p.chunk_rows;
       if (cnt > 0 && (slot < 0 || !p.registered[slot])) {
@@ -69,7 +72,7 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p) {
     int first_chunk = running + before + inc - nch;
     if (tid == NT - 1) s_total = before + inc;
     if (nch > 0) {
-      const int off = __ldcg(&p.offsets[e]);   // may have been written by another CTA of this kernel
+      const int off = s_offsets ? s_offsets[e] : __ldcg(&p.offsets[e]);   // may have been written by another CTA of this kernel
       for (int c = 0; c < nch; ++c) {
         if (first_chunk + c >= p.max_chunks) break;
         ChunkDesc d;

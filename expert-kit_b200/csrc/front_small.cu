@@ -28,6 +28,7 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kMaxT = 8;         // tokens (one warp each in phase 2); beyond that the separate kernels are as fast
 constexpr int kMaxE = 256;       // experts
+constexpr int kMaxTk = 1024;     // assignments (T * k)
 constexpr int kSlice = 512;      // K elements per CTA of phase 1: two 16-byte vectors per lane
 constexpr int kTokBatch = 4;     // tokens in flight per warp (independent loads and butterflies)
 
@@ -49,8 +50,6 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
   const int T = r.T, E = r.E, H = r.H;
   pdl_wait();
   pdl_trigger();
-  if (blockIdx.x == 0 && blockIdx.y == 0)
-    for (int e = tid; e < E; e += kThreads) r.counts[e] = 0;
 
   // ---- phase 1: partial logits of (K slice blockIdx.x, experts blockIdx.y * 32 + warp) -----------
   {
@@ -107,8 +106,20 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
   __threadfence();
 
   // ---- phase 2: logits = partial sums in slice order; then routing, one warp per token ---------
+  // Everything the CTA makes and uses again stays in shared memory (logits, ids, weights, histogram,
+  // offsets, permutation): the chain of steps below would otherwise pay a round trip to L2 at every
+  // hand-over.  The results go to global memory on the side, for the kernels behind and the caller.
+  __shared__ float s_logits[kMaxT * kMaxE];
+  __shared__ float s_w[kMaxTk];
+  __shared__ int s_ids[kMaxTk];
+  __shared__ int s_perm[kMaxTk];
+  __shared__ int s_hist[kMaxE];                         // the histogram over all experts
+  __shared__ int s_cnt[kMaxE];                          // ... of the experts this rank serves (0 elsewhere)
+  __shared__ int s_off[kMaxE + 1];
+  const int Tk = T * r.k;
   {
     const int n_slices = (int)gridDim.x;
+    for (int e = tid; e < E; e += kThreads) s_hist[e] = 0;
     for (int o = tid; o < T * E; o += kThreads) {
       float v = 0.f;
       for (int c0 = 0; c0 < n_slices; c0 += 16) {
@@ -119,23 +130,35 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
         for (int a = 0; a < 16; ++a) v += tmp[a];
       }
       // the softmax router's linear layer runs in bf16 in the reference
-      r.logits[o] = r.scoring == EK_SCORE_SOFTMAX ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+      v = r.scoring == EK_SCORE_SOFTMAX ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+      s_logits[o] = v;
+      r.logits[o] = v;
     }
     __syncthreads();
     float* sc = smem + (size_t)warp * (2 * kMaxE + 64);
-    if (warp < T) select_token(r, warp, lane, sc, sc + kMaxE, sc + 2 * kMaxE);   // r.partial is null: the logits are final
+    if (warp < T) {
+      RouteParams rs = r;                               // the same routine as the stand-alone select kernel, on shared memory
+      rs.logits = s_logits;
+      rs.ids = s_ids;
+      rs.weights = s_w;
+      rs.counts = s_hist;
+      rs.partial = nullptr;                             // the logits are final
+      select_token(rs, warp, lane, sc, sc + kMaxE, sc + 2 * kMaxE);
+    }
   }
   __syncthreads();
   // ---- offsets: exclusive scan of the counts of the experts this rank serves -------------------
-  int* s_cnt = reinterpret_cast<int*>(smem);            // [kMaxE] (the routing scratch is free again)
-  int* s_off = s_cnt + kMaxE;                           // [kMaxE + 1]
-  int* s_ids = s_off + kMaxE + 1;                       // [T * k]
   const PermuteParams& pp = p.permute;
   auto is_local = [&](int j) { return pp.owners ? pp.owners[j] == pp.rank : (j >= pp.e_lo && j < pp.e_hi); };
-  const int Tk = T * r.k;
-  __syncthreads();
-  if (tid < E) s_cnt[tid] = is_local(tid) ? __ldcg(&r.counts[tid]) : 0;   // written with atomics: read at L2
-  for (int i = tid; i < Tk; i += kThreads) s_ids[i] = r.ids[i];
+  for (int i = tid; i < Tk; i += kThreads) {
+    r.ids[i] = s_ids[i];
+    r.weights[i] = s_w[i];
+  }
+  if (tid < E) {
+    const int c = s_hist[tid];
+    r.counts[tid] = c;
+    s_cnt[tid] = is_local(tid) ? c : 0;
+  }
   __syncthreads();
   if (warp == 0) {                                      // E <= 256: eight experts per lane
     int v[8], sum = 0;
@@ -170,14 +193,15 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
       for (int j = 0; j < i; ++j) rank += s_ids[j] == e;
       const int pos = s_off[e] + rank;
       pp.perm[pos] = i;
+      s_perm[pos] = i;
       pp.inv[i] = pos;
     } else {
       pp.inv[i] = -1;
     }
   }
-  __syncthreads();                                      // counts / offsets / perm are in global memory for this CTA
+  __syncthreads();
   // ---- chunk work list -----------------------------------------------------------------------------
-  build_worklist<kThreads>(p.worklist);
+  build_worklist<kThreads>(p.worklist, s_hist, s_off);
   // ---- row gather (only when the host asked for it: a handful of rows) --------------------------------
   if (p.gather_rows) {
     __syncthreads();
@@ -189,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
       int src;
       if (row < Tk) {
         if (row >= n_routed) continue;
-        src = pp.perm[row] / r.k;
+        src = s_perm[row] / r.k;
       } else {
         src = p.shared_t0 + row - Tk;
       }
