@@ -657,6 +657,8 @@ int run_layer(ek_backend* be, Layer& L, const __nv_bfloat16* x, int T, int k, co
     fp.ticket = be->front_ticket;
     fp.xp = be->xp;
     fp.gather_rows = Tk + sh_T <= 24 ? 1 : 0;
+    // a batch of one token: all its rows are the same, one copy serves every expert
+    fp.worklist.same_row = (T == 1 && fp.gather_rows && (sh_T == 0 || opt.sh_t0 == 0)) ? 1 : 0;
     fp.shared_t0 = opt.sh_t0; fp.shared_T = sh_T;
     fp.to_f16 = f16_rows(be) ? 1 : 0;
     be->launches += launch_front_small(fp, s);

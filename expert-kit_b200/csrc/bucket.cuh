@@ -77,8 +77,8 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p, const in
         if (first_chunk + c >= p.max_chunks) break;
         ChunkDesc d;
         d.slot = slot;
-        d.in_row = off + c * p.chunk_rows;
-        d.out_row = d.in_row;
+        d.out_row = off + c * p.chunk_rows;
+        d.in_row = p.same_row ? 0 : d.out_row;
         d.n_rows = min(p.chunk_rows, cnt - c * p.chunk_rows) | (nch > 1 ? kChunkMulti : 0);
         p.chunks[first_chunk + c] = d;
       }
@@ -94,7 +94,7 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p, const in
     if (running + i >= p.max_chunks) break;
     ChunkDesc d;
     d.slot = n_local + j;
-    d.in_row = p.Tk + c * p.chunk_rows;
+    d.in_row = p.same_row ? 0 : p.Tk + c * p.chunk_rows;
     d.out_row = p.Tk + j * p.T + c * p.chunk_rows;
     d.n_rows = min(p.chunk_rows, p.T - c * p.chunk_rows) | (per_shared > 1 ? kChunkMulti : 0);
     p.chunks[running + i] = d;

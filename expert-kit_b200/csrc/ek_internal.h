@@ -188,6 +188,7 @@ struct WorklistParams {
   int32_t Tk;
   int32_t max_chunks;
   DevStatus* status;
+  int32_t same_row = 0;      // a batch of one token: every chunk reads activation row 0 (the one row that is gathered)
 };
 // permutation and work list in one launch (the CTA that finishes last builds the list); `ticket`: a zeroed counter
 struct PermuteWorklistParams {

@@ -206,19 +206,26 @@ __global__ void __launch_bounds__(kThreads, 1) front_small_kernel(const __grid_c
   if (p.gather_rows) {
     __syncthreads();
     const int n_routed = s_off[E];
-    const int rows = Tk + p.shared_T;
+    // one token: its row is gathered once, to row 0, and every chunk of the work list reads it there
+    const int rows = p.worklist.same_row ? 1 : Tk + p.shared_T;
     const int nv = H / 8;
-    for (int idx = tid; idx < rows * nv; idx += kThreads) {
-      const int row = idx / nv, v = idx % nv;
-      int src;
-      if (row < Tk) {
-        if (row >= n_routed) continue;
-        src = s_perm[row] / r.k;
-      } else {
-        src = p.shared_t0 + row - Tk;
+    // a thread owns a 16-byte column of the rows; four rows in flight (the loads are what this step costs)
+    for (int v = tid; v < nv; v += kThreads) {
+      for (int row0 = 0; row0 < rows; row0 += 4) {
+        uint4 val[4];
+        bool ok[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int row = row0 + u;
+          ok[u] = row < rows && (p.worklist.same_row || row >= Tk || row < n_routed);
+          const int src = !ok[u] || p.worklist.same_row ? 0 : row < Tk ? s_perm[row] / r.k : p.shared_t0 + row - Tk;
+          if (ok[u]) val[u] = reinterpret_cast<const uint4*>(r.x + (size_t)src * H)[v];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (ok[u])
+            reinterpret_cast<uint4*>(p.xp + (size_t)(row0 + u) * H)[v] = p.to_f16 ? bf16x8_to_f16x8(val[u]) : val[u];
       }
-      const uint4 val = reinterpret_cast<const uint4*>(r.x + (size_t)src * H)[v];
-      reinterpret_cast<uint4*>(p.xp + (size_t)row * H)[v] = p.to_f16 ? bf16x8_to_f16x8(val) : val;
     }
   }
 }

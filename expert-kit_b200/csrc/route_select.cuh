@@ -10,17 +10,17 @@
 
 namespace ek {
 
-// (value, index) argmax with the canonical tie rule: larger value first, then lower index.
+// (value, index) argmax over the warp with the canonical tie rule: larger value first, then lower
+// index.  Two warp reductions instead of a butterfly of shuffles: the maximum of the values mapped to
+// unsigned integers that order like the floats (no NaN reaches this point; -0 is folded into +0 so
+// that equal floats map to equal integers), then the lowest index among the lanes that hold it.
+// Every lane returns the winner.
 __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, v, o);
-    int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (ov > v || (ov == v && oi < idx)) {
-      v = ov;
-      idx = oi;
-    }
-  }
+  const uint32_t b = __float_as_uint(v + 0.0f);
+  const uint32_t key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+  idx = (int)__reduce_min_sync(0xffffffffu, key == best ? (uint32_t)idx : 0xffffffffu);
+  v = __uint_as_float((best & 0x80000000u) ? (best & 0x7fffffffu) : ~best);
 }
 
 // One warp routes token t.  `sc`, `ch`: per-warp scratch of E floats each (unbiased scores, scores used
@@ -78,10 +78,21 @@ __device__ __forceinline__ void select_token(const RouteParams& p, int t, int la
       ch[e] = pr;
     }
   } else {
-    for (int e = lane; e < E; e += 32) {
-      float s = 1.f / (1.f + expf(-lg[e]));
-      sc[e] = s;
-      ch[e] = p.bias ? s + p.bias[e] : s;
+    // the correction bias comes from global memory: eight loads in flight, not one per round behind
+    // the stores of the round before
+    for (int e0 = lane; e0 < E; e0 += 256) {
+      float b[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) b[j] = (p.bias && e0 + 32 * j < E) ? __ldg(&p.bias[e0 + 32 * j]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = e0 + 32 * j;
+        if (e < E) {
+          float s = 1.f / (1.f + expf(-lg[e]));
+          sc[e] = s;
+          ch[e] = p.bias ? s + b[j] : s;
+        }
+      }
     }
   }
   __syncwarp();
