@@ -34,6 +34,10 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p, const in
   // the table gives to this rank (slot from the layer's slot table: own experts and replicas)
   const int first = p.owners ? 0 : p.e_lo, last = p.owners ? p.E : p.e_hi;
   int running = 0;
+  // shared virtual experts: their registration flags are fetched now, alongside the loads of the loop below
+  const int per_shared = (p.T + p.chunk_rows - 1) / p.chunk_rows;
+  int shared_registered = 1;
+  if (tid < p.n_shared * per_shared && tid % per_shared == 0) shared_registered = p.registered[n_local + tid / per_shared];
   for (int e0 = first; e0 < last; e0 += NT) {
     const int e = e0 + tid;
     int cnt = 0, nch = 0, slot = -1;
@@ -88,7 +92,6 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p, const in
     __syncthreads();
   }
   // shared virtual experts
-  const int per_shared = (p.T + p.chunk_rows - 1) / p.chunk_rows;
   for (int i = tid; i < p.n_shared * per_shared; i += NT) {
     const int j = i / per_shared, c = i % per_shared;
     if (running + i >= p.max_chunks) break;
@@ -98,14 +101,14 @@ __device__ __forceinline__ void build_worklist(const WorklistParams& p, const in
     d.out_row = p.Tk + j * p.T + c * p.chunk_rows;
     d.n_rows = min(p.chunk_rows, p.T - c * p.chunk_rows) | (per_shared > 1 ? kChunkMulti : 0);
     p.chunks[running + i] = d;
-    if (c == 0 && !p.registered[d.slot]) {
+    if (c == 0 && !(i == tid ? shared_registered : p.registered[d.slot])) {
       if (atomicCAS(&p.status->code, DEV_OK, DEV_MISSING_EXPERT) == DEV_OK) {
         p.status->where = 3;
         p.status->aux0 = -1 - j;
       }
     }
   }
-  __threadfence();
+  // (the list is read by later kernels only: the end of this kernel publishes it, no fence needed here)
   __syncthreads();
   if (tid == 0) {
     int total = running + p.n_shared * per_shared;

@@ -99,13 +99,31 @@ __device__ __forceinline__ void select_token(const RouteParams& p, int t, int la
 
   if (p.n_group > 1) {
     const int per = E / p.n_group;
-    for (int g = lane; g < p.n_group; g += 32) {
-      float a = -INFINITY, b = -INFINITY;  // two largest
-      for (int j = 0; j < per; ++j) {
-        float v = ch[g * per + j];
+    const int lpg = 32 / p.n_group;          // lanes per group, when the groups divide the warp
+    if (p.n_group <= 32 && lpg * p.n_group == 32 && per % lpg == 0) {
+      // all lanes at work: a group's members are split over `lpg` neighbouring lanes, each keeps its
+      // two largest, a butterfly inside the group merges them (the sum of the two largest does not
+      // depend on the order they were found in)
+      const int g = lane / lpg, sub = lane % lpg;
+      float a = -INFINITY, b = -INFINITY;
+      for (int j = sub; j < per; j += lpg) {
+        const float v = ch[g * per + j];
         if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
       }
-      gs[g] = a + b;
+      for (int o = lpg >> 1; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+        if (oa > a) { b = fmaxf(a, ob); a = oa; } else { b = fmaxf(b, oa); }
+      }
+      if (sub == 0) gs[g] = a + b;
+    } else {
+      for (int g = lane; g < p.n_group; g += 32) {
+        float a = -INFINITY, b = -INFINITY;  // two largest
+        for (int j = 0; j < per; ++j) {
+          float v = ch[g * per + j];
+          if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+        }
+        gs[g] = a + b;
+      }
     }
     __syncwarp();
     // keep the best topk_group groups (descending score, ties towards the lower group)
